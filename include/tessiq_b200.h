@@ -1,0 +1,337 @@
+/* tessiq_b200 — C ABI of the B200 (sm_100a) kernel layer for tessiq's data-parallel hot path.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns a `tq_status`, and
+ * leaves a human-readable reason in a thread-local slot read with `tq_last_error()`. Nothing here
+ * names a torch type. Unless an entry point says otherwise:
+ *
+ *   - every data pointer is DEVICE memory on CUDA device `device` (the CUDA ordinal, i.e. the
+ *     reference's `tessiq:k` is ordinal k-1);
+ *   - `stream` is a raw `cudaStream_t` (0 = the legacy default stream); launches are asynchronous
+ *     and the caller orders readers of the result through that stream, exactly like
+ *     `Kernel::launch(tensors, out, stream)` in the reference (csrc/tessiq/torch/kernel.h:59-66);
+ *   - a zero-element problem launches nothing and returns TQ_OK
+ *     (csrc/tessiq/torch/fused.cpp:157-160, csrc/tessiq/torch/pack.cpp:93-96);
+ *   - TQ_UNSUPPORTED means "decline": the arguments are well formed but there is no kernel for
+ *     them; the reference's caller then runs its own fallback (csrc/tessiq/support/error.h:17-18).
+ *     This library never computes anything on the host.
+ *
+ * Status codes map one to one onto the reference's `ErrorCode` (csrc/tessiq/support/error.h:14-27)
+ * so a binding keeps the reference's exception mapping (csrc/bindings/module.cpp:75-92).
+ */
+#ifndef TESSIQ_B200_H_
+#define TESSIQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t tq_status;
+enum {
+  TQ_OK = 0,
+  TQ_INVALID_ARGUMENT = 1,   /* ErrorCode::kInvalidArgument   -> ValueError   */
+  TQ_UNSUPPORTED = 2,        /* ErrorCode::kUnsupported       -> TypeError (decline) */
+  TQ_NOT_FOUND = 3,          /* ErrorCode::kNotFound          -> KeyError     */
+  TQ_RESOURCE_EXHAUSTED = 4, /* ErrorCode::kResourceExhausted -> MemoryError  */
+  TQ_EXTERNAL = 5,           /* ErrorCode::kExternal          -> RuntimeError */
+  TQ_INTERNAL = 6            /* ErrorCode::kInternal          -> RuntimeError */
+};
+
+/* Element types. The numbering is this library's own; the reference's are ir::DType
+ * (csrc/tessiq/ir/types.h:18-26) and codegen::ElementType (csrc/tessiq/codegen/precompiled.h:36-47). */
+typedef int32_t tq_dtype;
+enum {
+  TQ_F32 = 0,
+  TQ_F64 = 1,
+  TQ_F16 = 2,
+  TQ_BF16 = 3,
+  TQ_I32 = 4,
+  TQ_I64 = 5,
+  TQ_BOOL = 6 /* one byte, 0 or 1 */
+};
+
+/* ------------------------------------------------------------------------------------------ */
+/* Library                                                                                      */
+
+/* ABI version of this header: major*1000 + minor. */
+int32_t tq_abi_version(void);
+
+/* The reason for the calling thread's most recent non-OK status. Never null; valid until the
+ * thread's next failing call. Replaces Error::message() (csrc/tessiq/support/error.h:37). */
+const char* tq_last_error(void);
+
+/* Bytes per element of `dtype`, or 0 for an unknown code. */
+int32_t tq_dtype_size(tq_dtype dtype);
+
+/* Number of CUDA devices visible (0 without a driver; never an error).
+ * Replaces the CUDA half of registry device discovery (csrc/tessiq/runtime/registry.cpp:25-67). */
+int32_t tq_device_count(void);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Runtime: per-GPU streams and a per-GPU arena                                                 */
+/* Replaces CudaDevice's single blocking copy stream and legacy-stream launches                 */
+/* (csrc/tessiq/runtime/cuda_device.cpp:34-147) and the stubbed getStream/recordStream          */
+/* (csrc/tessiq/torch/backend.cpp:165-168,357-363).                                             */
+
+/* Creates a non-blocking stream on `device`. */
+tq_status tq_stream_create(int32_t device, void** stream);
+tq_status tq_stream_destroy(int32_t device, void* stream);
+tq_status tq_stream_synchronize(int32_t device, void* stream);
+
+/* A bump arena: one cudaMalloc of `bytes` on `device`, carved by offset. This is the device side
+ * of the reference's arena memory plan (csrc/tessiq/ir/recipe.cpp:56, which the reference's
+ * executor never used). `tq_arena_at` returns base+offset after a bounds check. */
+typedef struct tq_arena tq_arena;
+tq_status tq_arena_create(int32_t device, size_t bytes, tq_arena** arena);
+tq_status tq_arena_destroy(tq_arena* arena);
+tq_status tq_arena_at(const tq_arena* arena, size_t offset, size_t bytes, void** pointer);
+size_t tq_arena_bytes(const tq_arena* arena);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Fused elementwise chains                                                                     */
+/* Replaces CudaEmitter::emit(FusedKernel) + compile_cached + load_program                      */
+/* (csrc/tessiq/codegen/cuda_emitter.cpp:212-255, csrc/tessiq/torch/fused.cpp:470-527) and      */
+/* FusedKernel::launch (csrc/tessiq/torch/fused.cpp:127-194); also the eager one-op kernels of  */
+/* run_elementwise (csrc/tessiq/torch/eager.cpp:461-493,546-624).                                */
+
+/* One compiled fusion group. `program` is a text description, one statement per line:
+ *
+ *     math fast|precise                      optional; default fast (see tq_fused_create)
+ *     in <name> <dtype> same|repeated|cycled|strided
+ *     scalar <name> <dtype>                  a by-value argument, given at launch as a double
+ *     <name> = <op> <arg> [<arg> [<arg>]]    arg: a value name or a numeric literal
+ *     <name> = cast <arg> <dtype>
+ *     out <name> <dtype>
+ *
+ * dtypes: f32 f64 f16 bf16 i32 i64 bool. `same` reads element i, `repeated` reads i / d (one
+ * operand element per run of d outputs, e.g. an [N,1] column), `cycled` reads i % d (e.g. a bias
+ * row), `strided` maps i through sizes/strides given at launch — the four kinds of
+ * OperandRead (csrc/tessiq/codegen/kernel.h:33-66, csrc/tessiq/codegen/kernel.cpp:210-244).
+ * Ops are the reference's ops.toml elementwise names (abs add div mul neg relu sigmoid sqrt sub
+ * tanh exp expm1 log log1p log2 log10 pow rsqrt reciprocal sin cos tan asin acos atan sinh cosh
+ * floor ceil trunc round erf erfc gelu) plus gelu_tanh silu fast_gelu swiglu maximum minimum
+ * gt ge lt le eq ne logical_and logical_or logical_not bitwise_not where cast.
+ * f16/bf16 values are computed in f32 registers and rounded once, at the store or at a cast.
+ *
+ * `math fast` selects hardware-approximation sequences whose relative error is bounded by 4e-6
+ * for f32; `math precise` selects the CUDA math library's functions, as the reference's NVRTC
+ * kernels do. f64 is always precise.
+ *
+ * Errors: TQ_INVALID_ARGUMENT for a malformed program, TQ_UNSUPPORTED for an op/dtype pair with no
+ * kernel (ints outside add sub mul neg relu abs maximum minimum compare where cast,
+ * csrc/tessiq/torch/eager.cpp:66-69), TQ_EXTERNAL if NVRTC fails. */
+typedef struct tq_fused tq_fused;
+tq_status tq_fused_create(const char* program, tq_fused** kernel);
+tq_status tq_fused_destroy(tq_fused* kernel);
+
+/* The CUDA source the selector instantiated (for tests and reports). Copies at most `capacity`
+ * bytes including the terminator; returns the full length in `*length` when non-null. */
+tq_status tq_fused_source(const tq_fused* kernel, char* buffer, size_t capacity, size_t* length);
+
+/* Layout of one strided operand: rank <= 8, sizes of the OUTPUT, strides of the operand in
+ * elements (0 for a broadcast axis). Negative strides are refused (kernel.cpp:84-88). */
+typedef struct tq_layout {
+  int32_t rank;
+  int64_t sizes[8];
+  int64_t strides[8];
+} tq_layout;
+
+/* Runs the group over `elements` outputs.
+ *   inputs[k]    device pointer of the k-th `in`, in program order
+ *   divisors[j]  the divisor of the j-th repeated/cycled `in`, in program order
+ *   layouts[j]   the layout of the j-th strided `in`, in program order (may be null if none)
+ *   scalars[j]   the j-th `scalar`, as a double (converted the way torch converts scalars,
+ *                csrc/tessiq/torch/eager.cpp:533-544)
+ * Pointers may have any alignment that suits their element type: 16-byte-aligned operands take
+ * the 128-bit path, others a narrower one. */
+tq_status tq_fused_launch(const tq_fused* kernel,
+                          const void* const* inputs,
+                          void* out,
+                          int64_t elements,
+                          const int64_t* divisors,
+                          const tq_layout* layouts,
+                          const double* scalars,
+                          int32_t device,
+                          void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Reductions                                                                                   */
+/* Replaces CudaEmitter::emit(ReductionKernel) (csrc/tessiq/codegen/cuda_emitter.cpp:159-210),   */
+/* ReductionKernel::launch (csrc/tessiq/torch/fused.cpp:212-285) and the eager two-pass          */
+/* reduce() (csrc/tessiq/torch/eager_reduction.cpp:163-255).                                     */
+
+typedef int32_t tq_reduce_op;
+enum {
+  TQ_SUM = 0,
+  TQ_MEAN = 1, /* sum / (T)reduce after the sum (cuda_emitter.cpp:166) */
+  TQ_AMAX = 2, /* NaN-propagating (cuda_emitter.cpp:52-65) */
+  TQ_AMIN = 3,
+  TQ_ARGMAX = 4 /* first index of the maximum, NaN counts as the maximum; result is int64.
+                   No counterpart kernel in the reference: aten.argmax runs on its host. */
+};
+
+/* Scratch bytes `tq_reduce_launch` needs for these extents (0 when it needs none). The scratch
+ * holds per-CTA partials of slices that are split over several CTAs and a ticket counter. */
+tq_status tq_reduce_workspace_bytes(tq_reduce_op op,
+                                    tq_dtype dtype,
+                                    int64_t outer,
+                                    int64_t reduce,
+                                    int64_t inner,
+                                    int32_t device,
+                                    size_t* bytes);
+
+/* Reduces `in`, viewed as a packed [outer, reduce, inner], to a packed [outer, inner] `out`
+ * (csrc/tessiq/codegen/reduction.h:69-117). Output type: the input's, except TQ_ARGMAX -> int64
+ * and TQ_SUM of int32 -> int64 (torch's promotion, eager_reduction.cpp:77-89). f16/bf16 are
+ * accumulated in f32. `workspace` must hold `tq_reduce_workspace_bytes` bytes of device memory
+ * that no other launch in flight uses; it may be null when that size is 0. reduce == 0, or a
+ * mean over an integer type, is TQ_UNSUPPORTED (reduction.cpp:110-113,148-152). */
+tq_status tq_reduce_launch(tq_reduce_op op,
+                           tq_dtype dtype,
+                           const void* in,
+                           void* out,
+                           int64_t outer,
+                           int64_t reduce,
+                           int64_t inner,
+                           void* workspace,
+                           size_t workspace_bytes,
+                           int32_t device,
+                           void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Pack: strided / expanded / permuted view -> packed copy                                      */
+/* Replaces pack_source + pack_on_device (csrc/tessiq/codegen/pack.cpp:41-94,                    */
+/* csrc/tessiq/torch/pack.cpp:80-122). Bit-exact byte copy.                                      */
+
+/* element_bytes in {1,2,4,8,16}; rank <= 8 (rank 9 declines, tests/python/test_pack.py:117-128);
+ * sizes are the view's extents, strides the view's strides in elements (>= 0). */
+tq_status tq_pack_launch(int32_t element_bytes,
+                         int32_t rank,
+                         const int64_t* sizes,
+                         const int64_t* strides,
+                         const void* src,
+                         void* dst,
+                         int32_t device,
+                         void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Row kernels: softmax, LayerNorm, RMSNorm, eval BatchNorm                                     */
+
+/* softmax over the middle extent of a packed [outer, extent, inner] tensor
+ * (csrc/custom_ops/softmax/softmax.cu:19-61, softmax.cpp:30-61). dtype f32/f16/bf16/f64;
+ * statistics in f32 (f64 for f64). `out_dtype` is `dtype`, or TQ_F32 for a half input
+ * (aten::_softmax's half_to_float). NaN in a row makes the whole row NaN, as torch does. */
+tq_status tq_softmax_launch(tq_dtype dtype,
+                            tq_dtype out_dtype,
+                            const void* in,
+                            void* out,
+                            int64_t outer,
+                            int64_t extent,
+                            int64_t inner,
+                            int32_t device,
+                            void* stream);
+
+/* LayerNorm forward over the last `width` elements of each of `rows` packed rows
+ * (csrc/tessiq/codegen/norm.cpp:22-135, csrc/tessiq/torch/eager_norm.cpp:226-271; the custom op
+ * csrc/custom_ops/layer_norm/layer_norm.nvcc.cu:43-120). Two passes over registers: the mean,
+ * then the centred sum of squares; rstd = 1/sqrt(var + eps); y = (x-mean)*rstd*weight + bias.
+ * weight, bias, mean, rstd may each be null (skipped). `stat_dtype` is the type of mean/rstd
+ * (torch returns them in the input's type for f16/bf16 inputs). */
+tq_status tq_layer_norm_launch(tq_dtype dtype,
+                               const void* in,
+                               const void* weight,
+                               const void* bias,
+                               void* out,
+                               void* mean,
+                               void* rstd,
+                               tq_dtype stat_dtype,
+                               int64_t rows,
+                               int64_t width,
+                               double eps,
+                               int32_t device,
+                               void* stream);
+
+/* RMSNorm: y = x * rsqrt(mean(x^2) + eps) * weight (csrc/custom_ops/rms_norm/rms_norm.cu:15-42). */
+tq_status tq_rms_norm_launch(tq_dtype dtype,
+                             const void* in,
+                             const void* weight,
+                             void* out,
+                             int64_t rows,
+                             int64_t width,
+                             double eps,
+                             int32_t device,
+                             void* stream);
+
+/* Eval-mode BatchNorm over a packed [n, c, inner] tensor: alpha = w/sqrt(var+eps),
+ * beta = b - mean*alpha, y = x*alpha + beta (csrc/tessiq/codegen/norm.cpp:137-199,
+ * csrc/tessiq/torch/eager_norm.cpp:136-199). weight/bias may be null (1 and 0). The four
+ * per-channel vectors have `param_dtype` (f32 for half inputs in torch's mixed mode, else dtype). */
+tq_status tq_batch_norm_eval_launch(tq_dtype dtype,
+                                    tq_dtype param_dtype,
+                                    const void* in,
+                                    const void* weight,
+                                    const void* bias,
+                                    const void* running_mean,
+                                    const void* running_var,
+                                    void* out,
+                                    int64_t n,
+                                    int64_t c,
+                                    int64_t inner,
+                                    double eps,
+                                    int32_t device,
+                                    void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
+/* GEMM (+ bias + activation)                                                                    */
+/* Replaces launch_gemm (csrc/tessiq/codegen/blas.cpp:92-193) with its bias pre-fill kernel      */
+/* (csrc/tessiq/codegen/gemm.cpp:186-199), and the custom ops gemm_bias_gelu_tanh                */
+/* (csrc/custom_ops/gemm_bias_gelu_tanh/gemm_bias_gelu_tanh.nvcc.cu:219-288) and gemm_bias_gelu  */
+/* (csrc/custom_ops/gemm_bias_gelu/gemm_bias_gelu.nvcc.cu:90-158).                               */
+
+typedef int32_t tq_activation;
+enum { TQ_ACT_NONE = 0, TQ_ACT_GELU_ERF = 1, TQ_ACT_GELU_TANH = 2 };
+
+/* C[b] = act(op(A[b]) @ op(B[b]) + bias), row-major, bf16 or f16 operands, f32 accumulation in
+ * tensor memory, one rounding to the output type after bias and activation.
+ *   op(A) is [m,k]: trans_a == 0 -> A is row-major [m,k] with leading dimension lda (elements);
+ *                   trans_a != 0 -> A is stored as [k,m] with leading dimension lda.
+ *   op(B) is [k,n]: trans_b == 0 -> B is row-major [k,n] (the `A @ B` form);
+ *                   trans_b != 0 -> B is stored as [n,k] (the nn.Linear weight form).
+ * Transposed operands are consumed in place, never copied (csrc/tessiq/codegen/gemm.cpp:28-53).
+ * bias is one value per output column ([n], same dtype as C) or null.
+ * batch >= 1 with element strides stride_a/b/c between problems (0 = shared operand).
+ * Requirements (else TQ_UNSUPPORTED, the caller's decline): 16-byte-aligned base pointers and
+ * leading dimensions/strides that are multiples of 8 elements (TMA's rules). */
+tq_status tq_gemm_bias_act_launch(tq_dtype dtype,
+                                  tq_activation activation,
+                                  const void* a,
+                                  int64_t lda,
+                                  int32_t trans_a,
+                                  const void* b,
+                                  int64_t ldb,
+                                  int32_t trans_b,
+                                  const void* bias,
+                                  void* c,
+                                  int64_t ldc,
+                                  int64_t m,
+                                  int64_t n,
+                                  int64_t k,
+                                  int64_t batch,
+                                  int64_t stride_a,
+                                  int64_t stride_b,
+                                  int64_t stride_c,
+                                  int32_t device,
+                                  void* stream);
+
+/* Reads and clears the device-side status word of `device`: 0 when every bounded wait inside
+ * this library's kernels completed, otherwise a code naming the wait that gave up. Synchronises
+ * `stream` first. */
+tq_status tq_status_poll(int32_t device, void* stream, int32_t* device_status);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TESSIQ_B200_H_ */

@@ -1,0 +1,182 @@
+// Shared host and device helpers of the tessiq_b200 kernel library.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "tessiq_b200.h"
+
+namespace tq {
+
+// ---------------------------------------------------------------------------------------------
+// Errors. Every entry point returns through fail()/ok(); the message goes to a thread-local slot.
+
+void set_error(const char* text);
+tq_status fail(tq_status code, const char* format, ...) __attribute__((format(printf, 2, 3)));
+
+#define TQ_CUDA(call)                                                                         \
+  do {                                                                                        \
+    cudaError_t tq_cuda_status_ = (call);                                                     \
+    if (tq_cuda_status_ != cudaSuccess) {                                                     \
+      return ::tq::fail(TQ_EXTERNAL, "%s failed: %s", #call,                                  \
+                        cudaGetErrorString(tq_cuda_status_));                                 \
+    }                                                                                         \
+  } while (0)
+
+#define TQ_REQUIRE(condition, code, ...)                                                      \
+  do {                                                                                        \
+    if (!(condition)) return ::tq::fail(code, __VA_ARGS__);                                   \
+  } while (0)
+
+// Makes `device` current for the calling thread. Cheap when it already is.
+tq_status use_device(int32_t device);
+
+// Number of SMs of `device` (cached).
+int sm_count(int32_t device);
+
+// Checks the launch that was just queued.
+inline tq_status check_launch(const char* what) {
+  cudaError_t status = cudaGetLastError();
+  if (status != cudaSuccess) {
+    return fail(TQ_EXTERNAL, "launching %s failed: %s", what, cudaGetErrorString(status));
+  }
+  return TQ_OK;
+}
+
+inline int dtype_size(tq_dtype dtype) {
+  switch (dtype) {
+    case TQ_F32: return 4;
+    case TQ_F64: return 8;
+    case TQ_F16: return 2;
+    case TQ_BF16: return 2;
+    case TQ_I32: return 4;
+    case TQ_I64: return 8;
+    case TQ_BOOL: return 1;
+    default: return 0;
+  }
+}
+
+inline const char* dtype_name(tq_dtype dtype) {
+  switch (dtype) {
+    case TQ_F32: return "f32";
+    case TQ_F64: return "f64";
+    case TQ_F16: return "f16";
+    case TQ_BF16: return "bf16";
+    case TQ_I32: return "i32";
+    case TQ_I64: return "i64";
+    case TQ_BOOL: return "bool";
+    default: return "?";
+  }
+}
+
+inline bool aligned_to(const void* pointer, size_t bytes) {
+  return (reinterpret_cast<uintptr_t>(pointer) % bytes) == 0;
+}
+
+// Device-side status word (one per device), written by kernels whose bounded waits give up.
+int32_t* device_status_word(int32_t device);
+
+}  // namespace tq
+
+// ---------------------------------------------------------------------------------------------
+// Device helpers
+#ifdef __CUDACC__
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace tq {
+
+// Storage type -> the type arithmetic runs in.
+template <typename T> struct Compute { using type = T; };
+template <> struct Compute<__half> { using type = float; };
+template <> struct Compute<__nv_bfloat16> { using type = float; };
+
+template <typename T> __device__ __forceinline__ typename Compute<T>::type to_compute(T v) { return v; }
+template <> __device__ __forceinline__ float to_compute<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_compute<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+
+template <typename T, typename C> __device__ __forceinline__ T from_compute(C v) { return static_cast<T>(v); }
+template <> __device__ __forceinline__ __half from_compute<__half, float>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_compute<__nv_bfloat16, float>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// A vector of N elements of T moved with one instruction when N*sizeof(T) is 4, 8 or 16 bytes.
+template <typename T, int N>
+struct alignas(sizeof(T) * N) Vec {
+  T v[N];
+};
+
+// Streaming (read-once) load: bypasses L1 allocation so that the data does not evict reused lines.
+template <typename T, int N>
+__device__ __forceinline__ Vec<T, N> load_stream(const T* pointer) {
+  Vec<T, N> out;
+  constexpr int kBytes = sizeof(T) * N;
+  if constexpr (kBytes == 16) {
+    uint4 raw;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                 : "l"(pointer));
+    *reinterpret_cast<uint4*>(&out) = raw;
+  } else if constexpr (kBytes == 32) {
+    uint4 lo, hi;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w)
+                 : "l"(pointer));
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+                 : "l"(reinterpret_cast<const char*>(pointer) + 16));
+    reinterpret_cast<uint4*>(&out)[0] = lo;
+    reinterpret_cast<uint4*>(&out)[1] = hi;
+  } else if constexpr (kBytes == 8) {
+    uint2 raw;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];"
+                 : "=r"(raw.x), "=r"(raw.y)
+                 : "l"(pointer));
+    *reinterpret_cast<uint2*>(&out) = raw;
+  } else if constexpr (kBytes == 4) {
+    uint32_t raw;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(raw) : "l"(pointer));
+    *reinterpret_cast<uint32_t*>(&out) = raw;
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) out.v[i] = pointer[i];
+  }
+  return out;
+}
+
+// Streaming store (evict-first): the result is not read again by this kernel.
+template <typename T, int N>
+__device__ __forceinline__ void store_stream(T* pointer, const Vec<T, N>& value) {
+  constexpr int kBytes = sizeof(T) * N;
+  if constexpr (kBytes == 16) {
+    __stcs(reinterpret_cast<uint4*>(pointer), *reinterpret_cast<const uint4*>(&value));
+  } else if constexpr (kBytes == 32) {
+    __stcs(reinterpret_cast<uint4*>(pointer), reinterpret_cast<const uint4*>(&value)[0]);
+    __stcs(reinterpret_cast<uint4*>(pointer) + 1, reinterpret_cast<const uint4*>(&value)[1]);
+  } else if constexpr (kBytes == 8) {
+    __stcs(reinterpret_cast<uint2*>(pointer), *reinterpret_cast<const uint2*>(&value));
+  } else if constexpr (kBytes == 4) {
+    __stcs(reinterpret_cast<unsigned int*>(pointer), *reinterpret_cast<const unsigned int*>(&value));
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) pointer[i] = value.v[i];
+  }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+  return v;
+}
+
+}  // namespace tq
+
+#endif  // __CUDACC__

@@ -1,0 +1,216 @@
+// Pack: gathers a strided / expanded / permuted view into a packed buffer, bit for bit.
+//
+// The host first drops extents of 1 and merges axes that are contiguous with one another, so the
+// kernels see the smallest rank that describes the view. Then one of three kernels runs:
+//   copy       the collapsed view is one contiguous run: a device-to-device copy on the stream;
+//   transpose  the destination's fastest axis is strided in the source while another axis has
+//              source stride 1 (a transposed or permuted view): TILE x TILE tiles go through
+//              padded shared memory so that both the HBM reads and the HBM writes are full
+//              128-byte lines; the remaining axes are unravelled once per tile, not per element;
+//   gather     anything else (slices, expanded axes, odd permutations): one thread per element,
+//              32-bit index arithmetic when the element count allows it.
+// The result is what pack_source's kernel writes (csrc/tessiq/codegen/pack.cpp:41-94): element i
+// of the packed buffer is the view's element at the unravelled coordinates of i.
+#include "common.h"
+
+namespace tq {
+namespace {
+
+constexpr int kMaxRank = 8;
+
+struct View {
+  int rank;
+  long long sizes[kMaxRank];
+  long long strides[kMaxRank];
+};
+
+template <int BYTES> struct Word;
+template <> struct Word<1> { using type = uint8_t; };
+template <> struct Word<2> { using type = uint16_t; };
+template <> struct Word<4> { using type = uint32_t; };
+template <> struct Word<8> { using type = uint2; };
+template <> struct Word<16> { using type = uint4; };
+
+template <typename W, typename Index>
+__global__ void __launch_bounds__(256)
+pack_gather_kernel(const W* __restrict__ src, W* __restrict__ dst, Index total, View view) {
+  const Index i = static_cast<Index>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= total) return;
+  Index rest = i;
+  long long offset = 0;
+#pragma unroll
+  for (int d = kMaxRank - 1; d >= 0; --d) {
+    if (d < view.rank) {
+      const Index extent = static_cast<Index>(view.sizes[d]);
+      const Index coordinate = rest % extent;
+      rest /= extent;
+      offset += static_cast<long long>(coordinate) * view.strides[d];
+    }
+  }
+  dst[i] = src[offset];
+}
+
+// Tiled transpose. The view, after collapsing, has its last axis (`cols`, destination-fastest)
+// strided by `col_stride` in the source and axis `row_axis` (`rows`) with source stride 1. A tile
+// covers TILE rows x TILE cols. Threads are 32 x 8; PER = TILE / 32 elements per thread per line.
+template <typename W, int TILE>
+__global__ void __launch_bounds__(256)
+pack_transpose_kernel(const W* __restrict__ src, W* __restrict__ dst, View view, int row_axis,
+                      long long row_tiles, long long col_tiles) {
+  __shared__ W tile[TILE][TILE + (sizeof(W) >= 4 ? 1 : 4 / sizeof(W))];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int last = view.rank - 1;
+  const long long rows = view.sizes[row_axis], cols = view.sizes[last];
+  const long long col_stride = view.strides[last];
+
+  long long tile_id = blockIdx.x;
+  const long long col_tile = tile_id % col_tiles;
+  tile_id /= col_tiles;
+  const long long row_tile = tile_id % row_tiles;
+  long long batch = tile_id / row_tiles;
+
+  // Unravel the batch index over the remaining axes; `dst_stride` is the packed stride.
+  long long src_base = 0, dst_base = 0, dst_stride = cols, row_dst_stride = 0;
+  for (int d = last - 1; d >= 0; --d) {
+    if (d == row_axis) {
+      row_dst_stride = dst_stride;
+    } else {
+      const long long coordinate = batch % view.sizes[d];
+      batch /= view.sizes[d];
+      src_base += coordinate * view.strides[d];
+      dst_base += coordinate * dst_stride;
+    }
+    dst_stride *= view.sizes[d];
+  }
+
+  const long long row0 = row_tile * TILE, col0 = col_tile * TILE;
+  // Read: consecutive threads walk the source-contiguous axis (rows).
+  for (int c = ty; c < TILE; c += 8) {
+    const long long col = col0 + c;
+    if (col < cols) {
+#pragma unroll
+      for (int r = tx; r < TILE; r += 32) {
+        const long long row = row0 + r;
+        if (row < rows) tile[c][r] = src[src_base + row + col * col_stride];
+      }
+    }
+  }
+  __syncthreads();
+  // Write: consecutive threads walk the destination-contiguous axis (cols).
+  for (int r = ty; r < TILE; r += 8) {
+    const long long row = row0 + r;
+    if (row < rows) {
+#pragma unroll
+      for (int c = tx; c < TILE; c += 32) {
+        const long long col = col0 + c;
+        if (col < cols) dst[dst_base + row * row_dst_stride + col] = tile[c][r];
+      }
+    }
+  }
+}
+
+View collapse(int rank, const int64_t* sizes, const int64_t* strides) {
+  View v = {};
+  for (int d = 0; d < rank; ++d) {
+    if (sizes[d] == 1) continue;
+    if (v.rank > 0 && v.strides[v.rank - 1] == strides[d] * sizes[d]) {
+      v.sizes[v.rank - 1] *= sizes[d];
+      v.strides[v.rank - 1] = strides[d];
+    } else {
+      v.sizes[v.rank] = sizes[d];
+      v.strides[v.rank] = strides[d];
+      ++v.rank;
+    }
+  }
+  if (v.rank == 0) {
+    v.rank = 1;
+    v.sizes[0] = 1;
+    v.strides[0] = 1;
+  }
+  return v;
+}
+
+template <int BYTES>
+tq_status run_pack(const View& view, long long total, const void* src, void* dst, cudaStream_t stream) {
+  using W = typename Word<BYTES>::type;
+  const W* source = static_cast<const W*>(src);
+  W* target = static_cast<W*>(dst);
+  const int last = view.rank - 1;
+
+  if (view.rank == 1 && view.strides[0] == 1) {
+    const long long bytes = total * BYTES;
+    if (aligned_to(src, 16) && aligned_to(dst, 16) && bytes % 16 == 0) {
+      TQ_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, stream));
+      return TQ_OK;
+    }
+  }
+
+  if (view.strides[last] != 1 && view.strides[last] != 0) {
+    int row_axis = -1;
+    for (int d = last - 1; d >= 0; --d) {
+      if (view.strides[d] == 1 && view.sizes[d] >= 16) {
+        row_axis = d;
+        break;
+      }
+    }
+    if (row_axis >= 0 && view.sizes[last] >= 16) {
+      constexpr int kTile = BYTES >= 4 ? 32 : (BYTES == 2 ? 64 : 128);
+      const long long row_tiles = (view.sizes[row_axis] + kTile - 1) / kTile;
+      const long long col_tiles = (view.sizes[last] + kTile - 1) / kTile;
+      long long batches = 1;
+      for (int d = 0; d < last; ++d) {
+        if (d != row_axis) batches *= view.sizes[d];
+      }
+      const long long blocks = batches * row_tiles * col_tiles;
+      if (blocks <= 0x7fffffffLL) {
+        pack_transpose_kernel<W, kTile><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+            source, target, view, row_axis, row_tiles, col_tiles);
+        return check_launch("pack_transpose_kernel");
+      }
+    }
+  }
+
+  const long long blocks = (total + 255) / 256;
+  TQ_REQUIRE(blocks <= 0x7fffffffLL, TQ_UNSUPPORTED, "%lld elements are more than the pack kernel's grid holds", total);
+  if (total < 0x7fffffffLL) {
+    pack_gather_kernel<W, unsigned><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        source, target, static_cast<unsigned>(total), view);
+  } else {
+    pack_gather_kernel<W, long long><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        source, target, total, view);
+  }
+  return check_launch("pack_gather_kernel");
+}
+
+}  // namespace
+}  // namespace tq
+
+extern "C" tq_status tq_pack_launch(int32_t element_bytes, int32_t rank, const int64_t* sizes,
+                                    const int64_t* strides, const void* src, void* dst,
+                                    int32_t device, void* stream) {
+  TQ_REQUIRE(rank >= 0, TQ_INVALID_ARGUMENT, "negative rank %d", rank);
+  TQ_REQUIRE(rank <= tq::kMaxRank, TQ_UNSUPPORTED, "the pack kernel takes up to %d axes, not %d", tq::kMaxRank, rank);
+  TQ_REQUIRE(rank == 0 || (sizes != nullptr && strides != nullptr), TQ_INVALID_ARGUMENT, "null sizes or strides");
+  long long total = 1;
+  for (int d = 0; d < rank; ++d) {
+    TQ_REQUIRE(sizes[d] >= 0, TQ_INVALID_ARGUMENT, "negative extent %lld on axis %d", (long long)sizes[d], d);
+    TQ_REQUIRE(strides[d] >= 0, TQ_UNSUPPORTED, "negative stride %lld on axis %d has no kernel", (long long)strides[d], d);
+    total *= sizes[d];
+  }
+  if (total == 0) return TQ_OK;
+  TQ_REQUIRE(src != nullptr && dst != nullptr, TQ_INVALID_ARGUMENT, "null source or destination");
+  TQ_REQUIRE(element_bytes == 1 || element_bytes == 2 || element_bytes == 4 || element_bytes == 8 || element_bytes == 16,
+             TQ_UNSUPPORTED, "elements of %d bytes have no pack kernel", element_bytes);
+  TQ_REQUIRE(tq::aligned_to(src, element_bytes) && tq::aligned_to(dst, element_bytes), TQ_INVALID_ARGUMENT,
+             "pointers must be aligned to the element width");
+  if (tq_status s = tq::use_device(device)) return s;
+  const tq::View view = tq::collapse(rank, sizes, strides);
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  switch (element_bytes) {
+    case 1: return tq::run_pack<1>(view, total, src, dst, cuda_stream);
+    case 2: return tq::run_pack<2>(view, total, src, dst, cuda_stream);
+    case 4: return tq::run_pack<4>(view, total, src, dst, cuda_stream);
+    case 8: return tq::run_pack<8>(view, total, src, dst, cuda_stream);
+    default: return tq::run_pack<16>(view, total, src, dst, cuda_stream);
+  }
+}

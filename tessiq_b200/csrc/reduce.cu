@@ -1,0 +1,680 @@
+// Reductions over a packed [outer, reduce, inner] view: sum, mean, amax, amin, argmax.
+//
+// Three kernel shapes, chosen on the host by plan():
+//   warp-per-slice   inner == 1, many slices of moderate length: each warp streams one slice with
+//                    128-bit loads and finishes with shuffles; no shared memory, no barrier.
+//   cta-per-slice    inner == 1, long or few slices: `split` CTAs stream one slice; warp shuffle,
+//                    then shared memory, then distributed shared memory across the thread-block
+//                    cluster, then (only when a slice spans more than one cluster) per-cluster
+//                    partials in scratch memory that the last cluster to arrive combines.
+//   columns          inner > 1: threads run along `inner` (coalesced), warps along `reduce`;
+//                    the same cluster / scratch steps when `reduce` is split.
+// No wait anywhere: the "last to arrive" step uses a ticket, not a spin.
+//
+// Semantics follow the reference's reduction kernels (csrc/tessiq/codegen/cuda_emitter.cpp:159-210):
+// mean divides once after the sum, amax/amin propagate NaN. argmax returns the first index of the
+// maximum with NaN counted as the maximum, which is what aten.argmax computes on the reference's
+// host device.
+#include <cooperative_groups.h>
+
+#include <limits>
+#include <type_traits>
+
+#include "common.h"
+
+namespace cg = cooperative_groups;
+
+namespace tq {
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kWarps = kBlock / 32;
+constexpr int kUnroll = 4;
+constexpr int kMaxCluster = 8;
+
+// ---------------------------------------------------------------------------------------------
+// Reducers
+
+template <typename C> __device__ __forceinline__ C shfl_xor(C v, int offset) {
+  return __shfl_xor_sync(0xffffffffu, v, offset);
+}
+
+template <typename T>
+struct SumReducer {
+  using C = typename Compute<T>::type;
+  using Acc = std::conditional_t<std::is_integral_v<C>, long long, C>;
+  using Out = std::conditional_t<std::is_same_v<T, int>, long long, T>;
+  __device__ static Acc identity() { return Acc(0); }
+  __device__ static Acc lift(T v, long long) { return static_cast<Acc>(to_compute(v)); }
+  __device__ static Acc combine(Acc a, Acc b) { return a + b; }
+  __device__ static Acc shuffle(Acc a, int offset) { return shfl_xor(a, offset); }
+  __device__ static Out finish(Acc a, long long count, bool mean) {
+    if constexpr (!std::is_integral_v<C>) {
+      if (mean) a = a / static_cast<Acc>(count);
+      return from_compute<Out, Acc>(a);
+    } else {
+      return static_cast<Out>(a);
+    }
+  }
+};
+
+template <typename T, bool kMax>
+struct ExtremeReducer {
+  using C = typename Compute<T>::type;
+  using Acc = C;
+  using Out = T;
+  __device__ static Acc identity() {
+    if constexpr (std::is_integral_v<C>) {
+      return kMax ? std::numeric_limits<C>::lowest() : std::numeric_limits<C>::max();
+    } else {
+      return kMax ? -std::numeric_limits<C>::infinity() : std::numeric_limits<C>::infinity();
+    }
+  }
+  __device__ static Acc lift(T v, long long) { return to_compute(v); }
+  __device__ static Acc combine(Acc a, Acc b) {
+    if constexpr (!std::is_integral_v<C>) {
+      if (a != a) return a;
+      if (b != b) return b;
+    }
+    if constexpr (kMax) return a > b ? a : b;
+    return a < b ? a : b;
+  }
+  __device__ static Acc shuffle(Acc a, int offset) { return shfl_xor(a, offset); }
+  __device__ static Out finish(Acc a, long long, bool) { return from_compute<Out, Acc>(a); }
+};
+
+template <typename C>
+struct alignas(16) Indexed {
+  C value;
+  long long index;
+};
+
+template <typename T>
+struct ArgmaxReducer {
+  using C = typename Compute<T>::type;
+  using Acc = Indexed<C>;
+  using Out = long long;
+  __device__ static Acc identity() {
+    Acc a;
+    if constexpr (std::is_integral_v<C>) {
+      a.value = std::numeric_limits<C>::lowest();
+    } else {
+      a.value = -std::numeric_limits<C>::infinity();
+    }
+    a.index = std::numeric_limits<long long>::max();
+    return a;
+  }
+  __device__ static Acc lift(T v, long long index) {
+    Acc a;
+    a.value = to_compute(v);
+    a.index = index;
+    return a;
+  }
+  // A total order: NaN above everything, then the value, then the lower index.
+  __device__ static Acc combine(Acc a, Acc b) {
+    bool a_nan = false, b_nan = false;
+    if constexpr (!std::is_integral_v<C>) {
+      a_nan = a.value != a.value;
+      b_nan = b.value != b.value;
+    }
+    bool take_b;
+    if (a_nan || b_nan) {
+      take_b = (a_nan && b_nan) ? (b.index < a.index) : b_nan;
+    } else if (a.value == b.value) {
+      take_b = b.index < a.index;
+    } else {
+      take_b = b.value > a.value;
+    }
+    return take_b ? b : a;
+  }
+  __device__ static Acc shuffle(Acc a, int offset) {
+    Acc b;
+    b.value = shfl_xor(a.value, offset);
+    b.index = shfl_xor(a.index, offset);
+    return b;
+  }
+  __device__ static Out finish(Acc a, long long, bool) { return a.index; }
+};
+
+// Reads a partial another CTA wrote, from L2 (never a stale L1 line).
+template <typename A>
+__device__ __forceinline__ A load_partial(const A* pointer) {
+  if constexpr (sizeof(A) == 16) {
+    uint4 raw = __ldcg(reinterpret_cast<const uint4*>(pointer));
+    return *reinterpret_cast<A*>(&raw);
+  } else if constexpr (sizeof(A) == 8) {
+    unsigned long long raw = __ldcg(reinterpret_cast<const unsigned long long*>(pointer));
+    return *reinterpret_cast<A*>(&raw);
+  } else {
+    static_assert(sizeof(A) == 4, "accumulators are 4, 8 or 16 bytes");
+    unsigned raw = __ldcg(reinterpret_cast<const unsigned*>(pointer));
+    return *reinterpret_cast<A*>(&raw);
+  }
+}
+
+template <typename R>
+__device__ __forceinline__ typename R::Acc warp_reduce(typename R::Acc a) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) a = R::combine(a, R::shuffle(a, offset));
+  return a;
+}
+
+// All threads call; the result is valid on thread 0.
+template <typename R>
+__device__ __forceinline__ typename R::Acc block_reduce(typename R::Acc a, typename R::Acc* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  a = warp_reduce<R>(a);
+  __syncthreads();  // scratch may still be read from an earlier use
+  if (lane == 0) scratch[warp] = a;
+  __syncthreads();
+  if (warp == 0) {
+    a = lane < kWarps ? scratch[lane] : R::identity();
+    a = warp_reduce<R>(a);
+  }
+  return a;
+}
+
+// Folds elements [begin, end) of `row` into `acc`, `threads` threads cooperating, this one being
+// `tid`. The span is cut into a scalar head up to the first 16-byte boundary, a body of VEC-wide
+// streaming loads, and a scalar tail, so that any element-aligned pointer works.
+template <typename T, typename R, int VEC>
+__device__ __forceinline__ void fold_span(const T* __restrict__ row, long long begin, long long end,
+                                          int tid, int threads, typename R::Acc& acc) {
+  if (begin >= end) return;
+  const T* start = row + begin;
+  long long head = 0;
+  if constexpr (VEC > 1) {
+    const unsigned misaligned =
+        static_cast<unsigned>(reinterpret_cast<uintptr_t>(start) % (sizeof(T) * VEC)) / sizeof(T);
+    head = misaligned ? (VEC - misaligned) : 0;
+    if (head > end - begin) head = end - begin;
+    if (tid < head) acc = R::combine(acc, R::lift(start[tid], begin + tid));
+  }
+  const long long body = begin + head;
+  const long long vectors = (end - body) / VEC;
+  const T* vector_base = row + body;
+  for (long long v = tid; v < vectors; v += static_cast<long long>(threads) * kUnroll) {
+    Vec<T, VEC> x[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long vi = v + static_cast<long long>(u) * threads;
+      if (vi < vectors) x[u] = load_stream<T, VEC>(vector_base + vi * VEC);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long vi = v + static_cast<long long>(u) * threads;
+      if (vi < vectors) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          acc = R::combine(acc, R::lift(x[u].v[e], body + vi * VEC + e));
+        }
+      }
+    }
+  }
+  const long long tail = body + vectors * VEC + tid;
+  if (tail < end) acc = R::combine(acc, R::lift(row[tail], tail));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernels
+
+// One warp per slice. grid.x * kWarps >= outer.
+template <typename T, typename R, int VEC>
+__global__ void __launch_bounds__(kBlock)
+reduce_warp_per_slice(const T* __restrict__ in, typename R::Out* __restrict__ out, long long outer,
+                      long long reduce, int mean) {
+  const int lane = threadIdx.x & 31;
+  const long long slice = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  if (slice >= outer) return;
+  typename R::Acc acc = R::identity();
+  fold_span<T, R, VEC>(in + slice * reduce, 0, reduce, lane, 32, acc);
+  acc = warp_reduce<R>(acc);
+  if (lane == 0) out[slice] = R::finish(acc, reduce, mean != 0);
+}
+
+// `split` CTAs per slice, `cluster` of them in one thread-block cluster (cluster divides split).
+// blockIdx.x = slice * split + part.
+template <typename T, typename R, int VEC>
+__global__ void __launch_bounds__(kBlock)
+reduce_cta_per_slice(const T* __restrict__ in, typename R::Out* __restrict__ out, long long reduce,
+                     int split, int cluster, int mean, typename R::Acc* __restrict__ partials,
+                     unsigned* __restrict__ tickets) {
+  using Acc = typename R::Acc;
+  __shared__ Acc warp_scratch[kWarps];
+  __shared__ Acc cluster_scratch[kMaxCluster];
+  __shared__ bool is_last;
+
+  const long long slice = blockIdx.x / split;
+  const int part = static_cast<int>(blockIdx.x % split);
+  // Parts are cut on multiples of the vector width so that only the first can be misaligned.
+  long long chunk = (reduce + split - 1) / split;
+  chunk = (chunk + VEC - 1) / VEC * VEC;
+  const long long begin = static_cast<long long>(part) * chunk;
+  long long end = begin + chunk;
+  if (end > reduce) end = reduce;
+
+  Acc acc = R::identity();
+  fold_span<T, R, VEC>(in + slice * reduce, begin, end, threadIdx.x, kBlock, acc);
+  acc = block_reduce<R>(acc, warp_scratch);
+
+  if (cluster > 1) {
+    cg::cluster_group group = cg::this_cluster();
+    const unsigned rank = group.block_rank();
+    if (threadIdx.x == 0) {
+      Acc* leader = group.map_shared_rank(cluster_scratch, 0);
+      leader[rank] = acc;
+    }
+    group.sync();
+    if (rank != 0) return;
+    if (threadIdx.x == 0) {
+      acc = cluster_scratch[0];
+      for (int j = 1; j < cluster; ++j) acc = R::combine(acc, cluster_scratch[j]);
+    }
+  }
+
+  const int clusters = split / cluster;
+  if (clusters == 1) {
+    if (threadIdx.x == 0) out[slice] = R::finish(acc, reduce, mean != 0);
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    partials[slice * clusters + part / cluster] = acc;
+    __threadfence();
+    const unsigned ticket = atomicAdd(&tickets[slice], 1u);
+    is_last = ticket == static_cast<unsigned>(clusters - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  Acc total = R::identity();
+  for (int j = threadIdx.x; j < clusters; j += kBlock) {
+    total = R::combine(total, load_partial(partials + slice * clusters + j));
+  }
+  total = block_reduce<R>(total, warp_scratch);
+  if (threadIdx.x == 0) out[slice] = R::finish(total, reduce, mean != 0);
+}
+
+// inner > 1. Thread layout: tx = threadIdx.x % lanes_x runs along inner (VEC columns each),
+// ty = threadIdx.x / lanes_x along reduce. grid = (column tiles, split, outer); the cluster, when
+// there is one, runs along grid.y.
+template <typename T, typename R, int VEC>
+__global__ void __launch_bounds__(kBlock)
+reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long long reduce,
+               long long inner, int lanes_x, int split, int cluster, int mean,
+               typename R::Acc* __restrict__ partials, unsigned* __restrict__ tickets) {
+  using Acc = typename R::Acc;
+  extern __shared__ __align__(16) unsigned char dynamic_smem[];
+  Acc* rows_scratch = reinterpret_cast<Acc*>(dynamic_smem);              // [kBlock * VEC]
+  Acc* cluster_scratch = rows_scratch + kBlock * VEC;                    // [cluster * lanes_x * VEC]
+  __shared__ bool is_last;
+
+  const int tx = threadIdx.x % lanes_x;
+  const int ty = threadIdx.x / lanes_x;
+  const int lanes_y = kBlock / lanes_x;
+  const long long slice = blockIdx.z;
+  const int part = blockIdx.y;
+  const long long column = (static_cast<long long>(blockIdx.x) * lanes_x + tx) * VEC;
+  const bool in_range = column < inner;
+
+  long long chunk = (reduce + split - 1) / split;
+  const long long begin = static_cast<long long>(part) * chunk;
+  long long end = begin + chunk;
+  if (end > reduce) end = reduce;
+
+  Acc acc[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) acc[e] = R::identity();
+
+  if (in_range) {
+    const T* base = in + slice * reduce * inner + column;
+    for (long long r = begin + ty; r < end; r += static_cast<long long>(lanes_y) * kUnroll) {
+      Vec<T, VEC> x[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const long long ri = r + static_cast<long long>(u) * lanes_y;
+        if (ri < end) x[u] = load_stream<T, VEC>(base + ri * inner);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const long long ri = r + static_cast<long long>(u) * lanes_y;
+        if (ri < end) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) acc[e] = R::combine(acc[e], R::lift(x[u].v[e], ri));
+        }
+      }
+    }
+  }
+
+  // Across ty, through shared memory, in a fixed order.
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) rows_scratch[(ty * lanes_x + tx) * VEC + e] = acc[e];
+  __syncthreads();
+  const bool holder = ty == 0;
+  if (holder) {
+    for (int y = 1; y < lanes_y; ++y) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        acc[e] = R::combine(acc[e], rows_scratch[(y * lanes_x + tx) * VEC + e]);
+      }
+    }
+  }
+
+  const int items = lanes_x * VEC;
+  if (cluster > 1) {
+    cg::cluster_group group = cg::this_cluster();
+    const unsigned rank = group.block_rank();
+    if (holder) {
+      Acc* leader = group.map_shared_rank(cluster_scratch, 0);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) leader[rank * items + tx * VEC + e] = acc[e];
+    }
+    group.sync();
+    if (rank != 0) return;
+    if (holder) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = cluster_scratch[tx * VEC + e];
+      for (int j = 1; j < cluster; ++j) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          acc[e] = R::combine(acc[e], cluster_scratch[j * items + tx * VEC + e]);
+        }
+      }
+    }
+  }
+
+  const int clusters = split / cluster;
+  typename R::Out* out_row = out + slice * inner;
+  if (clusters == 1) {
+    if (holder && in_range) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) out_row[column + e] = R::finish(acc[e], reduce, mean != 0);
+    }
+    return;
+  }
+
+  const long long tile = slice * gridDim.x + blockIdx.x;
+  Acc* tile_partials = partials + tile * clusters * items;
+  if (holder) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) tile_partials[(part / cluster) * items + tx * VEC + e] = acc[e];
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned ticket = atomicAdd(&tickets[tile], 1u);
+    is_last = ticket == static_cast<unsigned>(clusters - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (holder && in_range) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      Acc total = R::identity();
+      for (int j = 0; j < clusters; ++j) {
+        total = R::combine(total, load_partial(tile_partials + j * items + tx * VEC + e));
+      }
+      out_row[column + e] = R::finish(total, reduce, mean != 0);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host: the plan and the launch
+
+enum class Shape { kWarpPerSlice, kCtaPerSlice, kColumns };
+
+struct Plan {
+  Shape shape = Shape::kWarpPerSlice;
+  int split = 1;      // CTAs per slice (or per column tile)
+  int cluster = 1;    // CTAs per thread-block cluster; divides split
+  int lanes_x = 32;   // columns kernel: threads along inner
+  int vec = 1;        // columns kernel: elements per thread along inner
+  long long tiles = 0;        // ticketed outputs: slices, or outer * column tiles
+  long long column_tiles = 0;
+  size_t acc_bytes = 0;
+  size_t partial_bytes = 0;   // scratch for partials (0 when one cluster covers a slice)
+  size_t ticket_bytes = 0;
+};
+
+int floor_pow2(long long v) {
+  int p = 1;
+  while (static_cast<long long>(p) * 2 <= v) p *= 2;
+  return p;
+}
+
+Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, long long inner,
+          int32_t device, int vec_bytes_limit) {
+  Plan p;
+  const int size = dtype_size(dtype);
+  const int sms = sm_count(device);
+  const long long target_ctas = static_cast<long long>(sms) * 4;
+  p.acc_bytes = op == TQ_ARGMAX ? 16 : 8;  // upper bound; every Acc fits 8 bytes but Indexed
+  if (inner == 1) {
+    const int vec = 16 / size;
+    const long long slice_bytes = reduce * size;
+    if (slice_bytes <= 4096 || (outer >= static_cast<long long>(sms) * 16 && slice_bytes <= 65536)) {
+      p.shape = Shape::kWarpPerSlice;
+      return p;
+    }
+    p.shape = Shape::kCtaPerSlice;
+    long long want = (target_ctas + outer - 1) / outer;
+    const long long per_pass = static_cast<long long>(kBlock) * vec * kUnroll;
+    long long most = reduce / per_pass;
+    if (most < 1) most = 1;
+    if (want > most) want = most;
+    if (want < 1) want = 1;
+    if (want <= kMaxCluster) {
+      p.split = floor_pow2(want);
+      p.cluster = p.split;
+    } else {
+      if (want > 1024) want = 1024;
+      p.split = static_cast<int>((want + kMaxCluster - 1) / kMaxCluster * kMaxCluster);
+      p.cluster = kMaxCluster;
+    }
+    p.tiles = outer;
+  } else {
+    p.shape = Shape::kColumns;
+    int vec = vec_bytes_limit / size;
+    if (vec > 4) vec = 4;
+    if (vec < 1) vec = 1;
+    while (vec > 1 && inner % vec != 0) vec /= 2;
+    p.vec = vec;
+    long long groups = (inner + vec - 1) / vec;
+    int lanes = 32;
+    while (lanes > 1 && lanes / 2 >= groups) lanes /= 2;
+    p.lanes_x = lanes;
+    p.column_tiles = (groups + lanes - 1) / lanes;
+    const long long base_ctas = p.column_tiles * outer;
+    long long want = (target_ctas + base_ctas - 1) / base_ctas;
+    const long long per_pass = static_cast<long long>(kBlock / lanes) * kUnroll;
+    long long most = reduce / per_pass;
+    if (most < 1) most = 1;
+    if (want > most) want = most;
+    if (want < 1) want = 1;
+    if (want <= kMaxCluster) {
+      p.split = floor_pow2(want);
+      p.cluster = p.split;
+    } else {
+      if (want > 512) want = 512;
+      p.split = static_cast<int>((want + kMaxCluster - 1) / kMaxCluster * kMaxCluster);
+      p.cluster = kMaxCluster;
+    }
+    p.tiles = base_ctas;
+  }
+  const int clusters = p.split / p.cluster;
+  if (clusters > 1) {
+    const long long items = p.shape == Shape::kColumns ? p.lanes_x * p.vec : 1;
+    p.partial_bytes = static_cast<size_t>(p.tiles) * clusters * items * p.acc_bytes;
+    p.partial_bytes = (p.partial_bytes + 255) / 256 * 256;
+    p.ticket_bytes = (static_cast<size_t>(p.tiles) * sizeof(unsigned) + 255) / 256 * 256;
+  }
+  return p;
+}
+
+template <typename Kernel, typename... Args>
+tq_status launch_clustered(Kernel kernel, dim3 grid, dim3 cluster, size_t smem, cudaStream_t stream,
+                           Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = dim3(kBlock);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = cluster.x;
+  attribute[0].val.clusterDim.y = cluster.y;
+  attribute[0].val.clusterDim.z = cluster.z;
+  config.attrs = attribute;
+  config.numAttrs = (cluster.x * cluster.y * cluster.z > 1) ? 1 : 0;
+  TQ_CUDA(cudaLaunchKernelEx(&config, kernel, args...));
+  return TQ_OK;
+}
+
+template <typename T, typename R>
+tq_status run(const Plan& p, const void* in, void* out, long long outer, long long reduce,
+              long long inner, bool mean, void* workspace, cudaStream_t stream) {
+  using Acc = typename R::Acc;
+  using Out = typename R::Out;
+  static_assert(sizeof(Acc) <= 16, "accumulators are sized as at most 16 bytes in plan()");
+  const T* input = static_cast<const T*>(in);
+  Out* output = static_cast<Out*>(out);
+  Acc* partials = static_cast<Acc*>(workspace);
+  unsigned* tickets =
+      reinterpret_cast<unsigned*>(static_cast<unsigned char*>(workspace) + p.partial_bytes);
+  if (p.ticket_bytes) TQ_CUDA(cudaMemsetAsync(tickets, 0, p.ticket_bytes, stream));
+  constexpr int kVec = 16 / sizeof(T);
+  switch (p.shape) {
+    case Shape::kWarpPerSlice: {
+      const long long blocks = (outer + kWarps - 1) / kWarps;
+      TQ_REQUIRE(blocks <= 0x7fffffffLL, TQ_UNSUPPORTED, "%lld slices are more than a grid holds", outer);
+      reduce_warp_per_slice<T, R, kVec><<<static_cast<unsigned>(blocks), kBlock, 0, stream>>>(
+          input, output, outer, reduce, mean ? 1 : 0);
+      return check_launch("reduce_warp_per_slice");
+    }
+    case Shape::kCtaPerSlice: {
+      const long long blocks = outer * p.split;
+      TQ_REQUIRE(blocks <= 0x7fffffffLL, TQ_UNSUPPORTED, "%lld slices are more than a grid holds", outer);
+      if (tq_status s = launch_clustered(reduce_cta_per_slice<T, R, kVec>,
+                                         dim3(static_cast<unsigned>(blocks)), dim3(p.cluster), 0,
+                                         stream, input, output, reduce, p.split, p.cluster,
+                                         mean ? 1 : 0, partials, tickets)) {
+        return s;
+      }
+      return check_launch("reduce_cta_per_slice");
+    }
+    case Shape::kColumns: {
+      TQ_REQUIRE(outer <= 65535, TQ_UNSUPPORTED,
+                 "a reduction with kept axes on both sides and %lld leading slices has no kernel", outer);
+      dim3 grid(static_cast<unsigned>(p.column_tiles), p.split, static_cast<unsigned>(outer));
+      auto go = [&](auto kernel, int vec) -> tq_status {
+        const size_t smem = (static_cast<size_t>(kBlock) * vec +
+                             static_cast<size_t>(p.cluster) * p.lanes_x * vec) * sizeof(Acc);
+        if (smem > 48 * 1024) {
+          TQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem)));
+        }
+        if (tq_status s = launch_clustered(kernel, grid, dim3(1, p.cluster, 1), smem, stream, input,
+                                           output, reduce, inner, p.lanes_x, p.split, p.cluster,
+                                           mean ? 1 : 0, partials, tickets)) {
+          return s;
+        }
+        return check_launch("reduce_columns");
+      };
+      constexpr int kColumnVec = kVec > 4 ? 4 : kVec;
+      if (p.vec == 1) return go(reduce_columns<T, R, 1>, 1);
+      if constexpr (kColumnVec >= 2) {
+        if (p.vec == 2) return go(reduce_columns<T, R, 2>, 2);
+      }
+      if constexpr (kColumnVec >= 4) {
+        if (p.vec == 4) return go(reduce_columns<T, R, 4>, 4);
+      }
+      return fail(TQ_INTERNAL, "no column kernel for %d elements per thread", p.vec);
+    }
+  }
+  return fail(TQ_INTERNAL, "unreachable reduction shape");
+}
+
+template <typename T>
+tq_status run_op(tq_reduce_op op, const Plan& p, const void* in, void* out, long long outer,
+                 long long reduce, long long inner, void* workspace, cudaStream_t stream) {
+  switch (op) {
+    case TQ_SUM: return run<T, SumReducer<T>>(p, in, out, outer, reduce, inner, false, workspace, stream);
+    case TQ_MEAN: return run<T, SumReducer<T>>(p, in, out, outer, reduce, inner, true, workspace, stream);
+    case TQ_AMAX: return run<T, ExtremeReducer<T, true>>(p, in, out, outer, reduce, inner, false, workspace, stream);
+    case TQ_AMIN: return run<T, ExtremeReducer<T, false>>(p, in, out, outer, reduce, inner, false, workspace, stream);
+    case TQ_ARGMAX: return run<T, ArgmaxReducer<T>>(p, in, out, outer, reduce, inner, false, workspace, stream);
+    default: return fail(TQ_INVALID_ARGUMENT, "unknown reduction %d", op);
+  }
+}
+
+tq_status validate(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, long long inner) {
+  TQ_REQUIRE(op >= TQ_SUM && op <= TQ_ARGMAX, TQ_INVALID_ARGUMENT, "unknown reduction %d", op);
+  TQ_REQUIRE(dtype_size(dtype) != 0 && dtype != TQ_BOOL, TQ_UNSUPPORTED,
+             "reductions have no kernel for element type %s", dtype_name(dtype));
+  TQ_REQUIRE(outer >= 0 && reduce >= 0 && inner >= 0, TQ_INVALID_ARGUMENT,
+             "negative extent in [%lld, %lld, %lld]", outer, reduce, inner);
+  TQ_REQUIRE(reduce > 0, TQ_UNSUPPORTED, "a reduction over no elements has no kernel");
+  TQ_REQUIRE(!(op == TQ_MEAN && (dtype == TQ_I32 || dtype == TQ_I64)), TQ_UNSUPPORTED,
+             "mean of an integer tensor has no kernel");
+  return TQ_OK;
+}
+
+// The columns kernel needs vector loads aligned in every row: inner * size and the base pointer
+// must both be multiples of the vector's bytes.
+int column_vec_bytes(const void* in, long long inner, int size) {
+  int bytes = 16;
+  while (bytes > size && (!aligned_to(in, bytes) || (inner * size) % bytes != 0)) bytes /= 2;
+  return bytes;
+}
+
+}  // namespace
+}  // namespace tq
+
+extern "C" {
+
+tq_status tq_reduce_workspace_bytes(tq_reduce_op op, tq_dtype dtype, int64_t outer, int64_t reduce,
+                                    int64_t inner, int32_t device, size_t* bytes) {
+  TQ_REQUIRE(bytes != nullptr, TQ_INVALID_ARGUMENT, "bytes out-pointer is null");
+  if (tq_status s = tq::validate(op, dtype, outer, reduce, inner)) return s;
+  *bytes = 0;
+  if (outer == 0 || inner == 0) return TQ_OK;
+  // The input's alignment is unknown here and decides the vector width of the columns kernel,
+  // which changes its tiling: answer with the largest need over the widths it may pick.
+  for (int limit = 16; limit >= tq::dtype_size(dtype); limit /= 2) {
+    tq::Plan p = tq::plan(op, dtype, outer, reduce, inner, device, limit);
+    if (p.partial_bytes + p.ticket_bytes > *bytes) *bytes = p.partial_bytes + p.ticket_bytes;
+  }
+  return TQ_OK;
+}
+
+tq_status tq_reduce_launch(tq_reduce_op op, tq_dtype dtype, const void* in, void* out, int64_t outer,
+                           int64_t reduce, int64_t inner, void* workspace, size_t workspace_bytes,
+                           int32_t device, void* stream) {
+  if (tq_status s = tq::validate(op, dtype, outer, reduce, inner)) return s;
+  if (outer == 0 || inner == 0) return TQ_OK;
+  TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");
+  const int size = tq::dtype_size(dtype);
+  TQ_REQUIRE(tq::aligned_to(in, size), TQ_INVALID_ARGUMENT, "input pointer is not aligned to its element type");
+  if (tq_status s = tq::use_device(device)) return s;
+  tq::Plan p = tq::plan(op, dtype, outer, reduce, inner, device,
+                        inner == 1 ? 16 : tq::column_vec_bytes(in, inner, size));
+  const size_t need = p.partial_bytes + p.ticket_bytes;
+  TQ_REQUIRE(need == 0 || (workspace != nullptr && workspace_bytes >= need), TQ_INVALID_ARGUMENT,
+             "this reduction needs %zu bytes of scratch and was given %zu", need, workspace_bytes);
+  TQ_REQUIRE(need == 0 || tq::aligned_to(workspace, 16), TQ_INVALID_ARGUMENT,
+             "scratch memory must be 16-byte aligned");
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case TQ_F32: return tq::run_op<float>(op, p, in, out, outer, reduce, inner, workspace, cuda_stream);
+    case TQ_F64: return tq::run_op<double>(op, p, in, out, outer, reduce, inner, workspace, cuda_stream);
+    case TQ_F16: return tq::run_op<__half>(op, p, in, out, outer, reduce, inner, workspace, cuda_stream);
+    case TQ_BF16: return tq::run_op<__nv_bfloat16>(op, p, in, out, outer, reduce, inner, workspace, cuda_stream);
+    case TQ_I32: return tq::run_op<int>(op, p, in, out, outer, reduce, inner, workspace, cuda_stream);
+    case TQ_I64: return tq::run_op<long long>(op, p, in, out, outer, reduce, inner, workspace, cuda_stream);
+    default: return tq::fail(TQ_UNSUPPORTED, "reductions have no kernel for element type %s", tq::dtype_name(dtype));
+  }
+}
+
+}  // extern "C"

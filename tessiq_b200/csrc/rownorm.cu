@@ -1,0 +1,530 @@
+// Row kernels that need a statistic of the whole row before they can write it: softmax,
+// LayerNorm, RMSNorm. The row is read from HBM once, kept in registers, and written once.
+//
+//   warp-per-row     rows of up to 32*VEC*8 elements: one warp holds a row; shuffles only.
+//   cluster-per-row  wider rows: a thread-block cluster of 1, 2, 4 or 8 CTAs holds a row
+//                    (256 threads x up to 8 vectors each per CTA). Statistics go warp shuffle ->
+//                    shared memory -> distributed shared memory: every CTA writes its block value
+//                    into each peer's slot array, one cluster barrier, every CTA folds the slots
+//                    in rank order, so all CTAs hold the same bits.
+//   loop-per-row     any width or alignment: one CTA streams the row three times (two for
+//                    RMSNorm). The fallback for rows that are unaligned or beyond what a cluster
+//                    can hold.
+//   softmax-columns  softmax over an axis that is not the last one: one thread per column, an
+//                    online max/sum pass and a write pass, coalesced along the kept axis.
+//
+// Semantics follow csrc/custom_ops/softmax/softmax.cu:19-61 (softmax), csrc/tessiq/codegen/
+// norm.cpp:22-135 (LayerNorm: mean, then centred sum of squares, rstd = 1/sqrt(var+eps)) and
+// csrc/custom_ops/rms_norm/rms_norm.cu:15-42, except that a NaN anywhere in a softmax row makes
+// the row NaN, as aten::_softmax does on the reference's host device (the reference's own kernel
+// drops NaN from the maximum).
+#include <cooperative_groups.h>
+
+#include <limits>
+
+#include "common.h"
+
+namespace cg = cooperative_groups;
+
+namespace tq {
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kWarps = kBlock / 32;
+constexpr int kMaxCluster = 8;
+constexpr int kMaxVectors = 8;
+
+enum RowOp { kSoftmax = 0, kLayerNorm = 1, kRmsNorm = 2 };
+
+struct RowArgs {
+  const void* in;
+  void* out;
+  const void* weight;
+  const void* bias;
+  void* mean;
+  void* rstd;
+  long long rows;
+  long long width;
+  double eps;
+  int stat_is_f32;  // mean/rstd are stored as float rather than as the input's type
+};
+
+template <typename C> __device__ __forceinline__ C math_exp(C v);
+template <> __device__ __forceinline__ float math_exp<float>(float v) { return expf(v); }
+template <> __device__ __forceinline__ double math_exp<double>(double v) { return exp(v); }
+template <typename C> __device__ __forceinline__ C math_sqrt(C v);
+template <> __device__ __forceinline__ float math_sqrt<float>(float v) { return sqrtf(v); }
+template <> __device__ __forceinline__ double math_sqrt<double>(double v) { return sqrt(v); }
+
+template <typename C> __device__ __forceinline__ C nan_max(C a, C b) {
+  // NaN-propagating: the row's NaN must reach every element of the result.
+  if (a != a) return a;
+  if (b != b) return b;
+  return a > b ? a : b;
+}
+
+template <typename C, bool kMax> __device__ __forceinline__ C fold(C a, C b) {
+  if constexpr (kMax) return nan_max(a, b);
+  return a + b;
+}
+
+template <typename C, bool kMax> __device__ __forceinline__ C warp_fold(C v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    v = fold<C, kMax>(v, __shfl_xor_sync(0xffffffffu, v, offset));
+  }
+  return v;
+}
+
+// Every thread of the CTA gets the CTA-wide result.
+template <typename C, bool kMax>
+__device__ __forceinline__ C block_fold(C v, C* warp_scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_fold<C, kMax>(v);
+  if (lane == 0) warp_scratch[warp] = v;
+  __syncthreads();
+  C total = warp_scratch[0];
+#pragma unroll
+  for (int w = 1; w < kWarps; ++w) total = fold<C, kMax>(total, warp_scratch[w]);
+  __syncthreads();  // warp_scratch is reused by the next statistic
+  return total;
+}
+
+// Every thread of every CTA of the cluster gets the cluster-wide result. `slots` is an array of
+// kMaxCluster values in this CTA's shared memory that no other statistic uses.
+template <typename C, bool kMax>
+__device__ __forceinline__ C cluster_fold(C v, C* warp_scratch, C* slots, int cluster) {
+  v = block_fold<C, kMax>(v, warp_scratch);
+  if (cluster == 1) return v;
+  cg::cluster_group group = cg::this_cluster();
+  const unsigned rank = group.block_rank();
+  if (threadIdx.x < cluster) {
+    C* peer = group.map_shared_rank(slots, threadIdx.x);
+    peer[rank] = v;
+  }
+  group.sync();
+  C total = slots[0];
+  for (int r = 1; r < cluster; ++r) total = fold<C, kMax>(total, slots[r]);
+  return total;
+}
+
+template <typename T>
+__device__ __forceinline__ void store_stat(void* pointer, long long row, float value, int is_f32) {
+  if (pointer == nullptr) return;
+  if (is_f32) {
+    static_cast<float*>(pointer)[row] = value;
+  } else {
+    static_cast<T*>(pointer)[row] = from_compute<T, float>(value);
+  }
+}
+
+// The arithmetic shared by the register-resident kernels. `v` holds this thread's elements of the
+// row as floats (invalid ones flagged in `valid`); Fold(value, is_max, stage) reduces over the row.
+template <typename T, typename OutT, int VEC, int K, int OP, typename FoldFn>
+__device__ __forceinline__ void finish_row(float (&v)[K][VEC], const bool (&valid)[K],
+                                           const long long (&vector_index)[K], const RowArgs& args,
+                                           long long row, bool writes_stats, FoldFn fold_row) {
+  OutT* out_row = static_cast<OutT*>(args.out) + row * args.width;
+  const float width = static_cast<float>(args.width);
+  if constexpr (OP == kSoftmax) {
+    float local = -std::numeric_limits<float>::infinity();
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      if (valid[j]) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) local = nan_max(local, v[j][e]);
+      }
+    }
+    const float row_max = fold_row(local, /*is_max=*/true, 0);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      if (valid[j]) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          v[j][e] = expf(v[j][e] - row_max);
+          sum += v[j][e];
+        }
+      }
+    }
+    const float inverse = 1.f / fold_row(sum, /*is_max=*/false, 1);
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      if (valid[j]) {
+        Vec<OutT, VEC> y;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) y.v[e] = from_compute<OutT, float>(v[j][e] * inverse);
+        store_stream<OutT, VEC>(out_row + vector_index[j] * VEC, y);
+      }
+    }
+  } else {
+    float mean = 0.f;
+    if constexpr (OP == kLayerNorm) {
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        if (valid[j]) {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) sum += v[j][e];
+        }
+      }
+      mean = fold_row(sum, false, 0) / width;
+    }
+    float squares = 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      if (valid[j]) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float centred = v[j][e] - mean;
+          squares += centred * centred;
+        }
+      }
+    }
+    const float variance = fold_row(squares, false, 1) / width;
+    const float rstd = 1.f / sqrtf(variance + static_cast<float>(args.eps));
+    if (writes_stats) {
+      if constexpr (OP == kLayerNorm) store_stat<T>(args.mean, row, mean, args.stat_is_f32);
+      store_stat<T>(args.rstd, row, rstd, args.stat_is_f32);
+    }
+    const T* weight = static_cast<const T*>(args.weight);
+    const T* bias = static_cast<const T*>(args.bias);
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      if (valid[j]) {
+        Vec<T, VEC> w, b;
+        if (weight) w = *reinterpret_cast<const Vec<T, VEC>*>(weight + vector_index[j] * VEC);
+        if (bias) b = *reinterpret_cast<const Vec<T, VEC>*>(bias + vector_index[j] * VEC);
+        Vec<OutT, VEC> y;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          float value = (v[j][e] - mean) * rstd;
+          if (weight) value *= to_compute(w.v[e]);
+          if (bias) value += to_compute(b.v[e]);
+          y.v[e] = from_compute<OutT, float>(value);
+        }
+        store_stream<OutT, VEC>(out_row + vector_index[j] * VEC, y);
+      }
+    }
+  }
+}
+
+// One warp per row; 8 rows per CTA.
+template <typename T, typename OutT, int VEC, int K, int OP>
+__global__ void __launch_bounds__(kBlock) row_warp_kernel(RowArgs args) {
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  if (row >= args.rows) return;
+  const long long vectors = args.width / VEC;
+  const T* in_row = static_cast<const T*>(args.in) + row * args.width;
+  float v[K][VEC];
+  bool valid[K];
+  long long vector_index[K];
+#pragma unroll
+  for (int j = 0; j < K; ++j) {
+    vector_index[j] = static_cast<long long>(j) * 32 + lane;
+    valid[j] = vector_index[j] < vectors;
+    if (valid[j]) {
+      Vec<T, VEC> x = load_stream<T, VEC>(in_row + vector_index[j] * VEC);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) v[j][e] = to_compute(x.v[e]);
+    }
+  }
+  auto fold_row = [](float value, bool is_max, int) {
+    return is_max ? warp_fold<float, true>(value) : warp_fold<float, false>(value);
+  };
+  finish_row<T, OutT, VEC, K, OP>(v, valid, vector_index, args, row, lane == 0, fold_row);
+}
+
+// A cluster of `cluster` CTAs per row. blockIdx.x = row * cluster + rank.
+template <typename T, typename OutT, int VEC, int K, int OP>
+__global__ void __launch_bounds__(kBlock) row_cluster_kernel(RowArgs args, int cluster) {
+  __shared__ float warp_scratch[kWarps];
+  __shared__ float slots[2][kMaxCluster];
+  const long long row = blockIdx.x / cluster;
+  const int rank = static_cast<int>(blockIdx.x % cluster);
+  const long long vectors = args.width / VEC;
+  const T* in_row = static_cast<const T*>(args.in) + row * args.width;
+  float v[K][VEC];
+  bool valid[K];
+  long long vector_index[K];
+#pragma unroll
+  for (int j = 0; j < K; ++j) {
+    vector_index[j] = (static_cast<long long>(rank) * K + j) * kBlock + threadIdx.x;
+    valid[j] = vector_index[j] < vectors;
+    if (valid[j]) {
+      Vec<T, VEC> x = load_stream<T, VEC>(in_row + vector_index[j] * VEC);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) v[j][e] = to_compute(x.v[e]);
+    }
+  }
+  auto fold_row = [&](float value, bool is_max, int stage) {
+    return is_max ? cluster_fold<float, true>(value, warp_scratch, slots[stage], cluster)
+                  : cluster_fold<float, false>(value, warp_scratch, slots[stage], cluster);
+  };
+  finish_row<T, OutT, VEC, K, OP>(v, valid, vector_index, args, row,
+                                  rank == 0 && threadIdx.x == 0, fold_row);
+}
+
+// Any width, any alignment: one CTA per row, scalar loads, the row re-read for each statistic.
+template <typename T, typename OutT, int OP>
+__global__ void __launch_bounds__(kBlock) row_loop_kernel(RowArgs args) {
+  using C = typename Compute<T>::type;  // float, or double for f64 rows
+  __shared__ C warp_scratch[kWarps];
+  const long long row = blockIdx.x;
+  const long long width = args.width;
+  const T* in_row = static_cast<const T*>(args.in) + row * width;
+  OutT* out_row = static_cast<OutT*>(args.out) + row * width;
+  if constexpr (OP == kSoftmax) {
+    C local = -std::numeric_limits<C>::infinity();
+    for (long long i = threadIdx.x; i < width; i += kBlock) local = nan_max<C>(local, to_compute(in_row[i]));
+    const C row_max = block_fold<C, true>(local, warp_scratch);
+    C sum = 0;
+    for (long long i = threadIdx.x; i < width; i += kBlock) sum += math_exp<C>(to_compute(in_row[i]) - row_max);
+    const C inverse = C(1) / block_fold<C, false>(sum, warp_scratch);
+    for (long long i = threadIdx.x; i < width; i += kBlock) {
+      out_row[i] = from_compute<OutT, C>(math_exp<C>(to_compute(in_row[i]) - row_max) * inverse);
+    }
+  } else {
+    C mean = 0;
+    if constexpr (OP == kLayerNorm) {
+      C sum = 0;
+      for (long long i = threadIdx.x; i < width; i += kBlock) sum += to_compute(in_row[i]);
+      mean = block_fold<C, false>(sum, warp_scratch) / static_cast<C>(width);
+    }
+    C squares = 0;
+    for (long long i = threadIdx.x; i < width; i += kBlock) {
+      const C centred = to_compute(in_row[i]) - mean;
+      squares += centred * centred;
+    }
+    const C variance = block_fold<C, false>(squares, warp_scratch) / static_cast<C>(width);
+    const C rstd = C(1) / math_sqrt<C>(variance + static_cast<C>(args.eps));
+    if (threadIdx.x == 0) {
+      if constexpr (std::is_same_v<C, double>) {
+        if (OP == kLayerNorm && args.mean) static_cast<double*>(args.mean)[row] = mean;
+        if (args.rstd) static_cast<double*>(args.rstd)[row] = rstd;
+      } else {
+        if constexpr (OP == kLayerNorm) store_stat<T>(args.mean, row, mean, args.stat_is_f32);
+        store_stat<T>(args.rstd, row, rstd, args.stat_is_f32);
+      }
+    }
+    const T* weight = static_cast<const T*>(args.weight);
+    const T* bias = static_cast<const T*>(args.bias);
+    for (long long i = threadIdx.x; i < width; i += kBlock) {
+      C value = (to_compute(in_row[i]) - mean) * rstd;
+      if (weight) value *= to_compute(weight[i]);
+      if (bias) value += to_compute(bias[i]);
+      out_row[i] = from_compute<OutT, C>(value);
+    }
+  }
+}
+
+// softmax over the middle axis of [outer, extent, inner], inner > 1: a thread per (outer, inner)
+// column; pass 1 keeps a running maximum and a sum rescaled whenever the maximum grows, pass 2
+// writes. Loads and stores of a warp are contiguous along inner.
+template <typename T, typename OutT>
+__global__ void __launch_bounds__(kBlock)
+softmax_columns_kernel(const T* __restrict__ in, OutT* __restrict__ out, long long outer,
+                       long long extent, long long inner) {
+  using C = typename Compute<T>::type;
+  const long long column = static_cast<long long>(blockIdx.x) * kBlock + threadIdx.x;
+  if (column >= outer * inner) return;
+  const long long o = column / inner, i = column % inner;
+  const T* base = in + o * extent * inner + i;
+  OutT* target = out + o * extent * inner + i;
+  C running_max = -std::numeric_limits<C>::infinity();
+  C sum = 0;
+  bool saw_nan = false;
+  for (long long r = 0; r < extent; ++r) {
+    const C x = to_compute(base[r * inner]);
+    if (x != x) saw_nan = true;
+    if (x > running_max) {
+      // exp(-inf - finite) is 0, so the first element needs no special case.
+      sum = sum * math_exp<C>(running_max - x) + C(1);
+      running_max = x;
+    } else {
+      sum += math_exp<C>(x - running_max);
+    }
+  }
+  if (saw_nan) sum = std::numeric_limits<C>::quiet_NaN();
+  const C inverse = C(1) / sum;
+  for (long long r = 0; r < extent; ++r) {
+    const C x = to_compute(base[r * inner]);
+    target[r * inner] = from_compute<OutT, C>(math_exp<C>(x - running_max) * inverse);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host dispatch
+
+template <typename Kernel>
+tq_status launch_rows(Kernel kernel, long long blocks, int cluster, cudaStream_t stream,
+                      const RowArgs& args, const char* name) {
+  TQ_REQUIRE(blocks <= 0x7fffffffLL, TQ_UNSUPPORTED, "%lld rows are more than a grid holds", args.rows);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(blocks));
+  config.blockDim = dim3(kBlock);
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = cluster;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = cluster > 1 ? 1 : 0;
+  TQ_CUDA(cudaLaunchKernelEx(&config, kernel, args, cluster));
+  return check_launch(name);
+}
+
+template <typename T, typename OutT, int VEC, int OP>
+tq_status run_vector(const RowArgs& args, cudaStream_t stream, bool* handled) {
+  *handled = true;
+  const long long vectors = args.width / VEC;
+  if (vectors <= 32 * kMaxVectors) {
+    const long long blocks = (args.rows + kWarps - 1) / kWarps;
+    TQ_REQUIRE(blocks <= 0x7fffffffLL, TQ_UNSUPPORTED, "%lld rows are more than a grid holds", args.rows);
+    const unsigned grid = static_cast<unsigned>(blocks);
+    if (vectors <= 32) {
+      row_warp_kernel<T, OutT, VEC, 1, OP><<<grid, kBlock, 0, stream>>>(args);
+    } else if (vectors <= 64) {
+      row_warp_kernel<T, OutT, VEC, 2, OP><<<grid, kBlock, 0, stream>>>(args);
+    } else if (vectors <= 128) {
+      row_warp_kernel<T, OutT, VEC, 4, OP><<<grid, kBlock, 0, stream>>>(args);
+    } else {
+      row_warp_kernel<T, OutT, VEC, 8, OP><<<grid, kBlock, 0, stream>>>(args);
+    }
+    return check_launch("row_warp_kernel");
+  }
+  int cluster = 1;
+  while (cluster < kMaxCluster && vectors > static_cast<long long>(kBlock) * kMaxVectors * cluster) cluster *= 2;
+  if (vectors > static_cast<long long>(kBlock) * kMaxVectors * cluster) {
+    *handled = false;  // wider than a cluster's registers
+    return TQ_OK;
+  }
+  const long long per_cta = (vectors + cluster - 1) / cluster;
+  const long long blocks = args.rows * cluster;
+  if (per_cta <= kBlock) return launch_rows(row_cluster_kernel<T, OutT, VEC, 1, OP>, blocks, cluster, stream, args, "row_cluster_kernel");
+  if (per_cta <= kBlock * 2) return launch_rows(row_cluster_kernel<T, OutT, VEC, 2, OP>, blocks, cluster, stream, args, "row_cluster_kernel");
+  if (per_cta <= kBlock * 4) return launch_rows(row_cluster_kernel<T, OutT, VEC, 4, OP>, blocks, cluster, stream, args, "row_cluster_kernel");
+  return launch_rows(row_cluster_kernel<T, OutT, VEC, 8, OP>, blocks, cluster, stream, args, "row_cluster_kernel");
+}
+
+template <typename T, typename OutT, int OP>
+tq_status run_rows(const RowArgs& args, cudaStream_t stream) {
+  if constexpr (!std::is_same_v<T, double>) {
+    constexpr int kVec = 16 / sizeof(T);
+    constexpr size_t kOutBytes = sizeof(OutT) * kVec;
+    const bool vectorisable =
+        args.width % kVec == 0 && aligned_to(args.in, 16) && aligned_to(args.out, kOutBytes > 16 ? 16 : kOutBytes) &&
+        (args.weight == nullptr || aligned_to(args.weight, 16)) &&
+        (args.bias == nullptr || aligned_to(args.bias, 16));
+    if (vectorisable) {
+      bool handled = false;
+      if (tq_status s = run_vector<T, OutT, kVec, OP>(args, stream, &handled)) return s;
+      if (handled) return TQ_OK;
+    }
+  }
+  TQ_REQUIRE(args.rows <= 0x7fffffffLL, TQ_UNSUPPORTED, "%lld rows are more than a grid holds", args.rows);
+  row_loop_kernel<T, OutT, OP><<<static_cast<unsigned>(args.rows), kBlock, 0, stream>>>(args);
+  return check_launch("row_loop_kernel");
+}
+
+template <typename T, typename OutT>
+tq_status run_softmax(const void* in, void* out, long long outer, long long extent, long long inner,
+                      cudaStream_t stream) {
+  if (inner == 1) {
+    RowArgs args = {};
+    args.in = in;
+    args.out = out;
+    args.rows = outer;
+    args.width = extent;
+    return run_rows<T, OutT, kSoftmax>(args, stream);
+  }
+  const long long columns = outer * inner;
+  const long long blocks = (columns + kBlock - 1) / kBlock;
+  TQ_REQUIRE(blocks <= 0x7fffffffLL, TQ_UNSUPPORTED, "%lld softmax columns are more than a grid holds", columns);
+  softmax_columns_kernel<T, OutT><<<static_cast<unsigned>(blocks), kBlock, 0, stream>>>(
+      static_cast<const T*>(in), static_cast<OutT*>(out), outer, extent, inner);
+  return check_launch("softmax_columns_kernel");
+}
+
+}  // namespace
+}  // namespace tq
+
+extern "C" {
+
+tq_status tq_softmax_launch(tq_dtype dtype, tq_dtype out_dtype, const void* in, void* out,
+                            int64_t outer, int64_t extent, int64_t inner, int32_t device,
+                            void* stream) {
+  TQ_REQUIRE(outer >= 0 && extent >= 0 && inner >= 0, TQ_INVALID_ARGUMENT,
+             "negative extent in [%lld, %lld, %lld]", (long long)outer, (long long)extent, (long long)inner);
+  if (outer == 0 || extent == 0 || inner == 0) return TQ_OK;
+  TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");
+  if (tq_status s = tq::use_device(device)) return s;
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  if (dtype == TQ_F32 && out_dtype == TQ_F32) return tq::run_softmax<float, float>(in, out, outer, extent, inner, cuda_stream);
+  if (dtype == TQ_BF16 && out_dtype == TQ_BF16) return tq::run_softmax<__nv_bfloat16, __nv_bfloat16>(in, out, outer, extent, inner, cuda_stream);
+  if (dtype == TQ_F16 && out_dtype == TQ_F16) return tq::run_softmax<__half, __half>(in, out, outer, extent, inner, cuda_stream);
+  if (dtype == TQ_BF16 && out_dtype == TQ_F32) return tq::run_softmax<__nv_bfloat16, float>(in, out, outer, extent, inner, cuda_stream);
+  if (dtype == TQ_F16 && out_dtype == TQ_F32) return tq::run_softmax<__half, float>(in, out, outer, extent, inner, cuda_stream);
+  if (dtype == TQ_F64 && out_dtype == TQ_F64) return tq::run_softmax<double, double>(in, out, outer, extent, inner, cuda_stream);
+  return tq::fail(TQ_UNSUPPORTED, "softmax has no kernel for %s -> %s", tq::dtype_name(dtype), tq::dtype_name(out_dtype));
+}
+
+tq_status tq_layer_norm_launch(tq_dtype dtype, const void* in, const void* weight, const void* bias,
+                               void* out, void* mean, void* rstd, tq_dtype stat_dtype, int64_t rows,
+                               int64_t width, double eps, int32_t device, void* stream) {
+  TQ_REQUIRE(rows >= 0 && width >= 0, TQ_INVALID_ARGUMENT, "negative extent in [%lld, %lld]", (long long)rows, (long long)width);
+  if (rows == 0) return TQ_OK;
+  TQ_REQUIRE(width > 0, TQ_UNSUPPORTED, "LayerNorm over no elements has no kernel");
+  TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");
+  TQ_REQUIRE(stat_dtype == dtype || (stat_dtype == TQ_F32 && dtype != TQ_F64), TQ_UNSUPPORTED,
+             "LayerNorm statistics of type %s for %s rows have no kernel", tq::dtype_name(stat_dtype), tq::dtype_name(dtype));
+  if (tq_status s = tq::use_device(device)) return s;
+  tq::RowArgs args = {};
+  args.in = in;
+  args.out = out;
+  args.weight = weight;
+  args.bias = bias;
+  args.mean = mean;
+  args.rstd = rstd;
+  args.rows = rows;
+  args.width = width;
+  args.eps = eps;
+  args.stat_is_f32 = stat_dtype == TQ_F32 ? 1 : 0;
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case TQ_F32: return tq::run_rows<float, float, tq::kLayerNorm>(args, cuda_stream);
+    case TQ_BF16: return tq::run_rows<__nv_bfloat16, __nv_bfloat16, tq::kLayerNorm>(args, cuda_stream);
+    case TQ_F16: return tq::run_rows<__half, __half, tq::kLayerNorm>(args, cuda_stream);
+    case TQ_F64: return tq::run_rows<double, double, tq::kLayerNorm>(args, cuda_stream);
+    default: return tq::fail(TQ_UNSUPPORTED, "LayerNorm has no kernel for element type %s", tq::dtype_name(dtype));
+  }
+}
+
+tq_status tq_rms_norm_launch(tq_dtype dtype, const void* in, const void* weight, void* out,
+                             int64_t rows, int64_t width, double eps, int32_t device, void* stream) {
+  TQ_REQUIRE(rows >= 0 && width >= 0, TQ_INVALID_ARGUMENT, "negative extent in [%lld, %lld]", (long long)rows, (long long)width);
+  if (rows == 0) return TQ_OK;
+  TQ_REQUIRE(width > 0, TQ_UNSUPPORTED, "RMSNorm over no elements has no kernel");
+  TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");
+  if (tq_status s = tq::use_device(device)) return s;
+  tq::RowArgs args = {};
+  args.in = in;
+  args.out = out;
+  args.weight = weight;
+  args.rows = rows;
+  args.width = width;
+  args.eps = eps;
+  args.stat_is_f32 = 1;
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case TQ_F32: return tq::run_rows<float, float, tq::kRmsNorm>(args, cuda_stream);
+    case TQ_BF16: return tq::run_rows<__nv_bfloat16, __nv_bfloat16, tq::kRmsNorm>(args, cuda_stream);
+    case TQ_F16: return tq::run_rows<__half, __half, tq::kRmsNorm>(args, cuda_stream);
+    case TQ_F64: return tq::run_rows<double, double, tq::kRmsNorm>(args, cuda_stream);
+    default: return tq::fail(TQ_UNSUPPORTED, "RMSNorm has no kernel for element type %s", tq::dtype_name(dtype));
+  }
+}
+
+}  // extern "C"

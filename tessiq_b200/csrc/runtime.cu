@@ -1,0 +1,163 @@
+// Library-wide state: error slot, device selection, per-GPU streams, the bump arena and the
+// device-side status word that bounded waits report through.
+#include <mutex>
+#include <vector>
+
+#include "common.h"
+
+namespace tq {
+
+namespace {
+thread_local std::string g_error = "";
+std::mutex g_mutex;
+constexpr int kMaxDevices = 64;
+int g_sm_count[kMaxDevices] = {0};
+int32_t* g_status_word[kMaxDevices] = {nullptr};
+}  // namespace
+
+void set_error(const char* text) { g_error = text ? text : ""; }
+
+tq_status fail(tq_status code, const char* format, ...) {
+  char buffer[1024];
+  va_list args;
+  va_start(args, format);
+  vsnprintf(buffer, sizeof(buffer), format, args);
+  va_end(args);
+  g_error = buffer;
+  return code;
+}
+
+tq_status use_device(int32_t device) {
+  TQ_REQUIRE(device >= 0 && device < kMaxDevices, TQ_INVALID_ARGUMENT,
+             "device ordinal %d is out of range", device);
+  int current = -1;
+  cudaError_t status = cudaGetDevice(&current);
+  if (status != cudaSuccess) {
+    return fail(TQ_EXTERNAL, "no usable CUDA device: %s", cudaGetErrorString(status));
+  }
+  if (current != device) TQ_CUDA(cudaSetDevice(device));
+  return TQ_OK;
+}
+
+int sm_count(int32_t device) {
+  if (device < 0 || device >= kMaxDevices) return 148;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_sm_count[device] == 0) {
+    int value = 0;
+    if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        value <= 0) {
+      value = 148;
+    }
+    g_sm_count[device] = value;
+  }
+  return g_sm_count[device];
+}
+
+int32_t* device_status_word(int32_t device) {
+  if (device < 0 || device >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_status_word[device] == nullptr) {
+    int32_t* word = nullptr;
+    if (cudaMalloc(&word, 256) != cudaSuccess) return nullptr;
+    if (cudaMemset(word, 0, 256) != cudaSuccess) return nullptr;
+    g_status_word[device] = word;
+  }
+  return g_status_word[device];
+}
+
+}  // namespace tq
+
+struct tq_arena {
+  int32_t device;
+  size_t bytes;
+  char* base;
+};
+
+extern "C" {
+
+int32_t tq_abi_version(void) { return 1000; }
+
+const char* tq_last_error(void) { return tq::g_error.c_str(); }
+
+int32_t tq_dtype_size(tq_dtype dtype) { return tq::dtype_size(dtype); }
+
+int32_t tq_device_count(void) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return count;
+}
+
+tq_status tq_stream_create(int32_t device, void** stream) {
+  TQ_REQUIRE(stream != nullptr, TQ_INVALID_ARGUMENT, "stream out-pointer is null");
+  if (tq_status s = tq::use_device(device)) return s;
+  cudaStream_t created = nullptr;
+  TQ_CUDA(cudaStreamCreateWithFlags(&created, cudaStreamNonBlocking));
+  *stream = created;
+  return TQ_OK;
+}
+
+tq_status tq_stream_destroy(int32_t device, void* stream) {
+  if (tq_status s = tq::use_device(device)) return s;
+  TQ_CUDA(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
+  return TQ_OK;
+}
+
+tq_status tq_stream_synchronize(int32_t device, void* stream) {
+  if (tq_status s = tq::use_device(device)) return s;
+  TQ_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  return TQ_OK;
+}
+
+tq_status tq_arena_create(int32_t device, size_t bytes, tq_arena** arena) {
+  TQ_REQUIRE(arena != nullptr, TQ_INVALID_ARGUMENT, "arena out-pointer is null");
+  TQ_REQUIRE(bytes > 0, TQ_INVALID_ARGUMENT, "an arena of 0 bytes");
+  if (tq_status s = tq::use_device(device)) return s;
+  void* base = nullptr;
+  cudaError_t status = cudaMalloc(&base, bytes);
+  if (status == cudaErrorMemoryAllocation) {
+    cudaGetLastError();
+    return tq::fail(TQ_RESOURCE_EXHAUSTED, "device %d has no %zu bytes for an arena", device, bytes);
+  }
+  TQ_CUDA(status);
+  *arena = new tq_arena{device, bytes, static_cast<char*>(base)};
+  return TQ_OK;
+}
+
+tq_status tq_arena_destroy(tq_arena* arena) {
+  if (arena == nullptr) return TQ_OK;
+  if (tq_status s = tq::use_device(arena->device)) return s;
+  cudaError_t status = cudaFree(arena->base);
+  delete arena;
+  TQ_CUDA(status);
+  return TQ_OK;
+}
+
+tq_status tq_arena_at(const tq_arena* arena, size_t offset, size_t bytes, void** pointer) {
+  TQ_REQUIRE(arena != nullptr && pointer != nullptr, TQ_INVALID_ARGUMENT, "null arena or pointer");
+  TQ_REQUIRE(offset <= arena->bytes && bytes <= arena->bytes - offset, TQ_INVALID_ARGUMENT,
+             "range [%zu, %zu) is outside an arena of %zu bytes", offset, offset + bytes,
+             arena->bytes);
+  *pointer = arena->base + offset;
+  return TQ_OK;
+}
+
+size_t tq_arena_bytes(const tq_arena* arena) { return arena ? arena->bytes : 0; }
+
+tq_status tq_status_poll(int32_t device, void* stream, int32_t* device_status) {
+  TQ_REQUIRE(device_status != nullptr, TQ_INVALID_ARGUMENT, "status out-pointer is null");
+  if (tq_status s = tq::use_device(device)) return s;
+  int32_t* word = tq::device_status_word(device);
+  TQ_REQUIRE(word != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  int32_t host = 0;
+  TQ_CUDA(cudaMemcpyAsync(&host, word, sizeof(host), cudaMemcpyDeviceToHost, cuda_stream));
+  TQ_CUDA(cudaStreamSynchronize(cuda_stream));
+  if (host != 0) TQ_CUDA(cudaMemsetAsync(word, 0, sizeof(host), cuda_stream));
+  *device_status = host;
+  return TQ_OK;
+}
+
+}  // extern "C"
