@@ -1,0 +1,470 @@
+"""Benchmark of the hot path on BASELINE config 2: row reductions and normalisation.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step = one pass of the hot path over one batch of synthetic input: x ~ N(0,1) of shape
+[32768, 4096] in f32 and in bf16, through sum, mean, amax, argmax, softmax and eval LayerNorm over
+the last axis, then the same six operations on the transposed, non-contiguous view x.t(), and the
+pack (x.t().contiguous()) alone — 13 operations per element type, 26 per step. The metric is the
+algorithmic HBM bytes of the step (each operand read once, each result written once; a pack made on
+the way is not credited) divided by the step's time, in GB/s, summed over ranks.
+
+`value` is device throughput with inputs resident in HBM: the step is captured once into a CUDA
+graph and replayed, timed with CUDA events on the replay stream. The input (768 MiB) is larger
+than L2 (126 MB), so nothing needs flushing between steps. `e2e` is the same step through the public
+API (`tessiq_b200.ops`) with HOST buffers: x is copied from pinned host memory, cast to bf16 on the
+device, every result is copied back to pinned host memory, all inside the timed region.
+
+With more than one GPU every rank runs the same step on its own rows (the path shards by rows with
+no exchange), so scaling is weak; the times are combined as the max over ranks.
+
+`--impl reference` times the reference's CPU implementation of the same step (PyTorch's CPU
+kernels, which its CPU device `tessiq:0` forwards every operator to) on the host cores, on a
+bounded sample of the rows.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+ROWS, WIDTH = 32768, 4096
+METRIC = "fused_kernel_hbm_throughput"
+UNIT = "GB/s"
+
+
+def algorithmic_bytes(rows: int, width: int, size: int) -> dict[str, int]:
+    """Bytes per operation (SURVEY/DESIGN table): operands read once, results written once."""
+    n = rows * width
+    out = {}
+    for view, (r, w) in (("rows", (rows, width)), ("cols", (width, rows))):
+        for op in ("sum", "mean", "amax"):
+            out[f"{op}_{view}"] = n * size + r * size
+        out[f"argmax_{view}"] = n * size + r * 8
+        out[f"softmax_{view}"] = 2 * n * size
+        out[f"layer_norm_{view}"] = 2 * n * size + 2 * w * size
+    out["pack"] = 2 * n * size
+    return out
+
+
+def peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock and throttle-reason samples of one GPU while a region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.process, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.process = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.process is not None:
+            self.process.terminate()
+            try:
+                output, _ = self.process.communicate(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.process.kill()
+                output, _ = self.process.communicate()
+            self.lines = [line for line in output.splitlines() if line.strip()]
+
+    def summary(self) -> dict:
+        sm, sm_max, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            fields = [f.strip() for f in line.split(",")]
+            if len(fields) < 6:
+                continue
+            try:
+                sm.append(float(fields[0]))
+                sm_max.append(float(fields[1]))
+            except ValueError:
+                continue
+            for name, field in zip(names, fields[2:6]):
+                if field.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# The step on the GPU
+
+
+class Step:
+    """The 26 operations with every output preallocated, so a step is launches only."""
+
+    def __init__(self, device: int):
+        import torch
+
+        from tessiq_b200 import kernel as K
+
+        self.torch, self.K, self.device = torch, K, device
+        self.launches = 0
+        g = torch.Generator().manual_seed(1234 + device)
+        x = torch.randn(ROWS, WIDTH, generator=g)
+        gamma = 1 + torch.randn(WIDTH, generator=g) * 0.02
+        beta = torch.randn(WIDTH, generator=g) * 0.02
+        gamma_t = 1 + torch.randn(ROWS, generator=g) * 0.02
+        beta_t = torch.randn(ROWS, generator=g) * 0.02
+        self.host_x = x.pin_memory()
+        dev = f"cuda:{device}"
+        self.sets = {}
+        for name, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+            xd = x.to(dev).to(dtype)
+            s = {"x": xd, "gamma": gamma.to(dev).to(dtype), "beta": beta.to(dev).to(dtype),
+                 "gamma_t": gamma_t.to(dev).to(dtype), "beta_t": beta_t.to(dev).to(dtype)}
+            for view, r in (("rows", ROWS), ("cols", WIDTH)):
+                for op in ("sum", "mean", "amax"):
+                    s[f"{op}_{view}"] = torch.empty(r, dtype=dtype, device=dev)
+                s[f"argmax_{view}"] = torch.empty(r, dtype=torch.int64, device=dev)
+            s["softmax_rows"] = torch.empty(ROWS, WIDTH, dtype=dtype, device=dev)
+            s["layer_norm_rows"] = torch.empty(ROWS, WIDTH, dtype=dtype, device=dev)
+            s["pack"] = torch.empty(WIDTH, ROWS, dtype=dtype, device=dev)
+            s["softmax_cols"] = torch.empty(WIDTH, ROWS, dtype=dtype, device=dev)
+            s["layer_norm_cols"] = torch.empty(WIDTH, ROWS, dtype=dtype, device=dev)
+            self.sets[name] = s
+        self.bytes = {name: algorithmic_bytes(ROWS, WIDTH, 4 if name == "f32" else 2) for name in self.sets}
+        self.step_bytes = sum(sum(b.values()) for b in self.bytes.values())
+        self.pack = K.PackKernel()
+        self.dominant = ("f32", "softmax_rows")
+        self.events = []
+
+    def operations(self, name: str, stream: int):
+        """(label, launch closure) for the 13 operations of one element type."""
+        K, s = self.K, self.sets[name]
+        x = s["x"]
+        ops = []
+        for op in ("sum", "mean", "amax", "argmax"):
+            ops.append((f"{op}_rows", lambda op=op: K.launch_reduce(op, x, s[f"{op}_rows"], ROWS, WIDTH, 1, self.device, stream)))
+        ops.append(("softmax_rows", lambda: K.SoftmaxKernel(-1).launch([x], s["softmax_rows"], stream)))
+        ops.append(("layer_norm_rows", lambda: K.LayerNormKernel(1, 1e-5).launch([x, s["gamma"], s["beta"]], s["layer_norm_rows"], stream)))
+        # x.t(): reductions over its last axis are column reductions of x, read in place
+        for op in ("sum", "mean", "amax", "argmax"):
+            ops.append((f"{op}_cols", lambda op=op: K.launch_reduce(op, x, s[f"{op}_cols"], 1, ROWS, WIDTH, self.device, stream)))
+        ops.append(("pack", lambda: self.pack.launch([x.t()], s["pack"], stream)))
+        # softmax / LayerNorm over the view's rows of 32768: pack, then one cluster of CTAs per row
+        ops.append(("softmax_cols", lambda: (self.pack.launch([x.t()], s["pack"], stream),
+                                            K.SoftmaxKernel(-1).launch([s["pack"]], s["softmax_cols"], stream))))
+        ops.append(("layer_norm_cols", lambda: (self.pack.launch([x.t()], s["pack"], stream),
+                                               K.LayerNormKernel(1, 1e-5).launch([s["pack"], s["gamma_t"], s["beta_t"]], s["layer_norm_cols"], stream))))
+        return ops
+
+    def launches_per_step(self) -> int:
+        # every operation is one kernel, except the two pack-then-row-kernel pairs per type
+        return 2 * (13 + 2)
+
+    def run(self, stream: int, time_dominant: bool = False) -> None:
+        torch = self.torch
+        for name in self.sets:
+            for label, launch in self.operations(name, stream):
+                if time_dominant and (name, label) == self.dominant:
+                    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    start.record(torch.cuda.current_stream())
+                    launch()
+                    stop.record(torch.cuda.current_stream())
+                    self.events.append((start, stop))
+                else:
+                    launch()
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: tessiq_b200 has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+
+    from tessiq_b200 import ops
+
+    step = Step(local)
+    stream = torch.cuda.Stream(device=local)
+    raw = stream.cuda_stream
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- value: the captured step, replayed -----------------------------------------------
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step.run(raw)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step.run(raw)
+        for _ in range(2):
+            graph.replay()
+        stream.synchronize()
+    barrier()
+    with ClockSampler(local) as clocks:
+        with torch.cuda.stream(stream):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            for _ in range(args.steps):
+                graph.replay()
+            stop.record(stream)
+            stream.synchronize()
+        # the dominant kernel, timed alone on the launch stream inside eager steps of the same work
+        with torch.cuda.stream(stream):
+            step.events.clear()
+            for _ in range(args.steps):
+                step.run(raw, time_dominant=True)
+            stream.synchronize()
+    seconds = start.elapsed_time(stop) * 1e-3
+    dominant_ms = statistics.mean(a.elapsed_time(b) for a, b in step.events)
+    barrier()
+
+    # ---- per-operation device times (one event pair per operation, eager) ----------------
+    per_op = {}
+    with torch.cuda.stream(stream):
+        for name in step.sets:
+            for label, launch in step.operations(name, raw):
+                launch()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                for _ in range(5):
+                    launch()
+                b.record(stream)
+                stream.synchronize()
+                us = a.elapsed_time(b) / 5 * 1e3
+                per_op[f"{label}_{name}"] = {"us": round(us, 1), "gbs": round(step.bytes[name][label] / us / 1e3, 1)}
+
+    # ---- e2e: host buffers in, host buffers out, through the public API --------------------
+    host_out = {}
+
+    def e2e_step():
+        x = step.host_x.to(f"cuda:{local}", non_blocking=True)
+        results = []
+        for dtype in (torch.float32, torch.bfloat16):
+            xd = x if dtype == torch.float32 else ops.cast(x, dtype)
+            gamma, beta = step.sets["f32" if dtype == torch.float32 else "bf16"]["gamma"], step.sets["f32" if dtype == torch.float32 else "bf16"]["beta"]
+            gamma_t, beta_t = step.sets["f32" if dtype == torch.float32 else "bf16"]["gamma_t"], step.sets["f32" if dtype == torch.float32 else "bf16"]["beta_t"]
+            xt = xd.t()
+            results += [ops.sum(xd, -1), ops.mean(xd, -1), ops.amax(xd, -1), ops.argmax(xd, -1), ops.softmax(xd, -1),
+                        ops.layer_norm(xd, [WIDTH], gamma, beta), ops.sum(xt, -1), ops.mean(xt, -1), ops.amax(xt, -1),
+                        ops.argmax(xt, -1), ops.contiguous(xt), ops.softmax(xt, -1), ops.layer_norm(xt, [ROWS], gamma_t, beta_t)]
+        for i, r in enumerate(results):
+            if i not in host_out:
+                host_out[i] = torch.empty(r.shape, dtype=r.dtype).pin_memory()
+            host_out[i].copy_(r, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_seconds = (time.perf_counter() - t0)
+    barrier()
+    d2h_bytes = sum(t.numel() * t.element_size() for t in host_out.values())
+    h2d_bytes = step.host_x.numel() * 4
+
+    times = torch.tensor([seconds, e2e_seconds, dominant_ms], dtype=torch.float64, device=f"cuda:{local}")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    seconds, e2e_seconds, dominant_ms = times.tolist()
+    clock_summary = clocks.summary()
+
+    peak, peak_kind = peaks()
+    dom_name, dom_label = step.dominant
+    dom_bytes = step.bytes[dom_name][dom_label]
+    achieved = dom_bytes / (dominant_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": round(world * step.step_bytes * args.steps / seconds / 1e9, 1), "unit": UNIT,
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(seconds / args.steps * 1e3, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32+bf16 (f32 accumulate)", "data": "synthetic",
+        "config": {"workload": "config 2: sum/mean/amax/argmax/softmax/LayerNorm over the last axis of x[32768,4096], "
+                               "f32 and bf16, contiguous and on the transposed view, plus the pack alone",
+                   "rows_per_gpu": ROWS, "width": WIDTH, "parallelism": f"rows sharded over {world} GPU(s), no collective",
+                   "l2": "inputs (768 MiB) exceed L2; no flush", "timing": "CUDA-graph replay, CUDA events on the replay stream"},
+        "algorithmic_bytes_per_step": step.step_bytes,
+        "roofline": {"bound": "hbm", "kernel": f"row_cluster_kernel<float, softmax> ({dom_label}_{dom_name})",
+                     "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                     "peak_kind": f"of {peak_kind} copy bandwidth", "traffic": DOMINANT_TRAFFIC_BYTES,
+                     "algorithmic_bytes_per_launch": dom_bytes, "us_per_launch": round(dominant_ms * 1e3, 1)},
+        "e2e": {"value": round(world * step.step_bytes * e2e_steps / e2e_seconds / 1e9, 1), "unit": UNIT,
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "ms_per_step": round(e2e_seconds / e2e_steps * 1e3, 2),
+                "steps": e2e_steps},
+        "gpu_launches": step.launches_per_step() * args.steps,
+        "clocks": clock_summary,
+        "kernels": per_op,
+    }
+    if rank == 0 and world == 1:
+        line["cpu_baseline"] = cpu_baseline(sample_rows=2048, repeats=3)
+    if world > 1:
+        dist.destroy_process_group()
+    return line if rank == 0 else {}
+
+
+def run_profile(args) -> None:
+    """Eager launches of one operation (or all), for a profiler to capture."""
+    import torch
+
+    torch.cuda.set_device(0)
+    if args.profile.startswith("chain1"):
+        # BASELINE config 1 (the fused chain on x[4096,4096] with a bias row), over rotating
+        # buffers so that no launch finds its input in L2. `chain1_precise` selects math precise.
+        from tessiq_b200.kernel import FusedKernel
+
+        mode = "precise" if args.profile.endswith("precise") else "fast"
+        kernel = FusedKernel(f"math {mode}\nin x f32 same\nin b f32 cycled\nv0 = add x b\nv1 = gelu_tanh v0\nv2 = sigmoid x\n"
+                             "v3 = mul v1 v2\nv4 = mul x 0.5\nv5 = sub v3 v4\nout v5 f32\n")
+        xs = [torch.randn(4096, 4096, device="cuda") for _ in range(6)]
+        out = torch.empty(4096, 4096, device="cuda")
+        bias = torch.randn(4096, device="cuda") * 0.02
+        for i in range(args.warmup + args.steps):
+            kernel.launch([xs[i % 6], bias], out, stream=None)
+        torch.cuda.synchronize()
+        return
+    step = Step(0)
+    stream = torch.cuda.Stream(device=0)
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup + args.steps):
+            for name in step.sets:
+                for label, launch in step.operations(name, stream.cuda_stream):
+                    if args.profile == "all" or args.profile == f"{label}_{name}":
+                        launch()
+        stream.synchronize()
+
+
+# Measured once with ncu on the dominant kernel (profiles/softmax_rows_f32.md): DRAM read + write
+# bytes per launch. None until a capture exists.
+DOMINANT_TRAFFIC_BYTES = None
+
+
+# ---------------------------------------------------------------------------------------------
+# The step on the host CPU (the reference's CPU device)
+
+
+def cpu_step(x32, gamma, beta, gamma_t, beta_t):
+    """The 26 operations as the reference's CPU device runs them: one ATen CPU kernel per node."""
+    import torch
+
+    from oracle import tessiq0
+
+    results = []
+    for dtype in (torch.float32, torch.bfloat16):
+        x = x32.to(dtype)
+        xt = x.t()
+        g, b, gt, bt = (t.to(dtype) for t in (gamma, beta, gamma_t, beta_t))
+        for view, width, gg, bb in ((x, x.shape[1], g, b), (xt, x.shape[0], gt, bt)):
+            for op in ("sum", "mean", "amax", "argmax"):
+                results.append(tessiq0.reduce(op, view, -1))
+            results.append(tessiq0.softmax(view, -1))
+            results.append(tessiq0.native_layer_norm(view, [width], gg, bb, 1e-5)[0])
+        results.append(tessiq0.pack(xt))
+    return results
+
+
+def cpu_baseline(sample_rows: int, repeats: int) -> dict:
+    import torch
+
+    g = torch.Generator().manual_seed(1234)
+    x = torch.randn(sample_rows, WIDTH, generator=g)
+    gamma, beta = 1 + torch.randn(WIDTH, generator=g) * 0.02, torch.randn(WIDTH, generator=g) * 0.02
+    gamma_t, beta_t = 1 + torch.randn(sample_rows, generator=g) * 0.02, torch.randn(sample_rows, generator=g) * 0.02
+    nbytes = sum(sum(algorithmic_bytes(sample_rows, WIDTH, size).values()) for size in (4, 2))
+    cpu_step(x, gamma, beta, gamma_t, beta_t)
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        cpu_step(x, gamma, beta, gamma_t, beta_t)
+        times.append(time.perf_counter() - t0)
+    seconds = statistics.median(times)
+    return {"value": round(nbytes / seconds / 1e9, 2), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"the same 26 operations on {sample_rows} of the {ROWS} rows (x[{sample_rows},{WIDTH}]), median of {repeats}; "
+                      "PyTorch CPU kernels called one operator per node, as the reference's tessiq:0 device does",
+            "seconds_per_sample": round(seconds, 3), "host_cpus": os.cpu_count()}
+
+
+def run_reference(args) -> dict:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return {}
+    import torch
+
+    sample_rows = 2048
+    g = torch.Generator().manual_seed(1234)
+    x = torch.randn(sample_rows, WIDTH, generator=g)
+    gamma, beta = 1 + torch.randn(WIDTH, generator=g) * 0.02, torch.randn(WIDTH, generator=g) * 0.02
+    gamma_t, beta_t = 1 + torch.randn(sample_rows, generator=g) * 0.02, torch.randn(sample_rows, generator=g) * 0.02
+    nbytes = sum(sum(algorithmic_bytes(sample_rows, WIDTH, size).values()) for size in (4, 2))
+    for _ in range(max(args.warmup, 1)):
+        cpu_step(x, gamma, beta, gamma_t, beta_t)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(x, gamma, beta, gamma_t, beta_t)
+    seconds = time.perf_counter() - t0
+    value = round(nbytes * args.steps / seconds / 1e9, 2)
+    sample = (f"each step is the 26 operations on {sample_rows} of the {ROWS} rows; PyTorch CPU kernels, one operator per node, "
+              "which is what the reference's CPU device tessiq:0 runs (csrc/tessiq/torch/ops.cpp:367-370)")
+    return {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
+        "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(seconds / args.steps * 1e3, 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32+bf16", "data": "synthetic",
+        "config": {"workload": "config 2 (see the default arm), bounded sample of rows on the host CPU", "rows": sample_rows, "width": WIDTH},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--rows", type=int, default=ROWS, help="rows of x per GPU (default: the config's 32768)")
+    parser.add_argument("--profile", metavar="OP", default=None,
+                        help="for ncu: run only eager launches of OP (e.g. softmax_rows_f32, or `all`), "
+                             "W warm-up + K steps, and print nothing else")
+    args = parser.parse_args()
+    globals()["ROWS"] = args.rows
+    if args.profile:
+        run_profile(args)
+        return
+    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if line:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -4,9 +4,11 @@
 // kernels see the smallest rank that describes the view. Then one of three kernels runs:
 //   copy       the collapsed view is one contiguous run: a device-to-device copy on the stream;
 //   transpose  the destination's fastest axis is strided in the source while another axis has
-//              source stride 1 (a transposed or permuted view): TILE x TILE tiles go through
-//              padded shared memory so that both the HBM reads and the HBM writes are full
-//              128-byte lines; the remaining axes are unravelled once per tile, not per element;
+//              source stride 1 (a transposed or permuted view). Aligned shapes take the
+//              register-block kernel (128-bit loads and stores, no shared memory); others go
+//              through TILE x TILE tiles in padded shared memory. Either way both the HBM reads
+//              and the HBM writes are whole sectors, and the remaining axes are unravelled once
+//              per tile, not per element;
 //   gather     anything else (slices, expanded axes, odd permutations): one thread per element,
 //              32-bit index arithmetic when the element count allows it.
 // The result is what pack_source's kernel writes (csrc/tessiq/codegen/pack.cpp:41-94): element i
@@ -109,6 +111,56 @@ pack_transpose_kernel(const W* __restrict__ src, W* __restrict__ dst, View view,
   }
 }
 
+// Register-block transpose, no shared memory. Each thread loads V vectors of V elements along the
+// source-contiguous axis (a V x V block), transposes the block in registers, and stores V vectors
+// along the destination-contiguous axis. A warp is 8 row-blocks x 4 column-blocks, so every load
+// instruction of a warp reads 4 runs of 8 x 16 bytes and every store writes 8 runs of 4 x 16 bytes:
+// whole 32-byte sectors in both directions. A CTA of 256 threads covers 16V x 16V elements.
+// Needs rows, cols and every stride involved to be multiples of V and 16-byte-aligned bases.
+template <typename W, int V>
+__global__ void __launch_bounds__(256)
+pack_transpose_blocks(const W* __restrict__ src, W* __restrict__ dst, View view, int row_axis,
+                      long long row_tiles, long long col_tiles) {
+  constexpr int kTile = 16 * V;
+  const int last = view.rank - 1;
+  const long long rows = view.sizes[row_axis], cols = view.sizes[last];
+  const long long col_stride = view.strides[last];
+
+  long long tile_id = blockIdx.x;
+  const long long col_tile = tile_id % col_tiles;
+  tile_id /= col_tiles;
+  const long long row_tile = tile_id % row_tiles;
+  long long batch = tile_id / row_tiles;
+  long long src_base = 0, dst_base = 0, dst_stride = cols, row_dst_stride = 0;
+  for (int d = last - 1; d >= 0; --d) {
+    if (d == row_axis) {
+      row_dst_stride = dst_stride;
+    } else {
+      const long long coordinate = batch % view.sizes[d];
+      batch /= view.sizes[d];
+      src_base += coordinate * view.strides[d];
+      dst_base += coordinate * dst_stride;
+    }
+    dst_stride *= view.sizes[d];
+  }
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tr = (lane & 7) + 8 * (warp & 1);
+  const int tc = (lane >> 3) + 4 * (warp >> 1);
+  const long long r0 = row_tile * kTile + tr * V, c0 = col_tile * kTile + tc * V;
+  if (r0 >= rows || c0 >= cols) return;
+  Vec<W, V> block[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) block[i] = load_stream<W, V>(src + src_base + r0 + (c0 + i) * col_stride);
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    Vec<W, V> line;
+#pragma unroll
+    for (int i = 0; i < V; ++i) line.v[i] = block[i].v[j];
+    store_stream<W, V>(dst + dst_base + (r0 + j) * row_dst_stride + c0, line);
+  }
+}
+
 View collapse(int rank, const int64_t* sizes, const int64_t* strides) {
   View v = {};
   for (int d = 0; d < rank; ++d) {
@@ -154,6 +206,27 @@ tq_status run_pack(const View& view, long long total, const void* src, void* dst
       }
     }
     if (row_axis >= 0 && view.sizes[last] >= 16) {
+      constexpr int kV = BYTES == 1 ? 8 : 16 / BYTES;
+      bool blocks_ok = aligned_to(src, 16) && aligned_to(dst, 16) && view.sizes[last] % kV == 0 &&
+                       view.sizes[row_axis] % kV == 0;
+      for (int d = 0; d <= last && blocks_ok; ++d) {
+        if (d != row_axis && view.strides[d] % kV != 0) blocks_ok = false;
+      }
+      if (blocks_ok) {
+        constexpr int kBlockTile = 16 * kV;
+        const long long row_tiles = (view.sizes[row_axis] + kBlockTile - 1) / kBlockTile;
+        const long long col_tiles = (view.sizes[last] + kBlockTile - 1) / kBlockTile;
+        long long batches = 1;
+        for (int d = 0; d < last; ++d) {
+          if (d != row_axis) batches *= view.sizes[d];
+        }
+        const long long blocks = batches * row_tiles * col_tiles;
+        if (blocks <= 0x7fffffffLL) {
+          pack_transpose_blocks<W, kV><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+              source, target, view, row_axis, row_tiles, col_tiles);
+          return check_launch("pack_transpose_blocks");
+        }
+      }
       constexpr int kTile = BYTES >= 4 ? 32 : (BYTES == 2 ? 64 : 128);
       const long long row_tiles = (view.sizes[row_axis] + kTile - 1) / kTile;
       const long long col_tiles = (view.sizes[last] + kTile - 1) / kTile;

@@ -48,6 +48,10 @@ struct SumReducer {
   __device__ static Acc lift(T v, long long) { return static_cast<Acc>(to_compute(v)); }
   __device__ static Acc combine(Acc a, Acc b) { return a + b; }
   __device__ static Acc shuffle(Acc a, int offset) { return shfl_xor(a, offset); }
+  using Local = Acc;
+  __device__ static Local local_identity() { return identity(); }
+  __device__ static void step(Local& local, T v, long long) { local += static_cast<Acc>(to_compute(v)); }
+  __device__ static Acc to_acc(Local local) { return local; }
   __device__ static Out finish(Acc a, long long count, bool mean) {
     if constexpr (!std::is_integral_v<C>) {
       if (mean) a = a / static_cast<Acc>(count);
@@ -72,14 +76,29 @@ struct ExtremeReducer {
   }
   __device__ static Acc lift(T v, long long) { return to_compute(v); }
   __device__ static Acc combine(Acc a, Acc b) {
-    if constexpr (!std::is_integral_v<C>) {
-      if (a != a) return a;
-      if (b != b) return b;
+    if constexpr (std::is_same_v<C, float>) {
+      // One instruction: the NaN-propagating maximum / minimum of PTX.
+      float r;
+      if constexpr (kMax) {
+        asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+      } else {
+        asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+      }
+      return r;
+    } else {
+      if constexpr (!std::is_integral_v<C>) {
+        if (a != a) return a;
+        if (b != b) return b;
+      }
+      if constexpr (kMax) return a > b ? a : b;
+      return a < b ? a : b;
     }
-    if constexpr (kMax) return a > b ? a : b;
-    return a < b ? a : b;
   }
   __device__ static Acc shuffle(Acc a, int offset) { return shfl_xor(a, offset); }
+  using Local = Acc;
+  __device__ static Local local_identity() { return identity(); }
+  __device__ static void step(Local& local, T v, long long) { local = combine(local, to_compute(v)); }
+  __device__ static Acc to_acc(Local local) { return local; }
   __device__ static Out finish(Acc a, long long, bool) { return from_compute<Out, Acc>(a); }
 };
 
@@ -133,7 +152,45 @@ struct ArgmaxReducer {
     b.index = shfl_xor(a.index, offset);
     return b;
   }
-  __device__ static Out finish(Acc a, long long, bool) { return a.index; }
+  // Within one thread the positions only grow, so a strict comparison keeps the first of equal
+  // values and the thread needs no index comparison. The position is kept in 32 bits (the host
+  // declines longer slices). `!(v <= best)` is true for a larger value and for a NaN; the second
+  // test freezes the state once `best` itself is a NaN.
+  struct Local {
+    C best;
+    unsigned index;
+  };
+  static constexpr unsigned kNone = 0xffffffffu;
+  __device__ static Local local_identity() {
+    Local l;
+    l.best = identity().value;
+    l.index = kNone;
+    return l;
+  }
+  __device__ static void step(Local& local, T v, long long index) {
+    const C value = to_compute(v);
+    bool take;
+    if constexpr (std::is_integral_v<C>) {
+      take = value > local.best;
+    } else {
+      take = !(value <= local.best) && (local.best == local.best);
+    }
+    if (take) {
+      local.best = value;
+      local.index = static_cast<unsigned>(index);
+    }
+  }
+  __device__ static Acc to_acc(Local local) {
+    Acc a;
+    a.value = local.best;
+    a.index = local.index == kNone ? std::numeric_limits<long long>::max() : static_cast<long long>(local.index);
+    return a;
+  }
+  // No position was ever taken only if every element equals the identity (-inf, or the lowest
+  // integer): the first of equal values is position 0.
+  __device__ static Out finish(Acc a, long long, bool) {
+    return a.index == std::numeric_limits<long long>::max() ? 0 : a.index;
+  }
 };
 
 // Reads a partial another CTA wrote, from L2 (never a stale L1 line).
@@ -179,7 +236,7 @@ __device__ __forceinline__ typename R::Acc block_reduce(typename R::Acc a, typen
 // streaming loads, and a scalar tail, so that any element-aligned pointer works.
 template <typename T, typename R, int VEC>
 __device__ __forceinline__ void fold_span(const T* __restrict__ row, long long begin, long long end,
-                                          int tid, int threads, typename R::Acc& acc) {
+                                          int tid, int threads, typename R::Local& acc) {
   if (begin >= end) return;
   const T* start = row + begin;
   long long head = 0;
@@ -188,7 +245,7 @@ __device__ __forceinline__ void fold_span(const T* __restrict__ row, long long b
         static_cast<unsigned>(reinterpret_cast<uintptr_t>(start) % (sizeof(T) * VEC)) / sizeof(T);
     head = misaligned ? (VEC - misaligned) : 0;
     if (head > end - begin) head = end - begin;
-    if (tid < head) acc = R::combine(acc, R::lift(start[tid], begin + tid));
+    if (tid < head) R::step(acc, start[tid], begin + tid);
   }
   const long long body = begin + head;
   const long long vectors = (end - body) / VEC;
@@ -206,13 +263,13 @@ __device__ __forceinline__ void fold_span(const T* __restrict__ row, long long b
       if (vi < vectors) {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          acc = R::combine(acc, R::lift(x[u].v[e], body + vi * VEC + e));
+          R::step(acc, x[u].v[e], body + vi * VEC + e);
         }
       }
     }
   }
   const long long tail = body + vectors * VEC + tid;
-  if (tail < end) acc = R::combine(acc, R::lift(row[tail], tail));
+  if (tail < end) R::step(acc, row[tail], tail);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -226,9 +283,9 @@ reduce_warp_per_slice(const T* __restrict__ in, typename R::Out* __restrict__ ou
   const int lane = threadIdx.x & 31;
   const long long slice = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
   if (slice >= outer) return;
-  typename R::Acc acc = R::identity();
-  fold_span<T, R, VEC>(in + slice * reduce, 0, reduce, lane, 32, acc);
-  acc = warp_reduce<R>(acc);
+  typename R::Local local = R::local_identity();
+  fold_span<T, R, VEC>(in + slice * reduce, 0, reduce, lane, 32, local);
+  typename R::Acc acc = warp_reduce<R>(R::to_acc(local));
   if (lane == 0) out[slice] = R::finish(acc, reduce, mean != 0);
 }
 
@@ -253,9 +310,9 @@ reduce_cta_per_slice(const T* __restrict__ in, typename R::Out* __restrict__ out
   long long end = begin + chunk;
   if (end > reduce) end = reduce;
 
-  Acc acc = R::identity();
-  fold_span<T, R, VEC>(in + slice * reduce, begin, end, threadIdx.x, kBlock, acc);
-  acc = block_reduce<R>(acc, warp_scratch);
+  typename R::Local local = R::local_identity();
+  fold_span<T, R, VEC>(in + slice * reduce, begin, end, threadIdx.x, kBlock, local);
+  Acc acc = block_reduce<R>(R::to_acc(local), warp_scratch);
 
   if (cluster > 1) {
     cg::cluster_group group = cg::this_cluster();
@@ -322,9 +379,9 @@ reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long
   long long end = begin + chunk;
   if (end > reduce) end = reduce;
 
-  Acc acc[VEC];
+  typename R::Local local[VEC];
 #pragma unroll
-  for (int e = 0; e < VEC; ++e) acc[e] = R::identity();
+  for (int e = 0; e < VEC; ++e) local[e] = R::local_identity();
 
   if (in_range) {
     const T* base = in + slice * reduce * inner + column;
@@ -340,13 +397,16 @@ reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long
         const long long ri = r + static_cast<long long>(u) * lanes_y;
         if (ri < end) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) acc[e] = R::combine(acc[e], R::lift(x[u].v[e], ri));
+          for (int e = 0; e < VEC; ++e) R::step(local[e], x[u].v[e], ri);
         }
       }
     }
   }
 
   // Across ty, through shared memory, in a fixed order.
+  Acc acc[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) acc[e] = R::to_acc(local[e]);
 #pragma unroll
   for (int e = 0; e < VEC; ++e) rows_scratch[(ty * lanes_x + tx) * VEC + e] = acc[e];
   __syncthreads();
@@ -477,7 +537,7 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
   } else {
     p.shape = Shape::kColumns;
     int vec = vec_bytes_limit / size;
-    if (vec > 4) vec = 4;
+    if (vec > 8) vec = 8;
     if (vec < 1) vec = 1;
     while (vec > 1 && inner % vec != 0) vec /= 2;
     p.vec = vec;
@@ -487,7 +547,8 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
     p.lanes_x = lanes;
     p.column_tiles = (groups + lanes - 1) / lanes;
     const long long base_ctas = p.column_tiles * outer;
-    long long want = (target_ctas + base_ctas - 1) / base_ctas;
+    // Many small CTAs: the hardware then balances the last wave at a fine grain.
+    long long want = (target_ctas * 4 + base_ctas - 1) / base_ctas;
     const long long per_pass = static_cast<long long>(kBlock / lanes) * kUnroll;
     long long most = reduce / per_pass;
     if (most < 1) most = 1;
@@ -582,13 +643,16 @@ tq_status run(const Plan& p, const void* in, void* out, long long outer, long lo
         }
         return check_launch("reduce_columns");
       };
-      constexpr int kColumnVec = kVec > 4 ? 4 : kVec;
+      constexpr int kColumnVec = kVec > 8 ? 8 : kVec;
       if (p.vec == 1) return go(reduce_columns<T, R, 1>, 1);
       if constexpr (kColumnVec >= 2) {
         if (p.vec == 2) return go(reduce_columns<T, R, 2>, 2);
       }
       if constexpr (kColumnVec >= 4) {
         if (p.vec == 4) return go(reduce_columns<T, R, 4>, 4);
+      }
+      if constexpr (kColumnVec >= 8) {
+        if (p.vec == 8) return go(reduce_columns<T, R, 8>, 8);
       }
       return fail(TQ_INTERNAL, "no column kernel for %d elements per thread", p.vec);
     }
@@ -616,6 +680,8 @@ tq_status validate(tq_reduce_op op, tq_dtype dtype, long long outer, long long r
   TQ_REQUIRE(outer >= 0 && reduce >= 0 && inner >= 0, TQ_INVALID_ARGUMENT,
              "negative extent in [%lld, %lld, %lld]", outer, reduce, inner);
   TQ_REQUIRE(reduce > 0, TQ_UNSUPPORTED, "a reduction over no elements has no kernel");
+  TQ_REQUIRE(!(op == TQ_ARGMAX && reduce >= 0xffffffffLL), TQ_UNSUPPORTED,
+             "argmax over %lld elements has no kernel (positions are kept in 32 bits)", reduce);
   TQ_REQUIRE(!(op == TQ_MEAN && (dtype == TQ_I32 || dtype == TQ_I64)), TQ_UNSUPPORTED,
              "mean of an integer tensor has no kernel");
   return TQ_OK;

@@ -56,11 +56,44 @@ template <typename C> __device__ __forceinline__ C math_sqrt(C v);
 template <> __device__ __forceinline__ float math_sqrt<float>(float v) { return sqrtf(v); }
 template <> __device__ __forceinline__ double math_sqrt<double>(double v) { return sqrt(v); }
 
+// NaN-propagating: the row's NaN must reach every element of the result.
 template <typename C> __device__ __forceinline__ C nan_max(C a, C b) {
-  // NaN-propagating: the row's NaN must reach every element of the result.
   if (a != a) return a;
   if (b != b) return b;
   return a > b ? a : b;
+}
+template <> __device__ __forceinline__ float nan_max<float>(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+
+// 2^t by the special-function unit (2 ulp). softmax uses it as exp(x - m) = 2^(x*log2e - m*log2e):
+// the rounding of m*log2e is common to the whole row and cancels in the normalisation.
+__device__ __forceinline__ float exp2_approx(float t) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+  return r;
+}
+
+// Element e of a vector, widened to the arithmetic type. For bf16 the widening is a shift or a
+// mask of the packed 32-bit word, written as volatile asm so that the compiler repeats it in each
+// pass over the row instead of keeping a widened copy of the whole row alive in registers.
+template <typename T, int VEC>
+__device__ __forceinline__ typename Compute<T>::type widen(const Vec<T, VEC>& x, int e) {
+  return to_compute(x.v[e]);
+}
+template <int VEC>
+__device__ __forceinline__ float widen(const Vec<__nv_bfloat16, VEC>& x, int e) {
+  static_assert(VEC % 2 == 0, "bf16 vectors are handled as 32-bit pairs");
+  const uint32_t word = reinterpret_cast<const uint32_t*>(&x)[e >> 1];
+  uint32_t bits;
+  if (e & 1) {
+    asm volatile("and.b32 %0, %1, 0xffff0000;" : "=r"(bits) : "r"(word));
+  } else {
+    asm volatile("shl.b32 %0, %1, 16;" : "=r"(bits) : "r"(word));
+  }
+  return __uint_as_float(bits);
 }
 
 template <typename C, bool kMax> __device__ __forceinline__ C fold(C a, C b) {
@@ -77,7 +110,7 @@ template <typename C, bool kMax> __device__ __forceinline__ C warp_fold(C v) {
 }
 
 // Every thread of the CTA gets the CTA-wide result.
-template <typename C, bool kMax>
+template <typename C, bool kMax, int WARPS = kWarps>
 __device__ __forceinline__ C block_fold(C v, C* warp_scratch) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   v = warp_fold<C, kMax>(v);
@@ -85,16 +118,16 @@ __device__ __forceinline__ C block_fold(C v, C* warp_scratch) {
   __syncthreads();
   C total = warp_scratch[0];
 #pragma unroll
-  for (int w = 1; w < kWarps; ++w) total = fold<C, kMax>(total, warp_scratch[w]);
+  for (int w = 1; w < WARPS; ++w) total = fold<C, kMax>(total, warp_scratch[w]);
   __syncthreads();  // warp_scratch is reused by the next statistic
   return total;
 }
 
 // Every thread of every CTA of the cluster gets the cluster-wide result. `slots` is an array of
 // kMaxCluster values in this CTA's shared memory that no other statistic uses.
-template <typename C, bool kMax>
+template <typename C, bool kMax, int WARPS = kWarps>
 __device__ __forceinline__ C cluster_fold(C v, C* warp_scratch, C* slots, int cluster) {
-  v = block_fold<C, kMax>(v, warp_scratch);
+  v = block_fold<C, kMax, WARPS>(v, warp_scratch);
   if (cluster == 1) return v;
   cg::cluster_group group = cg::this_cluster();
   const unsigned rank = group.block_rank();
@@ -118,43 +151,58 @@ __device__ __forceinline__ void store_stat(void* pointer, long long row, float v
   }
 }
 
-// The arithmetic shared by the register-resident kernels. `v` holds this thread's elements of the
-// row as floats (invalid ones flagged in `valid`); Fold(value, is_max, stage) reduces over the row.
+// The arithmetic shared by the register-resident kernels. `x` holds this thread's vectors of the
+// row exactly as loaded: half-precision rows stay packed (two elements per register) and are
+// widened on the fly in every pass, so a thread keeps twice the bytes in flight per register.
+// `first` + j * `step` is the index of vector j within the row; vectors at or beyond `vectors` do
+// not exist. fold_row(value, is_max, stage) reduces a float over the whole row.
 template <typename T, typename OutT, int VEC, int K, int OP, typename FoldFn>
-__device__ __forceinline__ void finish_row(float (&v)[K][VEC], const bool (&valid)[K],
-                                           const long long (&vector_index)[K], const RowArgs& args,
-                                           long long row, bool writes_stats, FoldFn fold_row) {
+__device__ __forceinline__ void finish_row(Vec<T, VEC> (&x)[K], int first, int step, int vectors,
+                                           const RowArgs& args, long long row, bool writes_stats,
+                                           FoldFn fold_row) {
   OutT* out_row = static_cast<OutT*>(args.out) + row * args.width;
   const float width = static_cast<float>(args.width);
+  constexpr bool kKeepsFloats = sizeof(T) == 4;  // a float row can hold exp(x - max) in place
   if constexpr (OP == kSoftmax) {
     float local = -std::numeric_limits<float>::infinity();
 #pragma unroll
     for (int j = 0; j < K; ++j) {
-      if (valid[j]) {
+      if (first + j * step < vectors) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) local = nan_max(local, v[j][e]);
+        for (int e = 0; e < VEC; ++e) local = nan_max(local, widen(x[j], e));
       }
     }
     const float row_max = fold_row(local, /*is_max=*/true, 0);
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float scaled_max = row_max * kLog2e;
     float sum = 0.f;
 #pragma unroll
     for (int j = 0; j < K; ++j) {
-      if (valid[j]) {
+      if (first + j * step < vectors) {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          v[j][e] = expf(v[j][e] - row_max);
-          sum += v[j][e];
+          const float value = exp2_approx(fmaf(widen(x[j], e), kLog2e, -scaled_max));
+          sum += value;
+          if constexpr (kKeepsFloats) x[j].v[e] = from_compute<T, float>(value);
         }
       }
     }
     const float inverse = 1.f / fold_row(sum, /*is_max=*/false, 1);
 #pragma unroll
     for (int j = 0; j < K; ++j) {
-      if (valid[j]) {
+      if (first + j * step < vectors) {
         Vec<OutT, VEC> y;
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) y.v[e] = from_compute<OutT, float>(v[j][e] * inverse);
-        store_stream<OutT, VEC>(out_row + vector_index[j] * VEC, y);
+        for (int e = 0; e < VEC; ++e) {
+          float value;
+          if constexpr (kKeepsFloats) {
+            value = widen(x[j], e);
+          } else {
+            value = exp2_approx(fmaf(widen(x[j], e), kLog2e, -scaled_max));
+          }
+          y.v[e] = from_compute<OutT, float>(value * inverse);
+        }
+        store_stream<OutT, VEC>(out_row + static_cast<long long>(first + j * step) * VEC, y);
       }
     }
   } else {
@@ -163,9 +211,9 @@ __device__ __forceinline__ void finish_row(float (&v)[K][VEC], const bool (&vali
       float sum = 0.f;
 #pragma unroll
       for (int j = 0; j < K; ++j) {
-        if (valid[j]) {
+        if (first + j * step < vectors) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) sum += v[j][e];
+          for (int e = 0; e < VEC; ++e) sum += widen(x[j], e);
         }
       }
       mean = fold_row(sum, false, 0) / width;
@@ -173,10 +221,10 @@ __device__ __forceinline__ void finish_row(float (&v)[K][VEC], const bool (&vali
     float squares = 0.f;
 #pragma unroll
     for (int j = 0; j < K; ++j) {
-      if (valid[j]) {
+      if (first + j * step < vectors) {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          const float centred = v[j][e] - mean;
+          const float centred = widen(x[j], e) - mean;
           squares += centred * centred;
         }
       }
@@ -191,19 +239,20 @@ __device__ __forceinline__ void finish_row(float (&v)[K][VEC], const bool (&vali
     const T* bias = static_cast<const T*>(args.bias);
 #pragma unroll
     for (int j = 0; j < K; ++j) {
-      if (valid[j]) {
+      if (first + j * step < vectors) {
+        const long long offset = static_cast<long long>(first + j * step) * VEC;
         Vec<T, VEC> w, b;
-        if (weight) w = *reinterpret_cast<const Vec<T, VEC>*>(weight + vector_index[j] * VEC);
-        if (bias) b = *reinterpret_cast<const Vec<T, VEC>*>(bias + vector_index[j] * VEC);
+        if (weight) w = *reinterpret_cast<const Vec<T, VEC>*>(weight + offset);
+        if (bias) b = *reinterpret_cast<const Vec<T, VEC>*>(bias + offset);
         Vec<OutT, VEC> y;
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          float value = (v[j][e] - mean) * rstd;
+          float value = (widen(x[j], e) - mean) * rstd;
           if (weight) value *= to_compute(w.v[e]);
           if (bias) value += to_compute(b.v[e]);
           y.v[e] = from_compute<OutT, float>(value);
         }
-        store_stream<OutT, VEC>(out_row + vector_index[j] * VEC, y);
+        store_stream<OutT, VEC>(out_row + offset, y);
       }
     }
   }
@@ -215,54 +264,41 @@ __global__ void __launch_bounds__(kBlock) row_warp_kernel(RowArgs args) {
   const int lane = threadIdx.x & 31;
   const long long row = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
   if (row >= args.rows) return;
-  const long long vectors = args.width / VEC;
+  const int vectors = static_cast<int>(args.width / VEC);
   const T* in_row = static_cast<const T*>(args.in) + row * args.width;
-  float v[K][VEC];
-  bool valid[K];
-  long long vector_index[K];
+  Vec<T, VEC> x[K];
 #pragma unroll
   for (int j = 0; j < K; ++j) {
-    vector_index[j] = static_cast<long long>(j) * 32 + lane;
-    valid[j] = vector_index[j] < vectors;
-    if (valid[j]) {
-      Vec<T, VEC> x = load_stream<T, VEC>(in_row + vector_index[j] * VEC);
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) v[j][e] = to_compute(x.v[e]);
-    }
+    if (lane + j * 32 < vectors) x[j] = load_stream<T, VEC>(in_row + static_cast<long long>(lane + j * 32) * VEC);
   }
   auto fold_row = [](float value, bool is_max, int) {
     return is_max ? warp_fold<float, true>(value) : warp_fold<float, false>(value);
   };
-  finish_row<T, OutT, VEC, K, OP>(v, valid, vector_index, args, row, lane == 0, fold_row);
+  finish_row<T, OutT, VEC, K, OP>(x, lane, 32, vectors, args, row, lane == 0, fold_row);
 }
 
 // A cluster of `cluster` CTAs per row. blockIdx.x = row * cluster + rank.
-template <typename T, typename OutT, int VEC, int K, int OP>
-__global__ void __launch_bounds__(kBlock) row_cluster_kernel(RowArgs args, int cluster) {
-  __shared__ float warp_scratch[kWarps];
+template <typename T, typename OutT, int VEC, int K, int OP, int THREADS = kBlock>
+__global__ void __launch_bounds__(THREADS) row_cluster_kernel(RowArgs args, int cluster) {
+  __shared__ float warp_scratch[THREADS / 32];
   __shared__ float slots[2][kMaxCluster];
   const long long row = blockIdx.x / cluster;
   const int rank = static_cast<int>(blockIdx.x % cluster);
-  const long long vectors = args.width / VEC;
+  const int vectors = static_cast<int>(args.width / VEC);
   const T* in_row = static_cast<const T*>(args.in) + row * args.width;
-  float v[K][VEC];
-  bool valid[K];
-  long long vector_index[K];
+  const int first = rank * K * THREADS + threadIdx.x;
+  Vec<T, VEC> x[K];
 #pragma unroll
   for (int j = 0; j < K; ++j) {
-    vector_index[j] = (static_cast<long long>(rank) * K + j) * kBlock + threadIdx.x;
-    valid[j] = vector_index[j] < vectors;
-    if (valid[j]) {
-      Vec<T, VEC> x = load_stream<T, VEC>(in_row + vector_index[j] * VEC);
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) v[j][e] = to_compute(x.v[e]);
+    if (first + j * THREADS < vectors) {
+      x[j] = load_stream<T, VEC>(in_row + static_cast<long long>(first + j * THREADS) * VEC);
     }
   }
   auto fold_row = [&](float value, bool is_max, int stage) {
-    return is_max ? cluster_fold<float, true>(value, warp_scratch, slots[stage], cluster)
-                  : cluster_fold<float, false>(value, warp_scratch, slots[stage], cluster);
+    return is_max ? cluster_fold<float, true, THREADS / 32>(value, warp_scratch, slots[stage], cluster)
+                  : cluster_fold<float, false, THREADS / 32>(value, warp_scratch, slots[stage], cluster);
   };
-  finish_row<T, OutT, VEC, K, OP>(v, valid, vector_index, args, row,
+  finish_row<T, OutT, VEC, K, OP>(x, first, THREADS, vectors, args, row,
                                   rank == 0 && threadIdx.x == 0, fold_row);
 }
 
@@ -359,11 +395,11 @@ softmax_columns_kernel(const T* __restrict__ in, OutT* __restrict__ out, long lo
 
 template <typename Kernel>
 tq_status launch_rows(Kernel kernel, long long blocks, int cluster, cudaStream_t stream,
-                      const RowArgs& args, const char* name) {
+                      const RowArgs& args, const char* name, int threads = kBlock) {
   TQ_REQUIRE(blocks <= 0x7fffffffLL, TQ_UNSUPPORTED, "%lld rows are more than a grid holds", args.rows);
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(static_cast<unsigned>(blocks));
-  config.blockDim = dim3(kBlock);
+  config.blockDim = dim3(threads);
   config.stream = stream;
   cudaLaunchAttribute attribute[1];
   attribute[0].id = cudaLaunchAttributeClusterDimension;
@@ -403,8 +439,11 @@ tq_status run_vector(const RowArgs& args, cudaStream_t stream, bool* handled) {
   }
   const long long per_cta = (vectors + cluster - 1) / cluster;
   const long long blocks = args.rows * cluster;
-  if (per_cta <= kBlock) return launch_rows(row_cluster_kernel<T, OutT, VEC, 1, OP>, blocks, cluster, stream, args, "row_cluster_kernel");
-  if (per_cta <= kBlock * 2) return launch_rows(row_cluster_kernel<T, OutT, VEC, 2, OP>, blocks, cluster, stream, args, "row_cluster_kernel");
+  // Few threads holding several vectors each beat many threads holding one: a row then costs
+  // fewer shuffles and barriers per byte, and more rows are in flight per SM.
+  if (per_cta <= 128 * 4) {
+    return launch_rows(row_cluster_kernel<T, OutT, VEC, 4, OP, 128>, blocks, cluster, stream, args, "row_cluster_kernel", 128);
+  }
   if (per_cta <= kBlock * 4) return launch_rows(row_cluster_kernel<T, OutT, VEC, 4, OP>, blocks, cluster, stream, args, "row_cluster_kernel");
   return launch_rows(row_cluster_kernel<T, OutT, VEC, 8, OP>, blocks, cluster, stream, args, "row_cluster_kernel");
 }
