@@ -194,6 +194,13 @@ bool literal(const std::string& text, Cls c, std::string* out) {
 struct Value {
   std::string variable;
   tq_dtype dtype;
+  // A value known only as numerator / denominator: in `math fast` the logistic family
+  // (sigmoid, silu, gelu_tanh, ...) is x / (1 + 2^t), and a product of such values needs one
+  // reciprocal, not one per factor. The division is written out when something other than a
+  // multiplication consumes the value.
+  bool lazy = false;
+  std::string numerator;
+  std::string denominator;
 };
 
 tq_dtype promote(tq_dtype a, tq_dtype b) {
@@ -227,7 +234,7 @@ const std::map<std::string, UnaryMath>& unary_math() {
   static const std::map<std::string, UnaryMath> table = {
       {"sqrt", {"sqrtf($0)", nullptr, "sqrt($0)"}},
       {"tanh", {"tanhf($0)", nullptr, "tanh($0)"}},
-      {"exp", {"expf($0)", "__expf($0)", "exp($0)"}},
+      {"exp", {"expf($0)", "tq_exp_fast($0)", "exp($0)"}},
       {"expm1", {"expm1f($0)", nullptr, "expm1($0)"}},
       {"log", {"logf($0)", nullptr, "log($0)"}},
       {"log1p", {"log1pf($0)", nullptr, "log1p($0)"}},
@@ -249,14 +256,33 @@ const std::map<std::string, UnaryMath>& unary_math() {
       {"round", {"rintf($0)", nullptr, "rint($0)"}},
       {"erf", {"erff($0)", nullptr, "erf($0)"}},
       {"erfc", {"erfcf($0)", nullptr, "erfc($0)"}},
-      {"sigmoid", {"(1.0f / (1.0f + expf(-$0)))", "__fdividef(1.0f, 1.0f + __expf(-$0))", "(1.0 / (1.0 + exp(-$0)))"}},
+      {"sigmoid", {"(1.0f / (1.0f + expf(-$0)))", nullptr, "(1.0 / (1.0 + exp(-$0)))"}},
       {"gelu", {"(0.5f * $0 * (1.0f + erff($0 * 0.70710678118654752440f)))", nullptr,
                 "(0.5 * $0 * (1.0 + erf($0 * 0.70710678118654752440)))"}},
-      {"gelu_tanh", {"tq_gelu_tanh_precise($0)", "tq_gelu_tanh_fast($0)", "tq_gelu_tanh_precise($0)"}},
-      {"silu", {"($0 / (1.0f + expf(-$0)))", "__fdividef($0, 1.0f + __expf(-$0))", "($0 / (1.0 + exp(-$0)))"}},
+      {"gelu_tanh", {"tq_gelu_tanh_precise($0)", nullptr, "tq_gelu_tanh_precise($0)"}},
+      {"silu", {"($0 / (1.0f + expf(-$0)))", nullptr, "($0 / (1.0 + exp(-$0)))"}},
       // csrc/custom_ops/fast_gelu/fast_gelu.cpp:23
-      {"fast_gelu", {"($0 * (1.0f / (1.0f + expf(-1.702f * $0))))", "__fdividef($0, 1.0f + __expf(-1.702f * $0))",
+      {"fast_gelu", {"($0 * (1.0f / (1.0f + expf(-1.702f * $0))))", nullptr,
                      "($0 * (1.0 / (1.0 + exp(-1.702 * $0))))"}},
+  };
+  return table;
+}
+
+// `math fast`, f32: the logistic family as numerator / denominator, the denominator being
+// 1 + 2^t with t a polynomial of the argument (log2(e) folded into its constants), evaluated with
+// ex2.approx.ftz. 0.5 (1 + tanh u) = 1 / (1 + exp(-2u)) turns gelu_tanh into the same form with no
+// cancellation in the negative tail.
+struct Quotient {
+  const char* numerator;
+  const char* denominator;
+};
+const std::map<std::string, Quotient>& fast_quotients() {
+  static const std::map<std::string, Quotient> table = {
+      {"sigmoid", {"1.0f", "(1.0f + tq_exp2_ftz(-1.4426950408889634f * $0))"}},
+      {"silu", {"$0", "(1.0f + tq_exp2_ftz(-1.4426950408889634f * $0))"}},
+      {"fast_gelu", {"$0", "(1.0f + tq_exp2_ftz(-2.4554669595930156f * $0))"}},
+      // -2 sqrt(2/pi) log2(e) = -2.302208198144325
+      {"gelu_tanh", {"$0", "(1.0f + tq_exp2_ftz(-2.302208198144325f * ($0 + 0.044715f * $0 * $0 * $0)))"}},
   };
   return table;
 }
@@ -265,6 +291,23 @@ class Selector {
  public:
   tq_status parse(const char* text, Program* program) {
     program_ = program;
+    {
+      // How often each name is read: a value read once, by a multiplication, can stay a quotient.
+      std::istringstream all(text);
+      std::string raw_line;
+      while (std::getline(all, raw_line)) {
+        const size_t comment = raw_line.find('#');
+        if (comment != std::string::npos) raw_line.resize(comment);
+        std::istringstream words(raw_line);
+        std::vector<std::string> t;
+        for (std::string w; words >> w;) t.push_back(w);
+        if (t.size() >= 3 && t[1] == "=") {
+          for (size_t i = 3; i < t.size(); ++i) ++uses_[t[i]];
+        } else if (t.size() == 3 && t[0] == "out") {
+          uses_[t[1]] += 2;  // stored: must be a plain value
+        }
+      }
+    }
     std::istringstream lines(text);
     std::string line;
     int number = 0;
@@ -342,6 +385,7 @@ class Selector {
     auto it = values_.find(t[1]);
     TQ_REQUIRE(it != values_.end(), TQ_INVALID_ARGUMENT, "line %d: `%s` is not defined", number, t[1].c_str());
     TQ_REQUIRE(parse_dtype(t[2], &program_->out_dtype), TQ_INVALID_ARGUMENT, "line %d: unknown dtype `%s`", number, t[2].c_str());
+    materialize(it->second);
     TQ_REQUIRE(cls_of(it->second.dtype) == cls_of(program_->out_dtype), TQ_INVALID_ARGUMENT,
                "line %d: a %s value cannot be stored as %s without a cast", number,
                dtype_name(it->second.dtype), dtype_name(program_->out_dtype));
@@ -364,6 +408,7 @@ class Selector {
     for (const std::string& a : raw) {
       auto it = values_.find(a);
       if (it != values_.end()) {
+        materialize(it->second);
         expr->push_back(it->second.variable);
         dtypes->push_back(it->second.dtype);
         is_value->push_back(true);
@@ -388,6 +433,7 @@ class Selector {
       TQ_REQUIRE(parse_dtype(raw[1], &to), TQ_INVALID_ARGUMENT, "line %d: unknown dtype `%s`", number, raw[1].c_str());
       auto it = values_.find(raw[0]);
       TQ_REQUIRE(it != values_.end(), TQ_INVALID_ARGUMENT, "line %d: `%s` is not defined", number, raw[0].c_str());
+      materialize(it->second);
       const Cls from = cls_of(it->second.dtype), target = cls_of(to);
       std::string e = it->second.variable;
       if (target == Cls::kBool) {
@@ -398,6 +444,12 @@ class Selector {
         if (to == TQ_F16 && it->second.dtype != TQ_F16) e = "tq_round_f16(" + e + ")";
       }
       return emit(result, to, e, number);
+    }
+
+    if (program_->fast) {
+      bool handled = false;
+      if (tq_status s = fast_quotient_step(result, op, raw, number, &handled)) return s;
+      if (handled) return TQ_OK;
     }
 
     std::vector<std::string> expr;
@@ -522,7 +574,6 @@ class Selector {
         // csrc/custom_ops/swiglu/swiglu.cpp:22
         if (!is_float(cls)) return no_kernel();
         const char* pattern = cls == Cls::kF64 ? "($0 / (1.0 + exp(-$0)) * $1)"
-                              : program_->fast ? "(__fdividef($0, 1.0f + __expf(-$0)) * $1)"
                                                : "($0 / (1.0f + expf(-$0)) * $1)";
         return emit(result, d, substitute(pattern, expr), number);
       }
@@ -541,6 +592,71 @@ class Selector {
     return fail(TQ_UNSUPPORTED, "line %d: no operation `%s` of %zu arguments", number, op.c_str(), expr.size());
   }
 
+  // Writes numerator * (1 / denominator) for a value kept as a quotient, once.
+  void materialize(Value& value) {
+    if (!value.lazy) return;
+    program_->body += "  const float " + value.variable + " = " + value.numerator + " * tq_rcp_ftz(" + value.denominator + ");\n";
+    value.lazy = false;
+  }
+
+  // In `math fast`: a member of the logistic family becomes a quotient, and a multiplication with
+  // a quotient operand multiplies numerators and denominators. Only f32-class values take part.
+  tq_status fast_quotient_step(const std::string& result, const std::string& op, const std::vector<std::string>& raw,
+                               int number, bool* handled) {
+    *handled = false;
+    auto float_value = [&](const std::string& name) -> Value* {
+      auto it = values_.find(name);
+      if (it == values_.end() || cls_of(it->second.dtype) != Cls::kF32) return nullptr;
+      return &it->second;
+    };
+    auto quotient = fast_quotients().find(op);
+    if (quotient != fast_quotients().end() && raw.size() == 1) {
+      Value* x = float_value(raw[0]);
+      if (x == nullptr) return TQ_OK;
+      materialize(*x);
+      return define_quotient(result, x->dtype, substitute(quotient->second.numerator, {x->variable}),
+                             substitute(quotient->second.denominator, {x->variable}), number, handled);
+    }
+    if (op == "swiglu" && raw.size() == 2) {  // gate / (1 + exp(-gate)) * up
+      Value* gate = float_value(raw[0]);
+      Value* up = float_value(raw[1]);
+      if (gate == nullptr || up == nullptr) return TQ_OK;
+      materialize(*gate);
+      materialize(*up);
+      return define_quotient(result, promote(gate->dtype, up->dtype), "(" + gate->variable + " * " + up->variable + ")",
+                             "(1.0f + tq_exp2_ftz(-1.4426950408889634f * " + gate->variable + "))", number, handled);
+    }
+    if (op == "mul" && raw.size() == 2) {
+      Value* a = float_value(raw[0]);
+      Value* b = float_value(raw[1]);
+      if (a == nullptr || b == nullptr || (!a->lazy && !b->lazy)) return TQ_OK;
+      const std::string numerator = "(" + (a->lazy ? a->numerator : a->variable) + " * " + (b->lazy ? b->numerator : b->variable) + ")";
+      const std::string denominator = a->lazy && b->lazy ? "(" + a->denominator + " * " + b->denominator + ")"
+                                      : a->lazy          ? a->denominator
+                                                         : b->denominator;
+      const tq_dtype dtype = promote(a->dtype, b->dtype);
+      // The operands were read exactly once (that is why they are still quotients): consumed here.
+      a->lazy = b->lazy = false;
+      return define_quotient(result, dtype, numerator, denominator, number, handled);
+    }
+    return TQ_OK;
+  }
+
+  tq_status define_quotient(const std::string& name, tq_dtype dtype, const std::string& numerator,
+                            const std::string& denominator, int number, bool* handled) {
+    if (tq_status s = define(name, dtype, number)) return s;
+    Value& value = values_[name];
+    // Name both halves so that they are computed once wherever the division ends up.
+    program_->body += "  const float v_" + name + "_n = " + numerator + ";\n";
+    program_->body += "  const float v_" + name + "_d = " + denominator + ";\n";
+    value.lazy = true;
+    value.numerator = "v_" + name + "_n";
+    value.denominator = "v_" + name + "_d";
+    if (uses_[name] != 1) materialize(value);  // read more than once, stored, or never: a plain value
+    *handled = true;
+    return TQ_OK;
+  }
+
   tq_status emit(const std::string& name, tq_dtype dtype, const std::string& expression, int number) {
     if (tq_status s = define(name, dtype, number)) return s;
     program_->body += std::string("  const ") + ctype(cls_of(dtype)) + " v_" + name + " = " + expression + ";\n";
@@ -549,6 +665,7 @@ class Selector {
 
   Program* program_ = nullptr;
   std::map<std::string, Value> values_;
+  std::map<std::string, int> uses_;
 };
 
 // ---------------------------------------------------------------------------------------------

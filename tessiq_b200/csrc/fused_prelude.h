@@ -91,12 +91,18 @@ TQ_DEV float tq_gelu_tanh_precise(float x) {
   const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
   return 0.5f * x * (1.0f + tanhf(inner));
 }
-// The same value through 0.5 (1 + tanh u) = 1 / (1 + exp(-2u)): one exponential, one division,
-// and no cancellation in the negative tail.
-TQ_DEV float tq_gelu_tanh_fast(float x) {
-  const float minus_two_u = -1.5957691216057308f * (x + 0.044715f * x * x * x);
-  return __fdividef(x, 1.0f + __expf(minus_two_u));
+// Hardware approximations with denormals flushed: one special-function instruction each, 2 ulp.
+TQ_DEV float tq_exp2_ftz(float t) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+  return r;
 }
+TQ_DEV float tq_rcp_ftz(float d) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+  return r;
+}
+TQ_DEV float tq_exp_fast(float x) { return tq_exp2_ftz(x * 1.4426950408889634f); }
 TQ_DEV double tq_gelu_tanh_precise(double x) {
   const double inner = 0.7978845608028654 * (x + 0.044715 * x * x * x);
   return 0.5 * x * (1.0 + tanh(inner));

@@ -17,6 +17,7 @@
 // host device.
 #include <cooperative_groups.h>
 
+#include <cstdlib>
 #include <limits>
 #include <type_traits>
 
@@ -30,6 +31,7 @@ namespace {
 constexpr int kBlock = 256;
 constexpr int kWarps = kBlock / 32;
 constexpr int kUnroll = 4;
+constexpr int kColumnUnroll = 4;  // rows in flight per thread in the columns kernel
 constexpr int kMaxCluster = 8;
 
 // ---------------------------------------------------------------------------------------------
@@ -48,10 +50,14 @@ struct SumReducer {
   __device__ static Acc lift(T v, long long) { return static_cast<Acc>(to_compute(v)); }
   __device__ static Acc combine(Acc a, Acc b) { return a + b; }
   __device__ static Acc shuffle(Acc a, int offset) { return shfl_xor(a, offset); }
-  using Local = Acc;
-  __device__ static Local local_identity() { return identity(); }
-  __device__ static void step(Local& local, T v, long long) { local += static_cast<Acc>(to_compute(v)); }
-  __device__ static Acc to_acc(Local local) { return local; }
+  template <int VEC> using Local = Acc;
+  template <int VEC> __device__ static Acc local_identity() { return identity(); }
+  template <int VEC> __device__ static void step(Acc& local, T v, long long) { local += static_cast<Acc>(to_compute(v)); }
+  template <int VEC> __device__ static void step_vector(Acc& local, const Vec<T, VEC>& x, long long) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) local += static_cast<Acc>(to_compute(x.v[e]));
+  }
+  template <int VEC> __device__ static Acc to_acc(Acc local) { return local; }
   __device__ static Out finish(Acc a, long long count, bool mean) {
     if constexpr (!std::is_integral_v<C>) {
       if (mean) a = a / static_cast<Acc>(count);
@@ -95,10 +101,14 @@ struct ExtremeReducer {
     }
   }
   __device__ static Acc shuffle(Acc a, int offset) { return shfl_xor(a, offset); }
-  using Local = Acc;
-  __device__ static Local local_identity() { return identity(); }
-  __device__ static void step(Local& local, T v, long long) { local = combine(local, to_compute(v)); }
-  __device__ static Acc to_acc(Local local) { return local; }
+  template <int VEC> using Local = Acc;
+  template <int VEC> __device__ static Acc local_identity() { return identity(); }
+  template <int VEC> __device__ static void step(Acc& local, T v, long long) { local = combine(local, to_compute(v)); }
+  template <int VEC> __device__ static void step_vector(Acc& local, const Vec<T, VEC>& x, long long) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) local = combine(local, to_compute(x.v[e]));
+  }
+  template <int VEC> __device__ static Acc to_acc(Acc local) { return local; }
   __device__ static Out finish(Acc a, long long, bool) { return from_compute<Out, Acc>(a); }
 };
 
@@ -153,37 +163,85 @@ struct ArgmaxReducer {
     return b;
   }
   // Within one thread the positions only grow, so a strict comparison keeps the first of equal
-  // values and the thread needs no index comparison. The position is kept in 32 bits (the host
-  // declines longer slices). `!(v <= best)` is true for a larger value and for a NaN; the second
-  // test freezes the state once `best` itself is a NaN.
+  // values and the thread needs no index comparison. A thread looks at one vector at a time: the
+  // vector's NaN-propagating maximum (packed two-at-a-time for the half types) is compared with
+  // the best so far, and a vector that beats it is kept whole together with its position; which
+  // element of the kept vector won is resolved once, at the end. Positions are kept in 32 bits
+  // (the host declines longer slices). `!(m <= best)` is true for a larger value and for a NaN;
+  // the second test freezes the state once `best` itself is a NaN.
+  template <int VEC>
   struct Local {
     C best;
-    unsigned index;
+    unsigned base;
+    Vec<T, VEC> winner;
   };
   static constexpr unsigned kNone = 0xffffffffu;
-  __device__ static Local local_identity() {
-    Local l;
+  template <int VEC> __device__ static Local<VEC> local_identity() {
+    Local<VEC> l;
     l.best = identity().value;
-    l.index = kNone;
+    l.base = kNone;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) l.winner.v[e] = T();
     return l;
   }
-  __device__ static void step(Local& local, T v, long long index) {
-    const C value = to_compute(v);
-    bool take;
+  __device__ static bool beats(C value, C best) {
     if constexpr (std::is_integral_v<C>) {
-      take = value > local.best;
+      return value > best;
     } else {
-      take = !(value <= local.best) && (local.best == local.best);
-    }
-    if (take) {
-      local.best = value;
-      local.index = static_cast<unsigned>(index);
+      return !(value <= best) && (best == best);
     }
   }
-  __device__ static Acc to_acc(Local local) {
+  template <int VEC> __device__ static void step(Local<VEC>& local, T v, long long index) {
+    const C value = to_compute(v);
+    if (beats(value, local.best)) {
+      local.best = value;
+      local.base = static_cast<unsigned>(index);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) local.winner.v[e] = v;
+    }
+  }
+  template <int VEC> __device__ static C vector_max(const Vec<T, VEC>& x) {
+    if constexpr (std::is_same_v<T, __nv_bfloat16> && VEC % 2 == 0) {
+      const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&x);
+      __nv_bfloat162 m = pairs[0];
+#pragma unroll
+      for (int i = 1; i < VEC / 2; ++i) m = __hmax2_nan(m, pairs[i]);
+      return ExtremeReducer<float, true>::combine(__low2float(m), __high2float(m));
+    } else if constexpr (std::is_same_v<T, __half> && VEC % 2 == 0) {
+      const __half2* pairs = reinterpret_cast<const __half2*>(&x);
+      __half2 m = pairs[0];
+#pragma unroll
+      for (int i = 1; i < VEC / 2; ++i) m = __hmax2_nan(m, pairs[i]);
+      return ExtremeReducer<float, true>::combine(__low2float(m), __high2float(m));
+    } else {
+      C m = to_compute(x.v[0]);
+#pragma unroll
+      for (int e = 1; e < VEC; ++e) m = ExtremeReducer<C, true>::combine(m, to_compute(x.v[e]));
+      return m;
+    }
+  }
+  template <int VEC> __device__ static void step_vector(Local<VEC>& local, const Vec<T, VEC>& x, long long index) {
+    const C m = vector_max<VEC>(x);
+    if (beats(m, local.best)) {
+      local.best = m;
+      local.base = static_cast<unsigned>(index);
+      local.winner = x;
+    }
+  }
+  template <int VEC> __device__ static Acc to_acc(const Local<VEC>& local) {
     Acc a;
     a.value = local.best;
-    a.index = local.index == kNone ? std::numeric_limits<long long>::max() : static_cast<long long>(local.index);
+    a.index = std::numeric_limits<long long>::max();
+    if (local.base != kNone) {
+      int offset = 0;
+#pragma unroll
+      for (int e = VEC - 1; e >= 0; --e) {
+        const C w = to_compute(local.winner.v[e]);
+        const bool same = (w == local.best) || (w != w && local.best != local.best);
+        if (same) offset = e;
+      }
+      a.index = static_cast<long long>(local.base) + offset;
+    }
     return a;
   }
   // No position was ever taken only if every element equals the identity (-inf, or the lowest
@@ -236,7 +294,7 @@ __device__ __forceinline__ typename R::Acc block_reduce(typename R::Acc a, typen
 // streaming loads, and a scalar tail, so that any element-aligned pointer works.
 template <typename T, typename R, int VEC>
 __device__ __forceinline__ void fold_span(const T* __restrict__ row, long long begin, long long end,
-                                          int tid, int threads, typename R::Local& acc) {
+                                          int tid, int threads, typename R::template Local<VEC>& acc) {
   if (begin >= end) return;
   const T* start = row + begin;
   long long head = 0;
@@ -245,7 +303,7 @@ __device__ __forceinline__ void fold_span(const T* __restrict__ row, long long b
         static_cast<unsigned>(reinterpret_cast<uintptr_t>(start) % (sizeof(T) * VEC)) / sizeof(T);
     head = misaligned ? (VEC - misaligned) : 0;
     if (head > end - begin) head = end - begin;
-    if (tid < head) R::step(acc, start[tid], begin + tid);
+    if (tid < head) R::template step<VEC>(acc, start[tid], begin + tid);
   }
   const long long body = begin + head;
   const long long vectors = (end - body) / VEC;
@@ -260,16 +318,11 @@ __device__ __forceinline__ void fold_span(const T* __restrict__ row, long long b
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const long long vi = v + static_cast<long long>(u) * threads;
-      if (vi < vectors) {
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          R::step(acc, x[u].v[e], body + vi * VEC + e);
-        }
-      }
+      if (vi < vectors) R::template step_vector<VEC>(acc, x[u], body + vi * VEC);
     }
   }
   const long long tail = body + vectors * VEC + tid;
-  if (tail < end) R::step(acc, row[tail], tail);
+  if (tail < end) R::template step<VEC>(acc, row[tail], tail);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -283,9 +336,9 @@ reduce_warp_per_slice(const T* __restrict__ in, typename R::Out* __restrict__ ou
   const int lane = threadIdx.x & 31;
   const long long slice = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
   if (slice >= outer) return;
-  typename R::Local local = R::local_identity();
+  typename R::template Local<VEC> local = R::template local_identity<VEC>();
   fold_span<T, R, VEC>(in + slice * reduce, 0, reduce, lane, 32, local);
-  typename R::Acc acc = warp_reduce<R>(R::to_acc(local));
+  typename R::Acc acc = warp_reduce<R>(R::template to_acc<VEC>(local));
   if (lane == 0) out[slice] = R::finish(acc, reduce, mean != 0);
 }
 
@@ -310,9 +363,9 @@ reduce_cta_per_slice(const T* __restrict__ in, typename R::Out* __restrict__ out
   long long end = begin + chunk;
   if (end > reduce) end = reduce;
 
-  typename R::Local local = R::local_identity();
+  typename R::template Local<VEC> local = R::template local_identity<VEC>();
   fold_span<T, R, VEC>(in + slice * reduce, begin, end, threadIdx.x, kBlock, local);
-  Acc acc = block_reduce<R>(R::to_acc(local), warp_scratch);
+  Acc acc = block_reduce<R>(R::template to_acc<VEC>(local), warp_scratch);
 
   if (cluster > 1) {
     cg::cluster_group group = cg::this_cluster();
@@ -356,14 +409,14 @@ reduce_cta_per_slice(const T* __restrict__ in, typename R::Out* __restrict__ out
 // ty = threadIdx.x / lanes_x along reduce. grid = (column tiles, split, outer); the cluster, when
 // there is one, runs along grid.y.
 template <typename T, typename R, int VEC>
-__global__ void __launch_bounds__(kBlock)
+__global__ void __launch_bounds__(kBlock, sizeof(typename R::Acc) > 8 ? 4 : 5)
 reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long long reduce,
                long long inner, int lanes_x, int split, int cluster, int mean,
                typename R::Acc* __restrict__ partials, unsigned* __restrict__ tickets) {
   using Acc = typename R::Acc;
   extern __shared__ __align__(16) unsigned char dynamic_smem[];
   Acc* rows_scratch = reinterpret_cast<Acc*>(dynamic_smem);              // [kBlock * VEC]
-  Acc* cluster_scratch = rows_scratch + kBlock * VEC;                    // [cluster * lanes_x * VEC]
+  Acc* cluster_scratch = rows_scratch + kBlock * VEC;                    // [lanes_x * VEC]
   __shared__ bool is_last;
 
   const int tx = threadIdx.x % lanes_x;
@@ -379,25 +432,25 @@ reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long
   long long end = begin + chunk;
   if (end > reduce) end = reduce;
 
-  typename R::Local local[VEC];
+  typename R::template Local<1> local[VEC];
 #pragma unroll
-  for (int e = 0; e < VEC; ++e) local[e] = R::local_identity();
+  for (int e = 0; e < VEC; ++e) local[e] = R::template local_identity<1>();
 
   if (in_range) {
     const T* base = in + slice * reduce * inner + column;
-    for (long long r = begin + ty; r < end; r += static_cast<long long>(lanes_y) * kUnroll) {
-      Vec<T, VEC> x[kUnroll];
+    for (long long r = begin + ty; r < end; r += static_cast<long long>(lanes_y) * kColumnUnroll) {
+      Vec<T, VEC> x[kColumnUnroll];
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
+      for (int u = 0; u < kColumnUnroll; ++u) {
         const long long ri = r + static_cast<long long>(u) * lanes_y;
         if (ri < end) x[u] = load_stream<T, VEC>(base + ri * inner);
       }
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
+      for (int u = 0; u < kColumnUnroll; ++u) {
         const long long ri = r + static_cast<long long>(u) * lanes_y;
         if (ri < end) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) R::step(local[e], x[u].v[e], ri);
+          for (int e = 0; e < VEC; ++e) R::template step<1>(local[e], x[u].v[e], ri);
         }
       }
     }
@@ -406,7 +459,7 @@ reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long
   // Across ty, through shared memory, in a fixed order.
   Acc acc[VEC];
 #pragma unroll
-  for (int e = 0; e < VEC; ++e) acc[e] = R::to_acc(local[e]);
+  for (int e = 0; e < VEC; ++e) acc[e] = R::template to_acc<1>(local[e]);
 #pragma unroll
   for (int e = 0; e < VEC; ++e) rows_scratch[(ty * lanes_x + tx) * VEC + e] = acc[e];
   __syncthreads();
@@ -420,63 +473,82 @@ reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long
     }
   }
 
+  // Across the CTAs of the cluster: a reduce-scatter through distributed shared memory. The
+  // tile's `items` accumulators are cut into `cluster` equal slices; every CTA sends slice q of
+  // its accumulators to CTA q, one cluster barrier, and CTA q folds what it received in rank
+  // order. Each CTA then owns items [rank * slice_items, (rank + 1) * slice_items) of the tile.
   const int items = lanes_x * VEC;
-  if (cluster > 1) {
-    cg::cluster_group group = cg::this_cluster();
-    const unsigned rank = group.block_rank();
-    if (holder) {
-      Acc* leader = group.map_shared_rank(cluster_scratch, 0);
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) leader[rank * items + tx * VEC + e] = acc[e];
-    }
-    group.sync();
-    if (rank != 0) return;
-    if (holder) {
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) acc[e] = cluster_scratch[tx * VEC + e];
-      for (int j = 1; j < cluster; ++j) {
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          acc[e] = R::combine(acc[e], cluster_scratch[j * items + tx * VEC + e]);
-        }
-      }
-    }
-  }
-
-  const int clusters = split / cluster;
+  const int slice_items = items / cluster;  // a multiple of VEC: cluster <= lanes_x, both powers of 2
+  unsigned rank = 0;
   typename R::Out* out_row = out + slice * inner;
-  if (clusters == 1) {
-    if (holder && in_range) {
-#pragma unroll
-      for (int e = 0; e < VEC; ++e) out_row[column + e] = R::finish(acc[e], reduce, mean != 0);
-    }
-    return;
-  }
-
+  const long long tile_column = static_cast<long long>(blockIdx.x) * items;
+  const int clusters = split / cluster;
   const long long tile = slice * gridDim.x + blockIdx.x;
   Acc* tile_partials = partials + tile * clusters * items;
-  if (holder) {
+
+  if (cluster > 1) {
+    cg::cluster_group group = cg::this_cluster();
+    rank = group.block_rank();
+    if (holder) {
+      const int item = tx * VEC;
+      Acc* owner = group.map_shared_rank(cluster_scratch, item / slice_items);
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) tile_partials[(part / cluster) * items + tx * VEC + e] = acc[e];
+      for (int e = 0; e < VEC; ++e) owner[rank * slice_items + item % slice_items + e] = acc[e];
+    }
+    group.sync();
+    // Thread t < slice_items now finishes item rank * slice_items + t.
+    if (threadIdx.x < slice_items) {
+      Acc total = cluster_scratch[threadIdx.x];
+      for (int j = 1; j < cluster; ++j) total = R::combine(total, cluster_scratch[j * slice_items + threadIdx.x]);
+      const int item = rank * slice_items + threadIdx.x;
+      if (clusters == 1) {
+        if (tile_column + item < inner) out_row[tile_column + item] = R::finish(total, reduce, mean != 0);
+      } else {
+        tile_partials[(part / cluster) * items + item] = total;
+      }
+    }
+    if (clusters == 1) return;
+  } else {
+    if (clusters == 1) {
+      if (holder && in_range) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) out_row[column + e] = R::finish(acc[e], reduce, mean != 0);
+      }
+      return;
+    }
+    if (holder) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) tile_partials[part * items + tx * VEC + e] = acc[e];
+    }
   }
+
+  // Across clusters: every CTA has written its share of its cluster's partial; the last CTA of
+  // the tile to take a ticket folds the `clusters` partials of every item, all threads at work,
+  // eight loads in flight each, in a fixed order.
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
     const unsigned ticket = atomicAdd(&tickets[tile], 1u);
-    is_last = ticket == static_cast<unsigned>(clusters - 1);
+    is_last = ticket == static_cast<unsigned>(split - 1);
   }
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  if (holder && in_range) {
+  for (int item = threadIdx.x; item < items; item += kBlock) {
+    if (tile_column + item >= inner) continue;
+    Acc total = R::identity();
+    for (int j = 0; j < clusters; j += 8) {
+      Acc batch[8];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      Acc total = R::identity();
-      for (int j = 0; j < clusters; ++j) {
-        total = R::combine(total, load_partial(tile_partials + j * items + tx * VEC + e));
+      for (int u = 0; u < 8; ++u) {
+        if (j + u < clusters) batch[u] = load_partial(tile_partials + static_cast<long long>(j + u) * items + item);
       }
-      out_row[column + e] = R::finish(total, reduce, mean != 0);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (j + u < clusters) total = R::combine(total, batch[u]);
+      }
     }
+    out_row[tile_column + item] = R::finish(total, reduce, mean != 0);
   }
 }
 
@@ -540,27 +612,37 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
     if (vec > 8) vec = 8;
     if (vec < 1) vec = 1;
     while (vec > 1 && inner % vec != 0) vec /= 2;
+    if (op == TQ_ARGMAX && vec > 4) vec = 4;  // its accumulators are 16 bytes each
     p.vec = vec;
     long long groups = (inner + vec - 1) / vec;
+    // A warp reads 32 vectors (512 bytes) of one row; the CTA's 8 warps read 8 consecutive rows.
     int lanes = 32;
+    if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_LANES")) {  // tuning override: 1..256, a power of two
+      const int value = std::atoi(forced);
+      if (value >= 1 && value <= kBlock && (value & (value - 1)) == 0) lanes = value;
+    }
     while (lanes > 1 && lanes / 2 >= groups) lanes /= 2;
     p.lanes_x = lanes;
     p.column_tiles = (groups + lanes - 1) / lanes;
     const long long base_ctas = p.column_tiles * outer;
-    // Many small CTAs: the hardware then balances the last wave at a fine grain.
+    // Several waves of small CTAs: measured faster than one wave of large ones, because the
+    // hardware then evens out the tail at a fine grain.
     long long want = (target_ctas * 4 + base_ctas - 1) / base_ctas;
-    const long long per_pass = static_cast<long long>(kBlock / lanes) * kUnroll;
+    const long long per_pass = static_cast<long long>(kBlock / lanes) * kColumnUnroll;
     long long most = reduce / per_pass;
     if (most < 1) most = 1;
     if (want > most) want = most;
     if (want < 1) want = 1;
-    if (want <= kMaxCluster) {
+    // The cluster's reduce-scatter gives every CTA a whole number of threads' accumulators.
+    int max_cluster = kMaxCluster;
+    while (max_cluster > lanes) max_cluster /= 2;
+    if (want <= max_cluster) {
       p.split = floor_pow2(want);
       p.cluster = p.split;
     } else {
-      if (want > 512) want = 512;
-      p.split = static_cast<int>((want + kMaxCluster - 1) / kMaxCluster * kMaxCluster);
-      p.cluster = kMaxCluster;
+      if (want > 1024) want = 1024;
+      p.split = static_cast<int>((want + max_cluster - 1) / max_cluster * max_cluster);
+      p.cluster = max_cluster;
     }
     p.tiles = base_ctas;
   }
@@ -630,9 +712,8 @@ tq_status run(const Plan& p, const void* in, void* out, long long outer, long lo
                  "a reduction with kept axes on both sides and %lld leading slices has no kernel", outer);
       dim3 grid(static_cast<unsigned>(p.column_tiles), p.split, static_cast<unsigned>(outer));
       auto go = [&](auto kernel, int vec) -> tq_status {
-        const size_t smem = (static_cast<size_t>(kBlock) * vec +
-                             static_cast<size_t>(p.cluster) * p.lanes_x * vec) * sizeof(Acc);
-        if (smem > 48 * 1024) {
+        const size_t smem = (static_cast<size_t>(kBlock) * vec + static_cast<size_t>(p.lanes_x) * vec) * sizeof(Acc);
+        if (smem > 40 * 1024) {
           TQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem)));
         }

@@ -68,8 +68,8 @@ template <> __device__ __forceinline__ float nan_max<float>(float a, float b) {
   return r;
 }
 
-// 2^t by the special-function unit (2 ulp). softmax uses it as exp(x - m) = 2^(x*log2e - m*log2e):
-// the rounding of m*log2e is common to the whole row and cancels in the normalisation.
+// 2^t by the special-function unit (2 ulp). softmax uses it as exp(x - m) = 2^((x - m) * log2e);
+// the subtraction comes first so that the row's maximum maps to exactly 2^0 whatever its size.
 __device__ __forceinline__ float exp2_approx(float t) {
   float r;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
@@ -174,14 +174,13 @@ __device__ __forceinline__ void finish_row(Vec<T, VEC> (&x)[K], int first, int s
     }
     const float row_max = fold_row(local, /*is_max=*/true, 0);
     constexpr float kLog2e = 1.4426950408889634f;
-    const float scaled_max = row_max * kLog2e;
     float sum = 0.f;
 #pragma unroll
     for (int j = 0; j < K; ++j) {
       if (first + j * step < vectors) {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          const float value = exp2_approx(fmaf(widen(x[j], e), kLog2e, -scaled_max));
+          const float value = exp2_approx((widen(x[j], e) - row_max) * kLog2e);
           sum += value;
           if constexpr (kKeepsFloats) x[j].v[e] = from_compute<T, float>(value);
         }
@@ -198,7 +197,7 @@ __device__ __forceinline__ void finish_row(Vec<T, VEC> (&x)[K], int first, int s
           if constexpr (kKeepsFloats) {
             value = widen(x[j], e);
           } else {
-            value = exp2_approx(fmaf(widen(x[j], e), kLog2e, -scaled_max));
+            value = exp2_approx((widen(x[j], e) - row_max) * kLog2e);
           }
           y.v[e] = from_compute<OutT, float>(value * inverse);
         }
