@@ -200,6 +200,39 @@ tq_status tq_reduce_launch(tq_reduce_op op,
                            int32_t device,
                            void* stream);
 
+/* The same reduction for callers that cannot allocate device memory and have nowhere to get
+ * scratch from: code that runs where cudaMalloc is off limits (a host callback on a stream, a
+ * latency-critical loop that must not take the allocator's lock or risk an implicit device
+ * synchronisation, a plugin whose host hands it tensors but no allocator), or that must keep its
+ * device-memory footprint fixed after start-up. This entry point has no counterpart in the
+ * reference, whose reductions always take their temporary from its caching allocator.
+ *
+ * It behaves like tq_reduce_launch with the scratch taken from a fixed array of
+ * TQ_STATIC_SCRATCH_BYTES bytes that is part of the library's device image: every GPU that loads
+ * the library holds that array until the process exits, whether or not this function is called.
+ * It never calls cudaMalloc, cudaFree or any allocating library routine.
+ *
+ *   - Extents whose scratch need (tq_reduce_workspace_bytes) exceeds TQ_STATIC_SCRATCH_BYTES are
+ *     refused with TQ_RESOURCE_EXHAUSTED and a message naming both sizes; nothing is launched.
+ *     Reductions that need no scratch at all are never refused for size.
+ *   - The first call on each device looks up the array's device address (one host-side runtime
+ *     query, no device work). Make that first call outside of any stream capture.
+ *   - All calls on a device share the one array. A call clears the words it needs cleared itself,
+ *     on `stream`, so the previous call's leftovers are harmless; but two calls whose kernels can
+ *     overlap on the GPU (different streams without an ordering between them, or two host
+ *     threads on different streams) race on the array and give wrong results. Order such calls
+ *     with events, or use tq_reduce_launch with separate scratch. */
+#define TQ_STATIC_SCRATCH_BYTES 524288
+tq_status tq_reduce_launch_static(tq_reduce_op op,
+                                  tq_dtype dtype,
+                                  const void* in,
+                                  void* out,
+                                  int64_t outer,
+                                  int64_t reduce,
+                                  int64_t inner,
+                                  int32_t device,
+                                  void* stream);
+
 /* ------------------------------------------------------------------------------------------ */
 /* Pack: strided / expanded / permuted view -> packed copy                                      */
 /* Replaces pack_source + pack_on_device (csrc/tessiq/codegen/pack.cpp:41-94,                    */

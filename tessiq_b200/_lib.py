@@ -21,6 +21,7 @@ F32, F64, F16, BF16, I32, I64, BOOL = range(7)
 SUM, MEAN, AMAX, AMIN, ARGMAX = range(5)
 # tq_activation
 ACT_NONE, ACT_GELU_ERF, ACT_GELU_TANH = range(3)
+STATIC_SCRATCH_BYTES = 512 * 1024  # TQ_STATIC_SCRATCH_BYTES
 
 
 class tq_layout(ctypes.Structure):
@@ -62,6 +63,7 @@ SIGNATURES = {
     "tq_reduce_workspace_bytes": (c_int32, [c_int32, c_int32, c_int64, c_int64, c_int64, c_int32, POINTER(c_size_t)]),
     "tq_reduce_launch": (c_int32, [c_int32, c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                     c_void_p, c_size_t, c_int32, c_void_p]),
+    "tq_reduce_launch_static": (c_int32, [c_int32, c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32, c_void_p]),
     "tq_pack_launch": (c_int32, [c_int32, c_int32, POINTER(c_int64), POINTER(c_int64), c_void_p, c_void_p,
                                   c_int32, c_void_p]),
     "tq_softmax_launch": (c_int32, [c_int32, c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64,

@@ -19,6 +19,7 @@
 
 #include <cstdlib>
 #include <limits>
+#include <mutex>
 #include <type_traits>
 
 #include "common.h"
@@ -776,6 +777,36 @@ int column_vec_bytes(const void* in, long long inner, int size) {
   return bytes;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Scratch that exists without anyone allocating it, for tq_reduce_launch_static.
+//
+// The array lives in the library's device image: every GPU that loads the library carries these
+// bytes from load until the process exits. In host code the array's name is only a stand-in for
+// the symbol, not a device address, so the host asks the runtime for the real address once per
+// device (with that device current) and hands that pointer to the kernels.
+constexpr size_t kStaticScratchBytes = TQ_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+std::mutex g_static_mutex;
+void* g_static_address[64] = {nullptr};
+
+// Looks the address up on first use for `device`, which must be current.
+tq_status static_scratch_for(int32_t device, void** address) {
+  TQ_REQUIRE(device >= 0 && device < 64, TQ_INVALID_ARGUMENT, "device ordinal %d is out of range", device);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_address[device] == nullptr) {
+    void* found = nullptr;
+    const cudaError_t status = cudaGetSymbolAddress(&found, g_static_scratch);
+    if (status != cudaSuccess || found == nullptr) {
+      return fail(TQ_EXTERNAL, "cannot find the built-in scratch on device %d: %s", device,
+                  cudaGetErrorString(status));
+    }
+    g_static_address[device] = found;
+  }
+  *address = g_static_address[device];
+  return TQ_OK;
+}
+
 }  // namespace
 }  // namespace tq
 
@@ -820,6 +851,40 @@ tq_status tq_reduce_launch(tq_reduce_op op, tq_dtype dtype, const void* in, void
     case TQ_BF16: return tq::run_op<__nv_bfloat16>(op, p, in, out, outer, reduce, inner, workspace, cuda_stream);
     case TQ_I32: return tq::run_op<int>(op, p, in, out, outer, reduce, inner, workspace, cuda_stream);
     case TQ_I64: return tq::run_op<long long>(op, p, in, out, outer, reduce, inner, workspace, cuda_stream);
+    default: return tq::fail(TQ_UNSUPPORTED, "reductions have no kernel for element type %s", tq::dtype_name(dtype));
+  }
+}
+
+tq_status tq_reduce_launch_static(tq_reduce_op op, tq_dtype dtype, const void* in, void* out,
+                                  int64_t outer, int64_t reduce, int64_t inner, int32_t device,
+                                  void* stream) {
+  if (tq_status s = tq::validate(op, dtype, outer, reduce, inner)) return s;
+  if (outer == 0 || inner == 0) return TQ_OK;
+  TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");
+  const int size = tq::dtype_size(dtype);
+  TQ_REQUIRE(tq::aligned_to(in, size), TQ_INVALID_ARGUMENT, "input pointer is not aligned to its element type");
+  if (tq_status s = tq::use_device(device)) return s;
+  const tq::Plan p = tq::plan(op, dtype, outer, reduce, inner, device,
+                              inner == 1 ? 16 : tq::column_vec_bytes(in, inner, size));
+  const size_t need = p.partial_bytes + p.ticket_bytes;
+  TQ_REQUIRE(need <= tq::kStaticScratchBytes, TQ_RESOURCE_EXHAUSTED,
+             "this reduction needs %zu bytes of scratch; the built-in scratch of tq_reduce_launch_static holds %zu. "
+             "Use tq_reduce_launch with caller-provided scratch for extents this large",
+             need, tq::kStaticScratchBytes);
+  void* scratch = nullptr;
+  if (need != 0) {
+    if (tq_status s = tq::static_scratch_for(device, &scratch)) return s;
+  }
+  // Partials are overwritten before they are read and the ticket words are cleared by the launch
+  // itself (a memset node on `stream`), so whatever the previous call left behind does not matter.
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case TQ_F32: return tq::run_op<float>(op, p, in, out, outer, reduce, inner, scratch, cuda_stream);
+    case TQ_F64: return tq::run_op<double>(op, p, in, out, outer, reduce, inner, scratch, cuda_stream);
+    case TQ_F16: return tq::run_op<__half>(op, p, in, out, outer, reduce, inner, scratch, cuda_stream);
+    case TQ_BF16: return tq::run_op<__nv_bfloat16>(op, p, in, out, outer, reduce, inner, scratch, cuda_stream);
+    case TQ_I32: return tq::run_op<int>(op, p, in, out, outer, reduce, inner, scratch, cuda_stream);
+    case TQ_I64: return tq::run_op<long long>(op, p, in, out, outer, reduce, inner, scratch, cuda_stream);
     default: return tq::fail(TQ_UNSUPPORTED, "reductions have no kernel for element type %s", tq::dtype_name(dtype));
   }
 }

@@ -1,0 +1,110 @@
+"""tq_reduce_launch_static: the reduction entry point that brings its own scratch.
+
+Some callers cannot allocate device memory — code running where cudaMalloc is off limits, or a
+host that hands a plugin tensors but no allocator — so they cannot give tq_reduce_launch the
+scratch a split reduction needs. This entry point uses a fixed array inside the library instead.
+The test calls it through the C ABI, twice in a row (the array keeps the first call's contents,
+which must not leak into the second), on reductions that really use scratch, and holds the
+results to those of tq_reduce_launch: same plan, same combining order, so bit-identical.
+
+The file sorts last on purpose: a run that stops at the first failure has then run every other
+test already. It passes alone in a fresh process and after the rest of the suite.
+"""
+
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def abi():
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu tests need a CUDA device")
+    from tessiq_b200 import _lib
+
+    return _lib
+
+
+def reference_reduce(abi, op, x, out, outer, reduce, inner):
+    """The existing entry point, with scratch from the caller."""
+    need = ctypes.c_size_t()
+    abi.check(abi.lib.tq_reduce_workspace_bytes(op, abi.F32 if x.dtype == torch.float32 else abi.BF16, outer, reduce, inner, 0, ctypes.byref(need)))
+    scratch = torch.empty(max(need.value, 16), dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    abi.check(abi.lib.tq_reduce_launch(op, abi.F32 if x.dtype == torch.float32 else abi.BF16, x.data_ptr(), out.data_ptr(), outer, reduce, inner,
+                                       scratch.data_ptr(), scratch.numel(), 0, ctypes.c_void_p(stream)))
+    torch.cuda.synchronize()
+    return need.value
+
+
+def static_reduce(abi, op, x, out, outer, reduce, inner):
+    stream = torch.cuda.current_stream().cuda_stream
+    abi.check(abi.lib.tq_reduce_launch_static(op, abi.F32 if x.dtype == torch.float32 else abi.BF16, x.data_ptr(), out.data_ptr(), outer, reduce, inner,
+                                              0, ctypes.c_void_p(stream)))
+    torch.cuda.synchronize()
+
+
+CASES = [
+    # (op name, dtype, outer, reduce, inner): each is split over clusters and finished by a ticket
+    ("SUM", torch.float32, 1, (1 << 22) + 3, 1),
+    ("AMAX", torch.float32, 1, 1_000_003, 1),
+    ("ARGMAX", torch.bfloat16, 3, 1 << 21, 1),
+    ("SUM", torch.float32, 1, 32768, 1024),
+    ("ARGMAX", torch.float32, 2, 20000, 128),
+    ("MEAN", torch.bfloat16, 1, 16384, 512),
+]
+
+
+@pytest.mark.parametrize("op_name, dtype, outer, reduce, inner", CASES)
+def test_static_scratch_matches_caller_scratch_twice_in_a_row(abi, op_name, dtype, outer, reduce, inner):
+    op = getattr(abi, op_name)
+    out_dtype = torch.int64 if op_name == "ARGMAX" else dtype
+    g = torch.Generator().manual_seed(outer * 31 + inner)
+    first = (torch.rand(outer, reduce, inner, generator=g) * 2 - 1).to(dtype).cuda()
+    second = (torch.rand(outer, reduce, inner, generator=g) * 2 - 1).to(dtype).cuda()
+    for x in (first, second):  # the second call finds the first call's partials and tickets in the array
+        expected = torch.empty(outer, inner, dtype=out_dtype, device="cuda")
+        need = reference_reduce(abi, op, x, expected, outer, reduce, inner)
+        assert 0 < need <= abi.STATIC_SCRATCH_BYTES, "the case must exercise the scratch and fit the built-in array"
+        got = torch.full((outer, inner), -7, dtype=out_dtype, device="cuda")
+        static_reduce(abi, op, x, got, outer, reduce, inner)
+        assert torch.equal(got, expected)
+    # and against the oracle, so that both entry points are not wrong together
+    x = second.cpu()
+    if op_name == "ARGMAX":
+        assert torch.equal(got.cpu(), x.argmax(1))
+    elif op_name == "AMAX":
+        assert torch.equal(got.cpu(), x.amax(1))
+    else:
+        truth = x.double().sum(1) / (reduce if op_name == "MEAN" else 1)
+        budget = 1e-5 * x.double().abs().sum(1).max().item() / (reduce if op_name == "MEAN" else 1) + 2.0**-8 * truth.abs().max().item() * (dtype == torch.bfloat16)
+        assert (got.cpu().double() - truth).abs().max().item() <= budget
+
+
+def test_reductions_without_scratch_need_none(abi):
+    x = torch.randn(4096, 512, device="cuda")
+    expected = torch.empty(4096, device="cuda")
+    assert reference_reduce(abi, abi.SUM, x, expected, 4096, 512, 1) == 0
+    got = torch.empty(4096, device="cuda")
+    static_reduce(abi, abi.SUM, x, got, 4096, 512, 1)
+    assert torch.equal(got, expected)
+
+
+def test_extents_beyond_the_built_in_scratch_are_refused(abi):
+    outer, reduce, inner = 2, 20000, 512  # argmax partials of about 600 KB: more than the built-in 512 KiB
+    need = ctypes.c_size_t()
+    abi.check(abi.lib.tq_reduce_workspace_bytes(abi.ARGMAX, abi.F32, outer, reduce, inner, 0, ctypes.byref(need)))
+    assert need.value > abi.STATIC_SCRATCH_BYTES
+    x = torch.zeros(outer, reduce, inner, device="cuda")
+    out = torch.full((outer, inner), -1, dtype=torch.int64, device="cuda")
+    status = abi.lib.tq_reduce_launch_static(abi.ARGMAX, abi.F32, x.data_ptr(), out.data_ptr(), outer, reduce, inner, 0, None)
+    assert status == abi.TQ_RESOURCE_EXHAUSTED
+    message = abi.last_error()
+    assert str(need.value) in message and str(abi.STATIC_SCRATCH_BYTES) in message
+    torch.cuda.synchronize()
+    assert (out == -1).all(), "a refused call must launch nothing"
+    with pytest.raises(MemoryError):
+        abi.check(status)
