@@ -1,9 +1,503 @@
-// GEMM + bias + activation. Placeholder until the tcgen05 kernel lands: every call declines.
+// GEMM + bias + activation on the 5th-generation tensor cores (tcgen05), for sm_100a.
+//
+//   C[b] = act(op(A[b]) @ op(B[b]) + bias)      bf16 or f16 operands, f32 accumulation, one rounding
+//
+// One persistent CTA per SM walks 128 x 256 output tiles. Inside a CTA, six warps have three jobs:
+//
+//   warp 0, one lane   producer: TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of a
+//                      128 x 64 slice of A and a 256 x 64 slice of B into a 4-stage ring in
+//                      shared memory, each stage announced on an mbarrier by its byte count;
+//   warp 1, one lane   issuer: for every stage four tcgen05.mma (128 x 256 x 16) accumulating in
+//                      tensor memory; tcgen05.commit hands the stage back to the producer and, after
+//                      the last slice of a tile, hands the accumulator to the epilogue;
+//   warps 2..5         epilogue: tcgen05.ld of the f32 accumulator (each warp its own 32 lanes of
+//                      tensor memory), + bias, activation in f32, one rounding, 128-bit stores.
+//
+// Tensor memory holds two 128 x 256 f32 accumulators (all 512 columns), so the epilogue of tile i
+// runs under the MMAs of tile i+1. Either operand may be K-major (row-major A, nn.Linear weight
+// [n,k]) or MN-major (A stored [k,m]; B stored [k,n], the `A @ B` form): transposed operands are
+// consumed in place through the shared-memory descriptor's major bit, never copied
+// (csrc/tessiq/codegen/gemm.cpp:28-53 in the reference does the same through cuBLAS flags).
+// No load uses cluster multicast. Every wait is bounded: a wait that gives up sets the device
+// status word (see tq_status_poll) and the CTA leaves through the normal teardown, freeing its
+// tensor memory.
+//
+// Replaces launch_gemm + the bias pre-fill (csrc/tessiq/codegen/blas.cpp:92-193,
+// csrc/tessiq/codegen/gemm.cpp:186-199) and the custom ops gemm_bias_gelu_tanh
+// (csrc/custom_ops/gemm_bias_gelu_tanh/gemm_bias_gelu_tanh.nvcc.cu:219-288) and gemm_bias_gelu
+// (csrc/custom_ops/gemm_bias_gelu/gemm_bias_gelu.nvcc.cu:90-158).
+#include <cuda.h>
+
+#include <mutex>
+#include <type_traits>
+
 #include "common.h"
 
-extern "C" tq_status tq_gemm_bias_act_launch(tq_dtype, tq_activation, const void*, int64_t, int32_t,
-                                             const void*, int64_t, int32_t, const void*, void*, int64_t,
-                                             int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
-                                             int32_t, void*) {
-  return tq::fail(TQ_UNSUPPORTED, "the GEMM kernel is not built yet");
+namespace tq {
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kTileN = 256;
+constexpr int kTileK = 64;    // 64 two-byte elements = one 128-byte swizzle row
+constexpr int kStages = 4;
+constexpr int kMmaK = 16;
+constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
+constexpr uint32_t kBytesA = kTileM * kTileK * 2;   // 16 KiB
+constexpr uint32_t kBytesB = kTileN * kTileK * 2;   // 32 KiB
+constexpr uint32_t kStageBytes = kBytesA + kBytesB;
+constexpr uint32_t kChunkBytes = 64 * kTileK * 2;   // one 64-wide MN chunk of an MN-major operand: 8 KiB
+constexpr uint32_t kTmemColumns = 512;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + static_cast<size_t>(kStages) * kStageBytes +
+                              2 * kTileN * sizeof(float) /*bias*/ + 256 /*barriers, tmem slot*/;
+
+enum WaitCode { kWaitEmpty = 101, kWaitFull = 102, kWaitTmemEmpty = 103, kWaitTmemFull = 104 };
+
+struct GemmParams {
+  int m, n, k, batch;
+  int tiles_m, tiles_n;
+  long long num_tiles;
+  const void* bias;
+  void* c;
+  long long ldc, stride_c;
+  int activation;
+  int* status;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX
+
+__device__ __forceinline__ uint32_t smem_address(const void* pointer) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
+}
+
+__device__ __forceinline__ void barrier_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void barrier_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void barrier_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool barrier_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Waits for the phase of `bar` with the given parity, for a bounded number of polls. When the
+// bound runs out (or another thread's already did) the status word gets `code` and the caller
+// must leave its loop.
+__device__ __forceinline__ bool barrier_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (barrier_try_wait(bar, parity)) return true;
+    if ((spin & 0x3ff) == 0x3ff && *reinterpret_cast<volatile int*>(status) != 0) return false;
+  }
+  atomicCAS(status, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(columns) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem], 128 x N x 16, issued by one thread.
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// The mbarrier gets one arrival when every tcgen05 operation this thread issued so far is done.
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 consecutive columns of tensor memory: lane i of the warp gets row i.
+__device__ __forceinline__ void tmem_load_32(uint32_t address, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(address)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle. Bits: [0,14) start address >> 4,
+// [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4, [46,48) version = 1,
+// [61,64) layout = 2 (SWIZZLE_128B). For a K-major operand the stride offset is the distance
+// between 8-row groups (8 x 128 B) and the leading offset is unused; for an MN-major operand the
+// leading offset is the distance between 64-element chunks along M/N and the stride offset the
+// distance between groups of 8 K-rows.
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t leading_bytes, uint32_t stride_bytes) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((address & 0x3ffff) >> 4);
+  desc |= static_cast<uint64_t>((leading_bytes >> 4) & 0x3fff) << 16;
+  desc |= static_cast<uint64_t>((stride_bytes >> 4) & 0x3fff) << 32;
+  desc |= static_cast<uint64_t>(1) << 46;
+  desc |= static_cast<uint64_t>(2) << 61;
+  return desc;
+}
+
+// Instruction descriptor of tcgen05.mma kind::f16: f32 accumulator, A/B format (0 f16, 1 bf16),
+// major bits (0 K-major, 1 MN-major), N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t instruction_descriptor(bool bf16, bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+         ((b_mn_major ? 1u : 0u) << 16) | (static_cast<uint32_t>(kTileN >> 3) << 17) |
+         (static_cast<uint32_t>(kTileM >> 4) << 24);
+}
+
+__device__ __forceinline__ float exp2_ftz(float t) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+  return r;
+}
+__device__ __forceinline__ float rcp_ftz(float d) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+  return r;
+}
+
+__device__ __forceinline__ float activate(float v, int activation) {
+  if (activation == TQ_ACT_GELU_TANH) {
+    // 0.5 v (1 + tanh(k (v + 0.044715 v^3))) = v / (1 + exp(-2k (v + 0.044715 v^3)))
+    return v * rcp_ftz(1.0f + exp2_ftz(-2.302208198144325f * (v + 0.044715f * v * v * v)));
+  }
+  if (activation == TQ_ACT_GELU_ERF) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+  return v;
+}
+
+// Tiles in groups of 16 rows of tiles, so that the CTAs running at one time share A and B slices
+// in L2.
+__device__ __forceinline__ void tile_coordinates(long long tile, const GemmParams& p, int& batch, int& tile_m, int& tile_n) {
+  const long long per_batch = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  batch = static_cast<int>(tile / per_batch);
+  const int t = static_cast<int>(tile % per_batch);
+  constexpr int kGroup = 16;
+  const int group_span = kGroup * p.tiles_n;
+  const int group = t / group_span;
+  const int first_m = group * kGroup;
+  const int rows = min(kGroup, p.tiles_m - first_m);
+  tile_m = first_m + (t % group_span) % rows;
+  tile_n = (t % group_span) / rows;
+}
+
+template <typename T, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bias_act_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  extern __shared__ unsigned char raw_smem[];
+  const uint32_t base = (smem_address(raw_smem) + 1023u) & ~1023u;   // swizzled tiles need 1024-byte alignment
+  unsigned char* aligned = raw_smem + (base - smem_address(raw_smem));
+  float* bias_smem = reinterpret_cast<float*>(aligned + kStages * kStageBytes);        // [2][kTileN]
+  const uint32_t barriers = base + kStages * kStageBytes + 2 * kTileN * sizeof(float);
+  // barrier slots, 8 bytes each: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](int s) { return barriers + 8u * s; };
+  auto empty_bar = [&](int s) { return barriers + 8u * (kStages + s); };
+  auto tmem_full_bar = [&](int a) { return barriers + 8u * (2 * kStages + a); };
+  auto tmem_empty_bar = [&](int a) { return barriers + 8u * (2 * kStages + 2 + a); };
+  const uint32_t tmem_slot = barriers + 8u * (2 * kStages + 4);
+  volatile uint32_t* tmem_slot_pointer =
+      reinterpret_cast<volatile uint32_t*>(aligned + kStages * kStageBytes + 2 * kTileN * sizeof(float) + 8 * (2 * kStages + 4));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      barrier_init(full_bar(s), 1);
+      barrier_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      barrier_init(tmem_full_bar(a), 1);
+      barrier_init(tmem_empty_bar(a), kEpilogueThreads / 32);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemColumns);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot_pointer;
+
+  const int k_blocks = (p.k + kTileK - 1) / kTileK;
+
+  if (warp == 0) {
+    // ---- producer --------------------------------------------------------------------------
+    if (lane == 0) {
+      uint32_t iteration = 0;
+      bool alive = true;
+      for (long long tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x) {
+        int batch, tile_m, tile_n;
+        tile_coordinates(tile, p, batch, tile_m, tile_n);
+        for (int kb = 0; kb < k_blocks; ++kb, ++iteration) {
+          const int s = iteration % kStages;
+          const uint32_t phase = (iteration / kStages) & 1;
+          if (!barrier_wait(empty_bar(s), phase ^ 1, p.status, kWaitEmpty)) { alive = false; break; }
+          barrier_expect_tx(full_bar(s), kStageBytes);
+          const uint32_t smem_a = base + s * kStageBytes;
+          const uint32_t smem_b = smem_a + kBytesA;
+          const int k0 = kb * kTileK;
+          if constexpr (A_MN) {
+#pragma unroll
+            for (int i = 0; i < kTileM / 64; ++i) tma_load_3d(smem_a + i * kChunkBytes, &map_a, full_bar(s), tile_m * kTileM + i * 64, k0, batch);
+          } else {
+            tma_load_3d(smem_a, &map_a, full_bar(s), k0, tile_m * kTileM, batch);
+          }
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int i = 0; i < kTileN / 64; ++i) tma_load_3d(smem_b + i * kChunkBytes, &map_b, full_bar(s), tile_n * kTileN + i * 64, k0, batch);
+          } else {
+            tma_load_3d(smem_b, &map_b, full_bar(s), k0, tile_n * kTileN, batch);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ------------------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = instruction_descriptor(std::is_same_v<T, __nv_bfloat16>, A_MN, B_MN);
+      // K-major: 8-row groups are 1024 B apart; a step of 16 along K is 32 B inside the swizzle row.
+      // MN-major: 64-wide chunks are kChunkBytes apart, groups of 8 K-rows 1024 B; 16 K-rows = 2048 B.
+      constexpr uint32_t lead_a = A_MN ? kChunkBytes : 0, lead_b = B_MN ? kChunkBytes : 0;
+      constexpr uint32_t step_a = A_MN ? 2048 : 32, step_b = B_MN ? 2048 : 32;
+      uint32_t iteration = 0;
+      uint32_t local_tile = 0;
+      bool alive = true;
+      for (long long tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x, ++local_tile) {
+        const uint32_t acc = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        if (!barrier_wait(tmem_empty_bar(acc), acc_phase ^ 1, p.status, kWaitTmemEmpty)) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * kTileN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++iteration) {
+          const int s = iteration % kStages;
+          const uint32_t phase = (iteration / kStages) & 1;
+          if (!barrier_wait(full_bar(s), phase, p.status, kWaitFull)) { alive = false; break; }
+          tcgen05_fence_after();
+          const uint32_t smem_a = base + s * kStageBytes;
+          const uint32_t smem_b = smem_a + kBytesA;
+#pragma unroll
+          for (int kk = 0; kk < kTileK / kMmaK; ++kk) {
+            const uint64_t desc_a = smem_descriptor(smem_a + kk * step_a, lead_a, 1024);
+            const uint64_t desc_b = smem_descriptor(smem_b + kk * step_b, lead_b, 1024);
+            mma_f16(tmem_d, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          mma_commit(empty_bar(s));                        // the stage is free once these MMAs have read it
+          if (kb == k_blocks - 1) mma_commit(tmem_full_bar(acc));  // and the tile is complete
+        }
+      }
+    }
+  } else {
+    // ---- epilogue: warps 2..5; warp w owns tensor-memory lanes 32 (w % 4) .. +31 -----------
+    const int epilogue_thread = threadIdx.x - 64;
+    const int quarter = warp & 3;
+    uint32_t local_tile = 0;
+    for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++local_tile) {
+      int batch, tile_m, tile_n;
+      tile_coordinates(tile, p, batch, tile_m, tile_n);
+      const uint32_t acc = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      const int n0 = tile_n * kTileN;
+      float* bias_tile = bias_smem + acc * kTileN;
+      for (int j = epilogue_thread; j < kTileN; j += kEpilogueThreads) {
+        float value = 0.f;
+        if (p.bias != nullptr && n0 + j < p.n) value = to_compute(static_cast<const T*>(p.bias)[n0 + j]);
+        bias_tile[j] = value;
+      }
+      if (!barrier_wait(tmem_full_bar(acc), acc_phase, p.status, kWaitTmemFull)) break;
+      tcgen05_fence_after();
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");   // bias_tile is complete
+
+      const int row = tile_m * kTileM + quarter * 32 + lane;
+      T* c_row = static_cast<T*>(p.c) + static_cast<long long>(batch) * p.stride_c + static_cast<long long>(row) * p.ldc + n0;
+      const bool vector_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (p.stride_c % 8 == 0);
+#pragma unroll 1
+      for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
+        uint32_t r[32];
+        tmem_load_32(tmem_base + acc * kTileN + chunk * 32 + (static_cast<uint32_t>(quarter * 32) << 16), r);
+        tmem_load_wait();
+        if (row < p.m) {
+          const int column = n0 + chunk * 32;
+          if (vector_ok && column + 32 <= p.n) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              Vec<T, 8> out;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float value = __uint_as_float(r[v * 8 + e]) + bias_tile[chunk * 32 + v * 8 + e];
+                out.v[e] = from_compute<T, float>(activate(value, p.activation));
+              }
+              *reinterpret_cast<uint4*>(c_row + chunk * 32 + v * 8) = *reinterpret_cast<const uint4*>(&out);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              if (column + e < p.n) {
+                const float value = __uint_as_float(r[e]) + bias_tile[chunk * 32 + e];
+                c_row[chunk * 32 + e] = from_compute<T, float>(activate(value, p.activation));
+              }
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) barrier_arrive(tmem_empty_bar(acc));   // this warp has read its lanes of the accumulator
+    }
+  }
+
+  // ---- teardown: every thread arrives here, also after a wait that gave up -----------------
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kTmemColumns);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled function = [] {
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &entry, 12000, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      return static_cast<EncodeTiled>(nullptr);
+    }
+    return reinterpret_cast<EncodeTiled>(entry);
+  }();
+  return function;
+}
+
+// A three-axis map over one operand: `inner` contiguous elements, `outer` rows `ld` elements apart,
+// `batch` matrices `stride` elements apart; box = box_inner x box_outer x 1, 128-byte swizzle.
+tq_status make_map(CUtensorMap* map, tq_dtype dtype, const void* pointer, long long inner, long long outer, long long ld,
+                   long long batch, long long stride, int box_inner, int box_outer) {
+  EncodeTiled encode = encode_tiled();
+  TQ_REQUIRE(encode != nullptr, TQ_EXTERNAL, "the CUDA driver does not provide cuTensorMapEncodeTiled");
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer), static_cast<cuuint64_t>(batch)};
+  // A stride of 0 (one operand shared by the whole batch) is not a legal map stride; such a map
+  // gets one matrix and the kernel is launched with batch coordinate 0 for it (see below).
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2, static_cast<cuuint64_t>(stride > 0 ? stride : ld * outer) * 2};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer), 1};
+  const cuuint32_t element_strides[3] = {1, 1, 1};
+  const CUresult result = encode(map, dtype == TQ_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                                 const_cast<void*>(pointer), dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TQ_REQUIRE(result == CUDA_SUCCESS, TQ_UNSUPPORTED, "this operand layout cannot be described to TMA (driver code %d)", static_cast<int>(result));
+  return TQ_OK;
+}
+
+template <typename T>
+tq_status launch(bool a_mn, bool b_mn, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, int32_t device, cudaStream_t stream) {
+  auto go = [&](auto kernel) -> tq_status {
+    static std::mutex mutex;
+    {
+      std::lock_guard<std::mutex> lock(mutex);
+      TQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes)));
+    }
+    long long ctas = p.num_tiles < sm_count(device) ? p.num_tiles : sm_count(device);
+    kernel<<<static_cast<unsigned>(ctas), kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+    return check_launch("gemm_bias_act_kernel");
+  };
+  if (!a_mn && !b_mn) return go(gemm_bias_act_kernel<T, false, false>);
+  if (!a_mn && b_mn) return go(gemm_bias_act_kernel<T, false, true>);
+  if (a_mn && !b_mn) return go(gemm_bias_act_kernel<T, true, false>);
+  return go(gemm_bias_act_kernel<T, true, true>);
+}
+
+}  // namespace
+}  // namespace tq
+
+extern "C" tq_status tq_gemm_bias_act_launch(tq_dtype dtype, tq_activation activation, const void* a, int64_t lda,
+                                             int32_t trans_a, const void* b, int64_t ldb, int32_t trans_b,
+                                             const void* bias, void* c, int64_t ldc, int64_t m, int64_t n, int64_t k,
+                                             int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_c,
+                                             int32_t device, void* stream) {
+  TQ_REQUIRE(dtype == TQ_BF16 || dtype == TQ_F16, TQ_UNSUPPORTED,
+             "the tensor-core GEMM takes bf16 or f16 operands, not %s", tq::dtype_name(dtype));
+  TQ_REQUIRE(activation >= TQ_ACT_NONE && activation <= TQ_ACT_GELU_TANH, TQ_INVALID_ARGUMENT, "unknown activation %d", activation);
+  TQ_REQUIRE(m >= 0 && n >= 0 && k >= 0 && batch >= 0, TQ_INVALID_ARGUMENT, "negative extent in m=%lld n=%lld k=%lld batch=%lld",
+             (long long)m, (long long)n, (long long)k, (long long)batch);
+  if (m == 0 || n == 0 || batch == 0) return TQ_OK;
+  TQ_REQUIRE(k > 0, TQ_UNSUPPORTED, "a product over no elements has no kernel");
+  TQ_REQUIRE(a != nullptr && b != nullptr && c != nullptr, TQ_INVALID_ARGUMENT, "null operand or result");
+  TQ_REQUIRE(m < (1LL << 31) && n < (1LL << 31) && k < (1LL << 31), TQ_UNSUPPORTED, "extents beyond 2^31 have no kernel");
+  // TMA's rules: 16-byte-aligned bases, strides that are multiples of 16 bytes.
+  const long long a_inner = trans_a ? m : k, a_outer = trans_a ? k : m;
+  const long long b_inner = trans_b ? k : n, b_outer = trans_b ? n : k;
+  TQ_REQUIRE(lda >= a_inner && ldb >= b_inner && ldc >= n, TQ_INVALID_ARGUMENT, "a leading dimension is smaller than its row");
+  TQ_REQUIRE(tq::aligned_to(a, 16) && tq::aligned_to(b, 16) && lda % 8 == 0 && ldb % 8 == 0 &&
+                 (batch == 1 || (stride_a % 8 == 0 && stride_b % 8 == 0)),
+             TQ_UNSUPPORTED, "operands must be 16-byte aligned with leading dimensions and batch strides that are multiples of 8 elements");
+  TQ_REQUIRE(tq::aligned_to(c, 2) && (bias == nullptr || tq::aligned_to(bias, 2)), TQ_INVALID_ARGUMENT, "misaligned result or bias");
+  if (tq_status s = tq::use_device(device)) return s;
+  int* status = tq::device_status_word(device);
+  TQ_REQUIRE(status != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
+
+  CUtensorMap map_a, map_b;
+  const long long batch_a = stride_a > 0 ? batch : 1, batch_b = stride_b > 0 ? batch : 1;
+  if (tq_status s = tq::make_map(&map_a, dtype, a, a_inner, a_outer, lda, batch_a, stride_a, 64, trans_a ? 64 : tq::kTileM)) return s;
+  if (tq_status s = tq::make_map(&map_b, dtype, b, b_inner, b_outer, ldb, batch_b, stride_b, 64, trans_b ? tq::kTileN : 64)) return s;
+  TQ_REQUIRE(batch == 1 || (stride_a > 0 && stride_b > 0), TQ_UNSUPPORTED,
+             "a batch that shares one operand (stride 0) has no kernel; fold the batch into m instead");
+
+  tq::GemmParams p = {};
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.k = static_cast<int>(k);
+  p.batch = static_cast<int>(batch);
+  p.tiles_m = static_cast<int>((m + tq::kTileM - 1) / tq::kTileM);
+  p.tiles_n = static_cast<int>((n + tq::kTileN - 1) / tq::kTileN);
+  p.num_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * batch;
+  p.bias = bias;
+  p.c = c;
+  p.ldc = ldc;
+  p.stride_c = stride_c;
+  p.activation = activation;
+  p.status = status;
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  if (dtype == TQ_BF16) return tq::launch<__nv_bfloat16>(trans_a != 0, trans_b == 0, map_a, map_b, p, device, cuda_stream);
+  return tq::launch<__half>(trans_a != 0, trans_b == 0, map_a, map_b, p, device, cuda_stream);
 }
