@@ -301,6 +301,8 @@ def run_ours(args) -> dict:
     d2h_bytes = sum(t.numel() * t.element_size() for t in host_out.values())
     h2d_bytes = step.host_x.numel() * 4
 
+    extra = other_configs(local, stream) if not args.no_extra else {}
+
     times = torch.tensor([seconds, e2e_seconds, dominant_ms], dtype=torch.float64, device=f"cuda:{local}")
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -331,12 +333,88 @@ def run_ours(args) -> dict:
         "gpu_launches": step.launches_per_step() * args.steps,
         "clocks": clock_summary,
         "kernels": per_op,
+        "extra": extra,
     }
     if rank == 0 and world == 1:
         line["cpu_baseline"] = cpu_baseline(sample_rows=2048, repeats=3)
     if world > 1:
         dist.destroy_process_group()
     return line if rank == 0 else {}
+
+
+def other_configs(device: int, stream) -> dict:
+    """The other BASELINE configs' headline kernels on this rank's GPU, device-timed: config 1's
+    fused chain (8 rotating buffer sets, graph replay), config 3's GEMM + bias + GELU (TFLOP/s
+    against the measured cuBLAS bf16 peaks), config 5's six-op chain at 2^28 elements."""
+    import torch
+
+    from tessiq_b200 import ops
+    from tessiq_b200.kernel import FusedKernel
+
+    dev = f"cuda:{device}"
+    raw = stream.cuda_stream
+    out = {}
+    peak_hbm, _ = peaks()
+    measured = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+
+    def timed(fn, iters):
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                fn()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(iters):
+                fn()
+            b.record(stream)
+            stream.synchronize()
+        return a.elapsed_time(b) / iters * 1e-3
+
+    # config 1: y = gelu_tanh(x + b) * sigmoid(x) - 0.5 x on x[4096,4096] f32
+    chain = FusedKernel("in x f32 same\nin b f32 cycled\nv0 = add x b\nv1 = gelu_tanh v0\nv2 = sigmoid x\nv3 = mul v1 v2\n"
+                        "v4 = mul x 0.5\nv5 = sub v3 v4\nout v5 f32\n")
+    xs = [torch.randn(4096, 4096, device=dev) for _ in range(8)]
+    ys = [torch.empty(4096, 4096, device=dev) for _ in range(8)]
+    bias = torch.randn(4096, device=dev) * 0.02
+    with torch.cuda.stream(stream):
+        for j in range(8):
+            chain.launch([xs[j], bias], ys[j], stream=raw)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for j in range(8):
+                chain.launch([xs[j], bias], ys[j], stream=raw)
+    seconds = timed(graph.replay, 10) / 8
+    nbytes = 2 * 4096 * 4096 * 4 + 4096 * 4
+    out["config1_fused_chain_f32"] = {"us": round(seconds * 1e6, 1), "gbs": round(nbytes / seconds / 1e9, 1),
+                                      "frac_of_measured_hbm": round(nbytes / seconds / 1e9 / peak_hbm, 4),
+                                      "note": "8 rotating buffer sets (1 GiB) so no launch finds its input in L2"}
+    del xs, ys, graph
+
+    # config 3: gelu_tanh(A @ B + bias), bf16, A[8192,4096], B[4096,16384]
+    g = torch.Generator().manual_seed(3)
+    a = (torch.randn(8192, 4096, generator=g) * 0.02).bfloat16().to(dev)
+    b = (torch.randn(4096, 16384, generator=g) * 0.02).bfloat16().to(dev)
+    gbias = (torch.randn(16384, generator=g) * 0.02).bfloat16().to(dev)
+    with torch.cuda.stream(stream):
+        seconds = timed(lambda: ops.matmul_bias_gelu_tanh(a, b, gbias), 20)
+    flop = 2 * 8192 * 4096 * 16384
+    tflops = flop / seconds / 1e12
+    out["config3_gemm_bias_gelu_bf16"] = {"us": round(seconds * 1e6, 1), "tflops": round(tflops, 1),
+                                          "frac_of_measured_burst": round(tflops / measured.get("bf16_tflops", 1590.0), 4),
+                                          "frac_of_measured_sustained": round(tflops / measured.get("bf16_tflops_sustained", 1400.0), 4),
+                                          "frac_of_nominal_2250": round(tflops / 2250.0, 4)}
+    del a, b
+
+    # config 5a: six-op chain with predicate and cast, f32 -> bf16, 2^28 elements
+    n = 1 << 28
+    p, q = torch.rand(n, device=dev) * 2 - 1, torch.rand(n, device=dev) * 2 - 1
+    y = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    six = FusedKernel("in a f32 same\nin b f32 same\nt0 = add a b\nt1 = exp t0\nt2 = mul t1 b\nt3 = tanh t2\nc = gt a 0\n"
+                      "w = where c t3 a\ny = cast w bf16\nout y bf16\n")
+    seconds = timed(lambda: six.launch([p, q], y, stream=raw), 10)
+    out["config5_six_op_chain_f32_to_bf16"] = {"us": round(seconds * 1e6, 1), "gbs": round(n * 10 / seconds / 1e9, 1),
+                                               "frac_of_measured_hbm": round(n * 10 / seconds / 1e9 / peak_hbm, 4)}
+    return out
 
 
 def run_profile(args) -> None:
@@ -359,6 +437,17 @@ def run_profile(args) -> None:
             kernel.launch([xs[i % 6], bias], out, stream=None)
         torch.cuda.synchronize()
         return
+    if args.profile == "gemm":
+        # config 3's operation at a quarter of its size: A[2048,4096] @ B[4096,16384] + bias, GELU
+        from tessiq_b200 import ops
+
+        a = (torch.randn(2048, 4096, device="cuda") * 0.02).bfloat16()
+        b = (torch.randn(4096, 16384, device="cuda") * 0.02).bfloat16()
+        bias = (torch.randn(16384, device="cuda") * 0.02).bfloat16()
+        for _ in range(args.warmup + args.steps):
+            ops.matmul_bias_gelu_tanh(a, b, bias)
+        torch.cuda.synchronize()
+        return
     step = Step(0)
     stream = torch.cuda.Stream(device=0)
     with torch.cuda.stream(stream):
@@ -370,9 +459,11 @@ def run_profile(args) -> None:
         stream.synchronize()
 
 
-# Measured once with ncu on the dominant kernel (profiles/softmax_rows_f32.md): DRAM read + write
-# bytes per launch. None until a capture exists.
-DOMINANT_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per full launch, from one
+# ncu capture at 16384 rows scaled by two (profiles/softmax_rows_f32_row_cluster_kernel.md); the
+# traffic grows in proportion to the rows. Below the 1 073 741 824 algorithmic bytes only because
+# the tail of the result is still in L2 when the kernel ends.
+DOMINANT_TRAFFIC_BYTES = 964180992
 
 
 # ---------------------------------------------------------------------------------------------
@@ -445,7 +536,10 @@ def run_reference(args) -> dict:
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
         "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(seconds / args.steps * 1e3, 2),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32+bf16", "data": "synthetic",
-        "config": {"workload": "config 2 (see the default arm), bounded sample of rows on the host CPU", "rows": sample_rows, "width": WIDTH},
+        "config": {"workload": "config 2: sum/mean/amax/argmax/softmax/LayerNorm over the last axis of x[32768,4096], "
+                               "f32 and bf16, contiguous and on the transposed view, plus the pack alone",
+                   "rows_per_gpu": ROWS, "width": WIDTH, "sample_rows": sample_rows,
+                   "timing": "host wall clock; each step runs the 26 operations on a bounded sample of the rows"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -458,6 +552,7 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--no-extra", action="store_true", help="skip the other configs' kernels (config 1, 3, 5)")
     parser.add_argument("--rows", type=int, default=ROWS, help="rows of x per GPU (default: the config's 32768)")
     parser.add_argument("--profile", metavar="OP", default=None,
                         help="for ncu: run only eager launches of OP (e.g. softmax_rows_f32, or `all`), "
