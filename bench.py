@@ -204,6 +204,8 @@ def run_ours(args) -> dict:
         raise RuntimeError("bench.py needs a CUDA device: tessiq_b200 has no CPU path")
     torch.cuda.set_device(local)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
 
     from tessiq_b200 import ops
@@ -302,6 +304,28 @@ def run_ours(args) -> dict:
     h2d_bytes = step.host_x.numel() * 4
 
     extra = other_configs(local, stream) if not args.no_extra else {}
+
+    # config 5c: a reduction over every element of the sharded tensor — one local kernel per rank,
+    # then an all-reduce of the per-GPU partials (NCCL; a no-op at one GPU).
+    from tessiq_b200 import sharding
+
+    x32 = step.sets["f32"]["x"]
+    start_row = rank * ROWS
+    for op in ("sum", "amax"):
+        for _ in range(3):
+            sharding.global_reduce(op, x32, offset=start_row * WIDTH, total=world * x32.numel())
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(20):
+            sharding.global_reduce(op, x32, offset=start_row * WIDTH, total=world * x32.numel())
+        b.record()
+        torch.cuda.synchronize()
+        us = torch.tensor([a.elapsed_time(b) / 20 * 1e3], dtype=torch.float64, device=f"cuda:{local}")
+        if world > 1:
+            dist.all_reduce(us, op=dist.ReduceOp.MAX)
+        extra[f"config5c_global_{op}_f32"] = {"us": round(us.item(), 1), "gbs": round(world * x32.numel() * 4 / us.item() / 1e3, 1),
+                                              "collective": "none" if world == 1 else f"all-reduce of per-GPU partials over {world} ranks"}
 
     times = torch.tensor([seconds, e2e_seconds, dominant_ms], dtype=torch.float64, device=f"cuda:{local}")
     if world > 1:
@@ -490,9 +514,19 @@ def cpu_step(x32, gamma, beta, gamma_t, beta_t):
     return results
 
 
+def use_all_host_threads() -> int:
+    """torchrun sets OMP_NUM_THREADS=1; the CPU arm is meant to use every host core."""
+    import torch
+
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(max(cores, 1))
+    return torch.get_num_threads()
+
+
 def cpu_baseline(sample_rows: int, repeats: int) -> dict:
     import torch
 
+    use_all_host_threads()
     g = torch.Generator().manual_seed(1234)
     x = torch.randn(sample_rows, WIDTH, generator=g)
     gamma, beta = 1 + torch.randn(WIDTH, generator=g) * 0.02, torch.randn(WIDTH, generator=g) * 0.02
@@ -517,6 +551,7 @@ def run_reference(args) -> dict:
         return {}
     import torch
 
+    use_all_host_threads()
     sample_rows = 2048
     g = torch.Generator().manual_seed(1234)
     x = torch.randn(sample_rows, WIDTH, generator=g)
