@@ -1,0 +1,118 @@
+"""The recipe executor: runs the steps of a compiled graph on one GPU, one stream.
+
+The reference walks its FX graph with an `fx.Interpreter` on every call and copies every result to
+the host (python/tessiq/executor.py:146-239); its own profile attributes 42 % of a call to the
+interpreted steps, 34 % to launching and 24 % to that copy (README.md:333-337). Here a recipe is a
+flat list of pre-bound steps (a kernel launch, a view, or an interpreted operator), values are
+dropped after their last reader, results stay on the device, and `GraphedRecipe` replays the whole
+recipe as one CUDA graph once it has seen a signature of input shapes twice: no Python and no
+launch latency between kernels.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+from torch import fx
+
+
+@dataclass
+class Step:
+    kind: str                      # fused | reduction | custom | gemm | pack | view | constant | interpreted
+    output: str                    # the FX node this step computes
+    run: Callable[[dict], Any]
+    reads: list[str]
+    kernel: Any = None
+    note: str = ""
+
+
+@dataclass
+class Recipe:
+    inputs: list[str] = field(default_factory=list)
+    steps: list[Step] = field(default_factory=list)
+    outputs: Any = None
+    kernels: list[Any] = field(default_factory=list)
+    _dead_after: list[list[str]] = field(default_factory=list)
+
+    def finish(self) -> None:
+        """Records, for every step, which values no later step reads."""
+        kept = {n.name for n in _nodes_in(self.outputs)}
+        last: dict[str, int] = {}
+        for i, step in enumerate(self.steps):
+            for name in step.reads:
+                last[name] = i
+        self._dead_after = [[] for _ in self.steps]
+        for name, i in last.items():
+            if name not in kept:
+                self._dead_after[i].append(name)
+
+    def counts(self) -> dict[str, int]:
+        out: dict[str, int] = {}
+        for step in self.steps:
+            out[step.kind] = out.get(step.kind, 0) + 1
+        return out
+
+    @property
+    def interpreted(self) -> list[str]:
+        """The nodes that have no kernel here and run as PyTorch operators."""
+        return [step.note for step in self.steps if step.kind == "interpreted"]
+
+    def run(self, *args):
+        if len(args) != len(self.inputs):
+            raise ValueError(f"the recipe takes {len(self.inputs)} inputs, not {len(args)}")
+        env = dict(zip(self.inputs, args))
+        for step, dead in zip(self.steps, self._dead_after):
+            env[step.output] = step.run(env)
+            for name in dead:
+                env.pop(name, None)
+        return fx.node.map_arg(self.outputs, lambda n: env[n.name])
+
+
+def _nodes_in(structure) -> list[fx.Node]:
+    found: list[fx.Node] = []
+    fx.node.map_arg(structure, lambda n: found.append(n) or n)
+    return found
+
+
+class GraphedRecipe:
+    """Runs a recipe eagerly the first time it sees a signature of input shapes, captures it into a
+    CUDA graph the second time, and replays the graph from then on (inputs are copied into the
+    graph's static buffers; outputs are the graph's static outputs, valid until the next call)."""
+
+    def __init__(self, recipe: Recipe):
+        self.recipe = recipe
+        self._seen: set = set()
+        self._graphs: dict = {}
+
+    @staticmethod
+    def _signature(args) -> tuple:
+        return tuple((tuple(a.shape), a.dtype, a.device.index, tuple(a.stride())) if isinstance(a, torch.Tensor) else ("scalar", a) for a in args)
+
+    def run(self, *args):
+        key = self._signature(args)
+        entry = self._graphs.get(key)
+        if entry is not None:
+            graph, static_inputs, outputs = entry
+            for static, arg in zip(static_inputs, args):
+                if isinstance(static, torch.Tensor) and static.data_ptr() != arg.data_ptr():
+                    static.copy_(arg)
+            graph.replay()
+            return outputs
+        if key not in self._seen or not all(isinstance(a, torch.Tensor) and a.is_cuda for a in args):
+            self._seen.add(key)
+            return self.recipe.run(*args)
+        static_inputs = [a.clone() for a in args]
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            self.recipe.run(*static_inputs)  # warm: modules loaded, scratch allocated, on the capture stream
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                outputs = self.recipe.run(*static_inputs)
+        torch.cuda.current_stream().wait_stream(side)
+        self._graphs[key] = (graph, static_inputs, outputs)
+        graph.replay()
+        return outputs

@@ -1,0 +1,183 @@
+"""The compile backend without a GPU: partitioning of ATen graphs into kernels (the programs are
+really compiled by NVRTC for sm_100a; nothing is launched), option checking, and on the GPU the
+compiled functions against the oracle."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+from torch.fx.experimental.proxy_tensor import make_fx
+
+
+def trace(fn, *inputs):
+    from tessiq_b200.backend import _decompositions
+
+    return make_fx(fn, decomposition_table=_decompositions(), tracing_mode="fake")(*inputs)
+
+
+def chain1(x, b):
+    return F.gelu(x + b, approximate="tanh") * torch.sigmoid(x) - 0.5 * x
+
+
+def chain5(a, b):
+    t = torch.tanh(torch.exp(a + b) * b)
+    return torch.where(a > 0, t, a).to(torch.bfloat16)
+
+
+def test_config_1_becomes_one_kernel():
+    from tessiq_b200.backend import build_recipe
+
+    recipe = build_recipe(trace(chain1, torch.randn(64, 128), torch.randn(128)))
+    assert recipe.counts() == {"fused": 1} and recipe.interpreted == []
+    (kernel,) = recipe.kernels
+    assert kernel.reads == ["same", "cycled"] and len(kernel.members) == 6
+    assert "gelu_tanh" in kernel.program and "sigmoid" in kernel.program
+    # the reference splits this chain in two groups around a host gelu (observed IR)
+
+
+def test_config_5_chain_fuses_predicate_and_cast():
+    from tessiq_b200.backend import build_recipe
+
+    recipe = build_recipe(trace(chain5, torch.randn(4096), torch.randn(4096)))
+    assert recipe.counts() == {"fused": 1} and recipe.interpreted == []
+    program = recipe.kernels[0].program
+    assert " gt " in program and " where " in program and "cast" in program and program.strip().endswith("bf16")
+
+
+def test_reductions_norms_and_views_map_onto_kernels():
+    from tessiq_b200.backend import build_recipe
+
+    def model(x, w, b):
+        y = F.layer_norm(x, (256,), w, b, 1e-5)
+        p = torch.softmax(y, -1)
+        return p.sum(-1), p.amax(-1), y.argmax(-1), (y.t().contiguous() * 2).mean(0)
+
+    recipe = build_recipe(trace(model, torch.randn(32, 256), torch.randn(256), torch.randn(256)))
+    counts = recipe.counts()
+    assert recipe.interpreted == []
+    assert counts["custom"] == 2 and counts["reduction"] == 4 and counts["pack"] == 1 and counts["fused"] == 1
+
+
+def test_a_value_read_twice_ends_its_group():
+    from tessiq_b200.backend import build_recipe
+
+    def fn(x):
+        y = torch.exp(x)          # read by both branches: must be materialised once
+        return torch.tanh(y) + 1, torch.relu(y) * 3
+
+    recipe = build_recipe(trace(fn, torch.randn(100)))
+    assert recipe.counts()["fused"] == 3 and recipe.interpreted == []
+
+
+def test_unclaimed_nodes_are_counted_not_hidden():
+    from tessiq_b200.backend import build_recipe
+
+    recipe = build_recipe(trace(lambda x: torch.cumsum(x, -1) + 1, torch.randn(8, 8)))
+    assert len(recipe.interpreted) == 1 and "cumsum" in recipe.interpreted[0]
+    assert recipe.counts()["fused"] == 1
+
+
+def test_bf16_matmuls_take_the_tensor_core_kernel_f32_stays_interpreted():
+    from tessiq_b200.backend import build_recipe
+
+    lin = lambda x, w, b: F.gelu(F.linear(x, w, b), approximate="tanh")  # noqa: E731
+    half = build_recipe(trace(lin, torch.randn(64, 128).bfloat16(), torch.randn(256, 128).bfloat16(), torch.randn(256).bfloat16()))
+    assert half.counts().get("gemm") == 1 and half.interpreted == []
+    full = build_recipe(trace(lin, torch.randn(64, 128), torch.randn(256, 128), torch.randn(256)))
+    assert any("addmm" in note for note in full.interpreted)
+
+
+def test_options_are_checked():
+    from tessiq_b200.backend import compile_graph
+
+    gm = torch.fx.symbolic_trace(lambda x: x + 1)
+    with pytest.raises(ValueError):
+        compile_graph(gm, [torch.zeros(1)], options={"colour": "red"})   # tests/python/test_backend.py:111
+    with pytest.raises(ValueError):
+        compile_graph(gm, [torch.zeros(1)], mode="max-autotune")
+    with pytest.raises(ValueError):
+        compile_graph(gm, [torch.zeros(1)], options={"math": "sloppy"})
+
+
+def test_recipe_frees_values_after_their_last_reader():
+    from tessiq_b200.executor import Recipe, Step
+
+    recipe = Recipe(inputs=["x"])
+    recipe.steps = [Step("interpreted", "a", lambda env: env["x"] + 1, ["x"]),
+                    Step("interpreted", "b", lambda env: ("x" in env, env["a"] * 2), ["a"])]
+
+    class Out:
+        name = "b"
+
+    import torch.fx as fx
+
+    graph = fx.Graph()
+    node = graph.placeholder("b")
+    recipe.outputs = (node,)
+    recipe.finish()
+    ((x_alive, value),) = recipe.run(3)
+    assert not x_alive and value == 8     # x was dropped once step a had read it
+
+
+# ---------------------------------------------------------------------------------------------
+# on the GPU
+
+
+@pytest.mark.gpu
+def test_compiled_functions_match_the_oracle():
+    from oracle import tessiq0
+    from tessiq_b200 import backend
+
+    backend.register()
+    g = torch.Generator().manual_seed(0)
+    x, b = torch.randn(512, 4096, generator=g), torch.randn(4096, generator=g) * 0.02
+    compiled = torch.compile(chain1, backend="tessiq")
+    got = compiled(x.cuda(), b.cuda())
+    ref = tessiq0.chain_gelu_sigmoid(x, b)
+    torch.testing.assert_close(got.cpu(), ref, rtol=1e-5, atol=1e-5 * ref.abs().max().item())
+
+    a, c = torch.rand(1 << 16, generator=g) * 2 - 1, torch.rand(1 << 16, generator=g) * 2 - 1
+    got = torch.compile(chain5, backend="tessiq")(a.cuda(), c.cuda())
+    ref = tessiq0.chain_six_ops(a, c, torch.bfloat16)
+    torch.testing.assert_close(got.cpu().float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("graphed", [False, True])
+def test_decoder_block_matches_eager_cpu(graphed):
+    # config 4's shape of work at a reduced size: pre-LN decoder block, bf16, causal attention
+    from tessiq_b200.backend import compile_graph
+
+    torch.manual_seed(0)
+    d, heads, t, batch = 128, 4, 64, 8
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln1, self.ln2 = torch.nn.LayerNorm(d), torch.nn.LayerNorm(d)
+            self.qkv, self.proj = torch.nn.Linear(d, 3 * d), torch.nn.Linear(d, d)
+            self.fc, self.out = torch.nn.Linear(d, 4 * d), torch.nn.Linear(4 * d, d)
+
+        def forward(self, x):
+            b, n, _ = x.shape
+            q, k, v = self.qkv(self.ln1(x)).split(d, dim=-1)
+            q, k, v = (z.view(b, n, heads, d // heads).transpose(1, 2) for z in (q, k, v))
+            scores = (q @ k.transpose(-1, -2)) / (d // heads) ** 0.5
+            mask = torch.tril(torch.ones(n, n, dtype=torch.bool, device=x.device))
+            scores = scores.masked_fill(~mask, float("-inf"))
+            y = (torch.softmax(scores, -1) @ v).transpose(1, 2).reshape(b, n, d)
+            x = x + self.proj(y)
+            return x + self.out(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
+
+    block = Block().eval().bfloat16()
+    for p in block.parameters():
+        if p.dim() > 1:
+            torch.nn.init.normal_(p, 0, 0.02)
+    x = torch.randn(batch, t, d).bfloat16()
+    with torch.no_grad():
+        ref = block(x).float()
+        gpu_block = Block().eval().bfloat16().cuda()
+        gpu_block.load_state_dict(block.state_dict())
+        compiled = torch.compile(gpu_block, backend=lambda gm, inputs: compile_graph(gm, inputs, options={"cuda_graph": graphed}))
+        for _ in range(3):  # eager, capture, replay
+            got = compiled(x.cuda())
+        torch.testing.assert_close(got.cpu().float(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
