@@ -438,7 +438,70 @@ def other_configs(device: int, stream) -> dict:
     seconds = timed(lambda: six.launch([p, q], y, stream=raw), 10)
     out["config5_six_op_chain_f32_to_bf16"] = {"us": round(seconds * 1e6, 1), "gbs": round(n * 10 / seconds / 1e9, 1),
                                                "frac_of_measured_hbm": round(n * 10 / seconds / 1e9 / peak_hbm, 4)}
+    del p, q, y
+    out["config4_decoder_block_bf16"] = decoder_block(dev, stream)
     return out
+
+
+def decoder_block(dev: str, stream) -> dict:
+    """BASELINE config 4, the batch of 64 per GPU (weak scaling like the rest of this file):
+    LayerNorm + QKV GEMM + causal softmax attention + output projection + GELU MLP + residual
+    adds, d_model 768, 12 heads, MLP 3072, 1024 tokens, bf16 inference, compiled by this repo's
+    torch.compile backend and replayed as a CUDA graph."""
+    import torch
+    import torch.nn.functional as F
+
+    from tessiq_b200.backend import compile_graph
+
+    d, heads, tokens, batch = 768, 12, 1024, 64
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln1, self.qkv, self.proj = torch.nn.LayerNorm(d), torch.nn.Linear(d, 3 * d), torch.nn.Linear(d, d)
+            self.ln2, self.fc, self.out = torch.nn.LayerNorm(d), torch.nn.Linear(d, 4 * d), torch.nn.Linear(4 * d, d)
+
+        def forward(self, x):
+            b, n, _ = x.shape
+            q, k, v = self.qkv(self.ln1(x)).split(d, dim=-1)
+            q, k, v = (z.view(b, n, heads, d // heads).transpose(1, 2) for z in (q, k, v))
+            scores = (q @ k.transpose(-1, -2)) / (d // heads) ** 0.5
+            mask = torch.tril(torch.ones(n, n, dtype=torch.bool, device=x.device))
+            scores = scores.masked_fill(~mask, float("-inf"))
+            y = (torch.softmax(scores, -1) @ v).transpose(1, 2).reshape(b, n, d)
+            x = x + self.proj(y)
+            return x + self.out(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
+
+    torch.manual_seed(4)
+    block = Block().eval()
+    for module in block.modules():
+        if isinstance(module, torch.nn.Linear):
+            torch.nn.init.normal_(module.weight, 0, 0.02)
+            torch.nn.init.normal_(module.bias, 0, 0.02)
+    block = block.bfloat16().to(dev)
+    x = torch.randn(batch, tokens, d).bfloat16().to(dev)
+    holder = {}
+
+    def backend(gm, inputs):
+        holder["fn"] = compile_graph(gm, inputs, options={"cuda_graph": True})
+        return holder["fn"]
+
+    compiled = torch.compile(block, backend=backend)
+    with torch.no_grad(), torch.cuda.stream(stream):
+        for _ in range(3):  # eager pass, capture, first replay
+            compiled(x)
+        stream.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(5):
+            compiled(x)
+        b.record(stream)
+        stream.synchronize()
+    seconds = a.elapsed_time(b) / 5 * 1e-3
+    flop = 1_133_871_366_144  # dense flop of the six GEMMs per call; causal masking not discounted
+    recipes = getattr(holder.get("fn"), "recipes", None) or []
+    return {"ms_per_call": round(seconds * 1e3, 3), "tokens_per_s": round(batch * tokens / seconds), "tflops": round(flop / seconds / 1e12, 1),
+            "steps": recipes[0].counts() if recipes else None, "interpreted": recipes[0].interpreted if recipes else None}
 
 
 def run_profile(args) -> None:

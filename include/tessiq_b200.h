@@ -126,6 +126,12 @@ typedef struct tq_fused tq_fused;
 tq_status tq_fused_create(const char* program, tq_fused** kernel);
 tq_status tq_fused_destroy(tq_fused* kernel);
 
+/* Compiled kernels are kept on disk between processes, keyed by FNV-1a of (source, sm_100a, NVRTC
+ * version), under $TESSIQ_CACHE_DIR (default ~/.cache/tessiq_b200; empty string disables) — the
+ * reference's cubin cache (csrc/tessiq/codegen/cubin_cache.cpp:43-64,127-168). A cache that cannot
+ * be read or written is ignored. Counters since the library was loaded; any pointer may be null. */
+tq_status tq_cubin_cache_stats(int64_t* hits, int64_t* misses, int64_t* stores);
+
 /* The CUDA source the selector instantiated (for tests and reports). Copies at most `capacity`
  * bytes including the terminator; returns the full length in `*length` when non-null. */
 tq_status tq_fused_source(const tq_fused* kernel, char* buffer, size_t capacity, size_t* length);

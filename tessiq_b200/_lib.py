@@ -57,6 +57,7 @@ SIGNATURES = {
     "tq_arena_bytes": (c_size_t, [c_void_p]),
     "tq_fused_create": (c_int32, [c_char_p, POINTER(c_void_p)]),
     "tq_fused_destroy": (c_int32, [c_void_p]),
+    "tq_cubin_cache_stats": (c_int32, [POINTER(c_int64), POINTER(c_int64), POINTER(c_int64)]),
     "tq_fused_source": (c_int32, [c_void_p, c_char_p, c_size_t, POINTER(c_size_t)]),
     "tq_fused_launch": (c_int32, [c_void_p, POINTER(c_void_p), c_void_p, c_int64, POINTER(c_int64),
                                    POINTER(tq_layout), POINTER(c_double), c_int32, c_void_p]),

@@ -11,6 +11,10 @@
 // This replaces the reference's string emitter (csrc/tessiq/codegen/cuda_emitter.cpp:212-255),
 // which writes one thread per element, scalar loads and a 64-bit `%` per broadcast element.
 #include <dlfcn.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <atomic>
 
 #include <cctype>
 #include <cmath>
@@ -41,6 +45,7 @@ struct Nvrtc {
   int (*log_size)(Program, size_t*) = nullptr;
   int (*log)(Program, char*) = nullptr;
   int (*destroy)(Program*) = nullptr;
+  int (*version)(int*, int*) = nullptr;
   const char* (*error_string)(int) = nullptr;
   bool ok = false;
   std::string why;
@@ -67,7 +72,8 @@ const Nvrtc& nvrtc() {
     n.ok = bind(n.create, "nvrtcCreateProgram") && bind(n.compile, "nvrtcCompileProgram") &&
            bind(n.cubin_size, "nvrtcGetCUBINSize") && bind(n.cubin, "nvrtcGetCUBIN") &&
            bind(n.log_size, "nvrtcGetProgramLogSize") && bind(n.log, "nvrtcGetProgramLog") &&
-           bind(n.destroy, "nvrtcDestroyProgram") && bind(n.error_string, "nvrtcGetErrorString");
+           bind(n.destroy, "nvrtcDestroyProgram") && bind(n.error_string, "nvrtcGetErrorString") &&
+           bind(n.version, "nvrtcVersion");
     if (!n.ok) n.why = "libnvrtc lacks a symbol this library needs";
     return n;
   }();
@@ -828,9 +834,85 @@ struct Module {
   cudaKernel_t kernels[4] = {nullptr, nullptr, nullptr, nullptr};
 };
 
+// ---------------------------------------------------------------------------------------------
+// On-disk cubin cache, as in the reference (csrc/tessiq/codegen/cubin_cache.cpp:43-64,98-168): the
+// key is FNV-1a over the source, the architecture and the NVRTC version (the source already
+// contains the whole template library, so a library change changes the key); files are written to a
+// temporary name and renamed; a cache that cannot be read or written is not an error.
+
+std::atomic<long long> g_cache_hits{0}, g_cache_misses{0}, g_cache_stores{0};
+
+std::string cache_directory() {
+  if (const char* dir = std::getenv("TESSIQ_CACHE_DIR")) return dir[0] ? std::string(dir) : std::string();
+  if (const char* home = std::getenv("HOME")) return std::string(home) + "/.cache/tessiq_b200";
+  return std::string();
+}
+
+std::string cache_path(const std::string& source) {
+  const std::string dir = cache_directory();
+  if (dir.empty()) return std::string();
+  int major = 0, minor = 0;
+  if (nvrtc().ok) nvrtc().version(&major, &minor);
+  const std::string salt = "|sm_100a|nvrtc " + std::to_string(major) + "." + std::to_string(minor);
+  uint64_t hash = 1469598103934665603ull;
+  auto mix = [&](const std::string& text) {
+    for (unsigned char c : text) {
+      hash ^= c;
+      hash *= 1099511628211ull;
+    }
+  };
+  mix(source);
+  mix(salt);
+  char name[32];
+  snprintf(name, sizeof(name), "%016llx", static_cast<unsigned long long>(hash));
+  return dir + "/" + name + ".sm_100a.cubin";
+}
+
+bool cache_load(const std::string& path, std::string* cubin) {
+  if (path.empty()) return false;
+  FILE* file = fopen(path.c_str(), "rb");
+  if (!file) return false;
+  std::string data;
+  char buffer[65536];
+  size_t got;
+  while ((got = fread(buffer, 1, sizeof(buffer), file)) > 0) data.append(buffer, got);
+  fclose(file);
+  if (data.size() < 64 || data.compare(0, 4, "\x7f" "ELF") != 0) return false;  // a cubin is an ELF image
+  *cubin = std::move(data);
+  return true;
+}
+
+void cache_store(const std::string& path, const std::string& cubin) {
+  if (path.empty()) return;
+  const std::string dir = path.substr(0, path.rfind('/'));
+  std::string partial;
+  for (size_t i = 1; i <= dir.size(); ++i) {  // mkdir -p
+    if (i == dir.size() || dir[i] == '/') {
+      partial = dir.substr(0, i);
+      mkdir(partial.c_str(), 0755);
+    }
+  }
+  const std::string temporary = path + ".tmp." + std::to_string(static_cast<long long>(getpid()));
+  FILE* file = fopen(temporary.c_str(), "wb");
+  if (!file) return;
+  const bool written = fwrite(cubin.data(), 1, cubin.size(), file) == cubin.size();
+  fclose(file);
+  if (written && rename(temporary.c_str(), path.c_str()) == 0) {
+    ++g_cache_stores;
+  } else {
+    remove(temporary.c_str());
+  }
+}
+
 tq_status compile(const std::string& source, std::string* cubin) {
   const Nvrtc& n = nvrtc();
   TQ_REQUIRE(n.ok, TQ_EXTERNAL, "NVRTC is not available: %s", n.why.c_str());
+  const std::string cached = cache_path(source);
+  if (cache_load(cached, cubin)) {
+    ++g_cache_hits;
+    return TQ_OK;
+  }
+  ++g_cache_misses;
   Nvrtc::Program program = nullptr;
   int status = n.create(&program, source.c_str(), "tq_fused.cu", 0, nullptr, nullptr);
   TQ_REQUIRE(status == 0, TQ_EXTERNAL, "nvrtcCreateProgram failed: %s", n.error_string(status));
@@ -852,6 +934,7 @@ tq_status compile(const std::string& source, std::string* cubin) {
   }
   n.destroy(&program);
   TQ_REQUIRE(status == 0 && size > 0, TQ_EXTERNAL, "NVRTC produced no cubin: %s", n.error_string(status));
+  cache_store(cached, *cubin);
   return TQ_OK;
 }
 
@@ -906,6 +989,13 @@ tq_status tq_fused_create(const char* program_text, tq_fused** kernel) {
     fused->module = inserted.first->second;
   }
   *kernel = fused.release();
+  return TQ_OK;
+}
+
+tq_status tq_cubin_cache_stats(int64_t* hits, int64_t* misses, int64_t* stores) {
+  if (hits) *hits = tq::g_cache_hits.load();
+  if (misses) *misses = tq::g_cache_misses.load();
+  if (stores) *stores = tq::g_cache_stores.load();
   return TQ_OK;
 }
 

@@ -28,6 +28,7 @@
 // (csrc/custom_ops/gemm_bias_gelu/gemm_bias_gelu.nvcc.cu:90-158).
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -389,6 +390,268 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// The CTA-pair variant: two CTAs on neighbouring SMs (a cluster of 2) compute one 256 x 256 tile
+// with tcgen05.mma.cta_group::2. Each CTA loads its own 128 rows of A and its own 128 columns of B
+// (half the bytes per SM of the single-CTA tile), each CTA's tensor memory holds its 128 rows of the
+// accumulator, and each CTA's epilogue warps write those rows. One lane of the even CTA (the
+// leader) issues the MMAs for both; the stages' "full" barriers live in the leader and count the
+// bytes of both CTAs' TMA loads (the loads name the leader's barrier; they are plain loads, no
+// multicast); tcgen05.commit reports to the barriers of both CTAs.
+
+constexpr int kPairStages = 6;
+constexpr int kPairTileM = 256;
+constexpr uint32_t kPairBytesB = (kTileN / 2) * kTileK * 2;     // 16 KiB: this CTA's half of B
+constexpr uint32_t kPairStageBytes = kBytesA + kPairBytesB;      // 32 KiB per CTA per stage
+constexpr size_t kPairSmemBytes = 1024 + static_cast<size_t>(kPairStages) * kPairStageBytes + 2 * kTileN * sizeof(float) + 256;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+
+// The address, in the cluster's shared window, of the same shared-memory offset in CTA `rank`.
+__device__ __forceinline__ uint32_t peer_address(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  return remote;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void remote_expect_tx(uint32_t cluster_bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+// A TMA load into this CTA's shared memory whose bytes are counted on a barrier that may live in
+// the other CTA of the pair.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(columns) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t address, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+
+__device__ __forceinline__ void mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// One arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair, once every
+// tcgen05 operation this thread issued so far is done.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(both)
+               : "memory");
+}
+
+__host__ __device__ constexpr uint32_t pair_instruction_descriptor(bool bf16, bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+         ((b_mn_major ? 1u : 0u) << 16) | (static_cast<uint32_t>(kTileN >> 3) << 17) |
+         (static_cast<uint32_t>(kPairTileM >> 4) << 24);
+}
+
+template <typename T, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bias_act_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+  extern __shared__ unsigned char raw_smem[];
+  const uint32_t base = (smem_address(raw_smem) + 1023u) & ~1023u;
+  unsigned char* aligned = raw_smem + (base - smem_address(raw_smem));
+  float* bias_smem = reinterpret_cast<float*>(aligned + kPairStages * kPairStageBytes);
+  const uint32_t barriers = base + kPairStages * kPairStageBytes + 2 * kTileN * sizeof(float);
+  auto full_bar = [&](int s) { return barriers + 8u * s; };                       // used in the leader only
+  auto empty_bar = [&](int s) { return barriers + 8u * (kPairStages + s); };       // one per CTA
+  auto tmem_full_bar = [&](int a) { return barriers + 8u * (2 * kPairStages + a); };      // one per CTA
+  auto tmem_empty_bar = [&](int a) { return barriers + 8u * (2 * kPairStages + 2 + a); }; // used in the leader only
+  const uint32_t tmem_slot = barriers + 8u * (2 * kPairStages + 4);
+  volatile uint32_t* tmem_slot_pointer =
+      reinterpret_cast<volatile uint32_t*>(aligned + kPairStages * kPairStageBytes + 2 * kTileN * sizeof(float) + 8 * (2 * kPairStages + 4));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();           // 0: leader, 1: peer
+  const long long pair = blockIdx.x >> 1;
+  const long long pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      barrier_init(full_bar(s), 2);                // one arrive.expect_tx from each CTA's producer
+      barrier_init(empty_bar(s), 1);               // one commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      barrier_init(tmem_full_bar(a), 1);           // one commit
+      barrier_init(tmem_empty_bar(a), 2 * (kEpilogueThreads / 32));   // the epilogue warps of both CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_slot, kTmemColumns);
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();                              // the peer's barriers exist before anything signals them
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot_pointer;
+
+  const int k_blocks = (p.k + kTileK - 1) / kTileK;
+
+  if (warp == 0) {
+    // ---- producer (one lane in each CTA) -----------------------------------------------------
+    if (lane == 0) {
+      uint32_t iteration = 0;
+      bool alive = true;
+      for (long long tile = pair; alive && tile < p.num_tiles; tile += pairs) {
+        int batch, tile_m, tile_n;
+        tile_coordinates(tile, p, batch, tile_m, tile_n);
+        const int m0 = tile_m * kPairTileM + static_cast<int>(rank) * kTileM;
+        const int n0 = tile_n * kTileN + static_cast<int>(rank) * (kTileN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb, ++iteration) {
+          const int s = iteration % kPairStages;
+          const uint32_t phase = (iteration / kPairStages) & 1;
+          if (!barrier_wait(empty_bar(s), phase ^ 1, p.status, kWaitEmpty)) { alive = false; break; }
+          const uint32_t leader_full = peer_address(full_bar(s), 0);
+          remote_expect_tx(leader_full, kPairStageBytes);
+          const uint32_t smem_a = base + s * kPairStageBytes;
+          const uint32_t smem_b = smem_a + kBytesA;
+          const int k0 = kb * kTileK;
+          if constexpr (A_MN) {
+#pragma unroll
+            for (int i = 0; i < kTileM / 64; ++i) tma_load_3d_pair(smem_a + i * kChunkBytes, &map_a, leader_full, m0 + i * 64, k0, batch);
+          } else {
+            tma_load_3d_pair(smem_a, &map_a, leader_full, k0, m0, batch);
+          }
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int i = 0; i < kTileN / 2 / 64; ++i) tma_load_3d_pair(smem_b + i * kChunkBytes, &map_b, leader_full, n0 + i * 64, k0, batch);
+          } else {
+            tma_load_3d_pair(smem_b, &map_b, leader_full, k0, n0, batch);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: one lane of the leader CTA, for both ------------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = pair_instruction_descriptor(std::is_same_v<T, __nv_bfloat16>, A_MN, B_MN);
+      constexpr uint32_t lead_a = A_MN ? kChunkBytes : 0, lead_b = B_MN ? kChunkBytes : 0;
+      constexpr uint32_t step_a = A_MN ? 2048 : 32, step_b = B_MN ? 2048 : 32;
+      uint32_t iteration = 0;
+      uint32_t local_tile = 0;
+      bool alive = true;
+      for (long long tile = pair; alive && tile < p.num_tiles; tile += pairs, ++local_tile) {
+        const uint32_t acc = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        if (!barrier_wait(tmem_empty_bar(acc), acc_phase ^ 1, p.status, kWaitTmemEmpty)) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * kTileN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++iteration) {
+          const int s = iteration % kPairStages;
+          const uint32_t phase = (iteration / kPairStages) & 1;
+          if (!barrier_wait(full_bar(s), phase, p.status, kWaitFull)) { alive = false; break; }
+          tcgen05_fence_after();
+          const uint32_t smem_a = base + s * kPairStageBytes;
+          const uint32_t smem_b = smem_a + kBytesA;
+#pragma unroll
+          for (int kk = 0; kk < kTileK / kMmaK; ++kk) {
+            const uint64_t desc_a = smem_descriptor(smem_a + kk * step_a, lead_a, 1024);
+            const uint64_t desc_b = smem_descriptor(smem_b + kk * step_b, lead_b, 1024);
+            mma_f16_pair(tmem_d, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          mma_commit_pair(empty_bar(s));
+          if (kb == k_blocks - 1) mma_commit_pair(tmem_full_bar(acc));
+        }
+      }
+    }
+  } else {
+    // ---- epilogue: this CTA's 128 rows of the pair's tile ------------------------------------
+    const int epilogue_thread = threadIdx.x - 64;
+    const int quarter = warp & 3;
+    uint32_t local_tile = 0;
+    for (long long tile = pair; tile < p.num_tiles; tile += pairs, ++local_tile) {
+      int batch, tile_m, tile_n;
+      tile_coordinates(tile, p, batch, tile_m, tile_n);
+      const uint32_t acc = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      const int n0 = tile_n * kTileN;
+      float* bias_tile = bias_smem + acc * kTileN;
+      for (int j = epilogue_thread; j < kTileN; j += kEpilogueThreads) {
+        float value = 0.f;
+        if (p.bias != nullptr && n0 + j < p.n) value = to_compute(static_cast<const T*>(p.bias)[n0 + j]);
+        bias_tile[j] = value;
+      }
+      if (!barrier_wait(tmem_full_bar(acc), acc_phase, p.status, kWaitTmemFull)) break;
+      tcgen05_fence_after();
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
+
+      const int row = tile_m * kPairTileM + static_cast<int>(rank) * kTileM + quarter * 32 + lane;
+      T* c_row = static_cast<T*>(p.c) + static_cast<long long>(batch) * p.stride_c + static_cast<long long>(row) * p.ldc + n0;
+      const bool vector_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (p.stride_c % 8 == 0);
+#pragma unroll 1
+      for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
+        uint32_t r[32];
+        tmem_load_32(tmem_base + acc * kTileN + chunk * 32 + (static_cast<uint32_t>(quarter * 32) << 16), r);
+        tmem_load_wait();
+        if (row < p.m) {
+          const int column = n0 + chunk * 32;
+          if (vector_ok && column + 32 <= p.n) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              Vec<T, 8> out;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float value = __uint_as_float(r[v * 8 + e]) + bias_tile[chunk * 32 + v * 8 + e];
+                out.v[e] = from_compute<T, float>(activate(value, p.activation));
+              }
+              *reinterpret_cast<uint4*>(c_row + chunk * 32 + v * 8) = *reinterpret_cast<const uint4*>(&out);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              if (column + e < p.n) {
+                const float value = __uint_as_float(r[e]) + bias_tile[chunk * 32 + e];
+                c_row[chunk * 32 + e] = from_compute<T, float>(activate(value, p.activation));
+              }
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) remote_arrive(peer_address(tmem_empty_bar(acc), 0));   // tell the leader: these lanes are drained
+    }
+  }
+
+  // ---- teardown: both CTAs stay until the pair is done (the leader's MMAs read the peer's
+  // shared memory and signal its barriers) -----------------------------------------------------
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemColumns);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host
 
@@ -427,6 +690,37 @@ tq_status make_map(CUtensorMap* map, tq_dtype dtype, const void* pointer, long l
                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TQ_REQUIRE(result == CUDA_SUCCESS, TQ_UNSUPPORTED, "this operand layout cannot be described to TMA (driver code %d)", static_cast<int>(result));
   return TQ_OK;
+}
+
+template <typename T>
+tq_status launch_pair(bool a_mn, bool b_mn, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& p, int32_t device, cudaStream_t stream) {
+  auto go = [&](auto kernel) -> tq_status {
+    static std::mutex mutex;
+    {
+      std::lock_guard<std::mutex> lock(mutex);
+      TQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPairSmemBytes)));
+    }
+    long long pairs = sm_count(device) / 2;
+    if (p.num_tiles < pairs) pairs = p.num_tiles;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(pairs * 2));
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = kPairSmemBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = 2;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    TQ_CUDA(cudaLaunchKernelEx(&config, kernel, map_a, map_b, p));
+    return check_launch("gemm_bias_act_pair_kernel");
+  };
+  if (!a_mn && !b_mn) return go(gemm_bias_act_pair_kernel<T, false, false>);
+  if (!a_mn && b_mn) return go(gemm_bias_act_pair_kernel<T, false, true>);
+  if (a_mn && !b_mn) return go(gemm_bias_act_pair_kernel<T, true, false>);
+  return go(gemm_bias_act_pair_kernel<T, true, true>);
 }
 
 template <typename T>
@@ -476,10 +770,16 @@ extern "C" tq_status tq_gemm_bias_act_launch(tq_dtype dtype, tq_activation activ
   int* status = tq::device_status_word(device);
   TQ_REQUIRE(status != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
 
+  // Large problems run on CTA pairs (256 x 256 tiles, half the shared-memory operand traffic per
+  // SM); problems with at most one row of 128 x 256 tiles keep the single-CTA kernel.
+  // TQ_GEMM_PAIR=0 forces the single-CTA kernel, =1 the pair kernel.
+  bool pair = false;
+  if (const char* forced = std::getenv("TQ_GEMM_PAIR")) pair = forced[0] == '1';
   CUtensorMap map_a, map_b;
   const long long batch_a = stride_a > 0 ? batch : 1, batch_b = stride_b > 0 ? batch : 1;
+  const int b_rows = pair ? tq::kTileN / 2 : tq::kTileN;
   if (tq_status s = tq::make_map(&map_a, dtype, a, a_inner, a_outer, lda, batch_a, stride_a, 64, trans_a ? 64 : tq::kTileM)) return s;
-  if (tq_status s = tq::make_map(&map_b, dtype, b, b_inner, b_outer, ldb, batch_b, stride_b, 64, trans_b ? tq::kTileN : 64)) return s;
+  if (tq_status s = tq::make_map(&map_b, dtype, b, b_inner, b_outer, ldb, batch_b, stride_b, 64, trans_b ? b_rows : 64)) return s;
   TQ_REQUIRE(batch == 1 || (stride_a > 0 && stride_b > 0), TQ_UNSUPPORTED,
              "a batch that shares one operand (stride 0) has no kernel; fold the batch into m instead");
 
@@ -488,7 +788,8 @@ extern "C" tq_status tq_gemm_bias_act_launch(tq_dtype dtype, tq_activation activ
   p.n = static_cast<int>(n);
   p.k = static_cast<int>(k);
   p.batch = static_cast<int>(batch);
-  p.tiles_m = static_cast<int>((m + tq::kTileM - 1) / tq::kTileM);
+  const int tile_m = pair ? tq::kPairTileM : tq::kTileM;
+  p.tiles_m = static_cast<int>((m + tile_m - 1) / tile_m);
   p.tiles_n = static_cast<int>((n + tq::kTileN - 1) / tq::kTileN);
   p.num_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * batch;
   p.bias = bias;
@@ -498,6 +799,10 @@ extern "C" tq_status tq_gemm_bias_act_launch(tq_dtype dtype, tq_activation activ
   p.activation = activation;
   p.status = status;
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  if (pair) {
+    if (dtype == TQ_BF16) return tq::launch_pair<__nv_bfloat16>(trans_a != 0, trans_b == 0, map_a, map_b, p, device, cuda_stream);
+    return tq::launch_pair<__half>(trans_a != 0, trans_b == 0, map_a, map_b, p, device, cuda_stream);
+  }
   if (dtype == TQ_BF16) return tq::launch<__nv_bfloat16>(trans_a != 0, trans_b == 0, map_a, map_b, p, device, cuda_stream);
   return tq::launch<__half>(trans_a != 0, trans_b == 0, map_a, map_b, p, device, cuda_stream);
 }

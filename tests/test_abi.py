@@ -179,3 +179,32 @@ def test_product_never_imports_the_oracle():
         if path.suffix in (".py", ".cu", ".h", ".cpp"):
             text = path.read_text()
             assert "oracle" not in text, path
+
+
+def test_cubin_cache_survives_the_process(tmp_path):
+    # csrc/tessiq/codegen/cubin_cache.cpp in the reference: keyed files, atomic writes, hits on reuse
+    import subprocess
+    import sys
+
+    script = (
+        "import ctypes, sys; sys.path.insert(0, %r)\n"
+        "from tessiq_b200 import _lib\n"
+        "h = ctypes.c_void_p()\n"
+        "assert _lib.lib.tq_fused_create(b'in x f32 same\\ny = expm1 x\\nz = mul y 3.25\\nout z f32\\n', ctypes.byref(h)) == 0, _lib.last_error()\n"
+        "a, b, c = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()\n"
+        "_lib.lib.tq_cubin_cache_stats(ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))\n"
+        "print(a.value, b.value, c.value)\n" % str(ROOT)
+    )
+    env = {**__import__("os").environ, "TESSIQ_CACHE_DIR": str(tmp_path / "cache")}
+    first = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env)
+    assert first.returncode == 0, first.stderr
+    assert first.stdout.split() == ["0", "1", "1"]           # a miss, compiled, stored
+    files = list((tmp_path / "cache").glob("*.sm_100a.cubin"))
+    assert len(files) == 1 and files[0].read_bytes()[:4] == b"\x7fELF"
+    second = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env)
+    assert second.stdout.split() == ["1", "0", "0"]          # served from disk, NVRTC not run
+    files[0].write_bytes(b"garbage")                           # a damaged entry is ignored and replaced
+    third = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env)
+    assert third.stdout.split() == ["0", "1", "1"]
+    off = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env={**env, "TESSIQ_CACHE_DIR": ""})
+    assert off.stdout.split() == ["0", "1", "0"]              # disabled: compiled, nothing stored
