@@ -228,7 +228,7 @@ tq_status tq_reduce_launch(tq_reduce_op op,
  *     overlap on the GPU (different streams without an ordering between them, or two host
  *     threads on different streams) race on the array and give wrong results. Order such calls
  *     with events, or use tq_reduce_launch with separate scratch. */
-#define TQ_STATIC_SCRATCH_BYTES 524288
+#define TQ_STATIC_SCRATCH_BYTES 131072
 tq_status tq_reduce_launch_static(tq_reduce_op op,
                                   tq_dtype dtype,
                                   const void* in,

@@ -21,7 +21,7 @@ F32, F64, F16, BF16, I32, I64, BOOL = range(7)
 SUM, MEAN, AMAX, AMIN, ARGMAX = range(5)
 # tq_activation
 ACT_NONE, ACT_GELU_ERF, ACT_GELU_TANH = range(3)
-STATIC_SCRATCH_BYTES = 512 * 1024  # TQ_STATIC_SCRATCH_BYTES
+STATIC_SCRATCH_BYTES = 128 * 1024  # TQ_STATIC_SCRATCH_BYTES
 
 
 class tq_layout(ctypes.Structure):

@@ -773,7 +773,7 @@ extern "C" tq_status tq_gemm_bias_act_launch(tq_dtype dtype, tq_activation activ
   // Large problems run on CTA pairs (256 x 256 tiles, half the shared-memory operand traffic per
   // SM); problems with at most one row of 128 x 256 tiles keep the single-CTA kernel.
   // TQ_GEMM_PAIR=0 forces the single-CTA kernel, =1 the pair kernel.
-  bool pair = false;
+  bool pair = m > tq::kTileM;
   if (const char* forced = std::getenv("TQ_GEMM_PAIR")) pair = forced[0] == '1';
   CUtensorMap map_a, map_b;
   const long long batch_a = stride_a > 0 ? batch : 1, batch_b = stride_b > 0 ? batch : 1;

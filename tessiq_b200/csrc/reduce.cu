@@ -17,6 +17,7 @@
 // host device.
 #include <cooperative_groups.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <limits>
 #include <mutex>
@@ -32,8 +33,8 @@ namespace {
 constexpr int kBlock = 256;
 constexpr int kWarps = kBlock / 32;
 constexpr int kUnroll = 4;
-constexpr int kColumnUnroll = 4;  // rows in flight per thread in the columns kernel
 constexpr int kMaxCluster = 8;
+constexpr int kRingDepth = 8;   // columns kernel: rows in flight per thread (cp.async ring)
 
 // ---------------------------------------------------------------------------------------------
 // Reducers
@@ -409,7 +410,7 @@ reduce_cta_per_slice(const T* __restrict__ in, typename R::Out* __restrict__ out
 // inner > 1. Thread layout: tx = threadIdx.x % lanes_x runs along inner (VEC columns each),
 // ty = threadIdx.x / lanes_x along reduce. grid = (column tiles, split, outer); the cluster, when
 // there is one, runs along grid.y.
-template <typename T, typename R, int VEC>
+template <typename T, typename R, int VEC, bool RING>
 __global__ void __launch_bounds__(kBlock, sizeof(typename R::Acc) > 8 ? 4 : 5)
 reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long long reduce,
                long long inner, int lanes_x, int split, int cluster, int mean,
@@ -439,19 +440,54 @@ reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long
 
   if (in_range) {
     const T* base = in + slice * reduce * inner + column;
-    for (long long r = begin + ty; r < end; r += static_cast<long long>(lanes_y) * kColumnUnroll) {
-      Vec<T, VEC> x[kColumnUnroll];
+    constexpr int kBytes = static_cast<int>(sizeof(T)) * VEC;
+    constexpr int UNROLL = kUnroll;
+    if constexpr (RING && (kBytes == 4 || kBytes == 8 || kBytes == 16)) {
+      // Each thread streams its own column vector through a private ring of kRingDepth slots in
+      // shared memory with cp.async: the copies in flight cost no registers, so a thread keeps
+      // kRingDepth - 1 rows (up to 112 bytes) on their way from HBM while it folds the oldest.
+      // A slot is written and read by the same thread only, so no barrier is involved.
+      Vec<T, VEC>* ring = reinterpret_cast<Vec<T, VEC>*>(cluster_scratch + lanes_x * VEC);
+      const long long first = begin + ty;
+      const long long count = first < end ? (end - first + lanes_y - 1) / lanes_y : 0;
+      auto issue = [&](long long i) {
+        if (i < count) {
+          const uint32_t slot = static_cast<uint32_t>(__cvta_generic_to_shared(ring + (i % kRingDepth) * kBlock + threadIdx.x));
+          const T* source = base + (first + i * lanes_y) * inner;
+          if constexpr (kBytes == 16) {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(slot), "l"(source) : "memory");
+          } else {
+            asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(slot), "l"(source), "n"(kBytes) : "memory");
+          }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");   // one group per row, empty past the end
+      };
 #pragma unroll
-      for (int u = 0; u < kColumnUnroll; ++u) {
-        const long long ri = r + static_cast<long long>(u) * lanes_y;
-        if (ri < end) x[u] = load_stream<T, VEC>(base + ri * inner);
+      for (int d = 0; d < kRingDepth - 1; ++d) issue(d);
+      for (long long i = 0; i < count; ++i) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(kRingDepth - 2) : "memory");   // row i has landed
+        const Vec<T, VEC> x = ring[(i % kRingDepth) * kBlock + threadIdx.x];
+        const long long ri = first + i * lanes_y;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) R::template step<1>(local[e], x.v[e], ri);
+        issue(i + kRingDepth - 1);   // into the slot read one iteration ago
       }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+      for (long long r = begin + ty; r < end; r += static_cast<long long>(lanes_y) * UNROLL) {
+        Vec<T, VEC> x[UNROLL];
 #pragma unroll
-      for (int u = 0; u < kColumnUnroll; ++u) {
-        const long long ri = r + static_cast<long long>(u) * lanes_y;
-        if (ri < end) {
+        for (int u = 0; u < UNROLL; ++u) {
+          const long long ri = r + static_cast<long long>(u) * lanes_y;
+          if (ri < end) x[u] = load_stream<T, VEC>(base + ri * inner);
+        }
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) R::template step<1>(local[e], x[u].v[e], ri);
+        for (int u = 0; u < UNROLL; ++u) {
+          const long long ri = r + static_cast<long long>(u) * lanes_y;
+          if (ri < end) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) R::template step<1>(local[e], x[u].v[e], ri);
+          }
         }
       }
     }
@@ -538,14 +574,14 @@ reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long
   for (int item = threadIdx.x; item < items; item += kBlock) {
     if (tile_column + item >= inner) continue;
     Acc total = R::identity();
-    for (int j = 0; j < clusters; j += 8) {
-      Acc batch[8];
+    for (int j = 0; j < clusters; j += 4) {
+      Acc batch[4];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
+      for (int u = 0; u < 4; ++u) {
         if (j + u < clusters) batch[u] = load_partial(tile_partials + static_cast<long long>(j + u) * items + item);
       }
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
+      for (int u = 0; u < 4; ++u) {
         if (j + u < clusters) total = R::combine(total, batch[u]);
       }
     }
@@ -564,6 +600,7 @@ struct Plan {
   int cluster = 1;    // CTAs per thread-block cluster; divides split
   int lanes_x = 32;   // columns kernel: threads along inner
   int vec = 1;        // columns kernel: elements per thread along inner
+  bool ring = false;  // columns kernel: stream through the per-thread cp.async ring
   long long tiles = 0;        // ticketed outputs: slices, or outer * column tiles
   long long column_tiles = 0;
   size_t acc_bytes = 0;
@@ -617,7 +654,11 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
     p.vec = vec;
     long long groups = (inner + vec - 1) / vec;
     // A warp reads 32 vectors (512 bytes) of one row; the CTA's 8 warps read 8 consecutive rows.
-    int lanes = 32;
+    // Measured on B200 at [32768, 4096]: 4-byte sums and extremes are fastest with plain unrolled
+    // loads, 64 lanes along `inner` and one wave of CTAs; 2-byte types and argmax (whose state
+    // costs registers) with the cp.async ring and 32 lanes.
+    p.ring = size <= 2 || op == TQ_ARGMAX;
+    int lanes = p.ring ? 32 : 64;
     if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_LANES")) {  // tuning override: 1..256, a power of two
       const int value = std::atoi(forced);
       if (value >= 1 && value <= kBlock && (value & (value - 1)) == 0) lanes = value;
@@ -626,10 +667,12 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
     p.lanes_x = lanes;
     p.column_tiles = (groups + lanes - 1) / lanes;
     const long long base_ctas = p.column_tiles * outer;
-    // Several waves of small CTAs: measured faster than one wave of large ones, because the
-    // hardware then evens out the tail at a fine grain.
-    long long want = (target_ctas * 4 + base_ctas - 1) / base_ctas;
-    const long long per_pass = static_cast<long long>(kBlock / lanes) * kColumnUnroll;
+    // One or two waves of CTAs (all of a wave resident at once, equal work each).
+    int waves = (p.ring && !(op == TQ_ARGMAX && size <= 2)) ? 2 : 1;
+    if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_WAVES")) waves = std::max(1, std::atoi(forced));
+    if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_RING")) p.ring = forced[0] == '1';
+    long long want = (target_ctas * waves + base_ctas - 1) / base_ctas;
+    const long long per_pass = static_cast<long long>(kBlock / lanes) * kUnroll;
     long long most = reduce / per_pass;
     if (most < 1) most = 1;
     if (want > most) want = most;
@@ -713,7 +756,8 @@ tq_status run(const Plan& p, const void* in, void* out, long long outer, long lo
                  "a reduction with kept axes on both sides and %lld leading slices has no kernel", outer);
       dim3 grid(static_cast<unsigned>(p.column_tiles), p.split, static_cast<unsigned>(outer));
       auto go = [&](auto kernel, int vec) -> tq_status {
-        const size_t smem = (static_cast<size_t>(kBlock) * vec + static_cast<size_t>(p.lanes_x) * vec) * sizeof(Acc);
+        const size_t smem = (static_cast<size_t>(kBlock) * vec + static_cast<size_t>(p.lanes_x) * vec) * sizeof(Acc) +
+                            static_cast<size_t>(kRingDepth) * kBlock * vec * sizeof(T);
         if (smem > 40 * 1024) {
           TQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem)));
@@ -726,15 +770,15 @@ tq_status run(const Plan& p, const void* in, void* out, long long outer, long lo
         return check_launch("reduce_columns");
       };
       constexpr int kColumnVec = kVec > 8 ? 8 : kVec;
-      if (p.vec == 1) return go(reduce_columns<T, R, 1>, 1);
+      if (p.vec == 1) return p.ring ? go(reduce_columns<T, R, 1, true>, 1) : go(reduce_columns<T, R, 1, false>, 1);
       if constexpr (kColumnVec >= 2) {
-        if (p.vec == 2) return go(reduce_columns<T, R, 2>, 2);
+        if (p.vec == 2) return p.ring ? go(reduce_columns<T, R, 2, true>, 2) : go(reduce_columns<T, R, 2, false>, 2);
       }
       if constexpr (kColumnVec >= 4) {
-        if (p.vec == 4) return go(reduce_columns<T, R, 4>, 4);
+        if (p.vec == 4) return p.ring ? go(reduce_columns<T, R, 4, true>, 4) : go(reduce_columns<T, R, 4, false>, 4);
       }
       if constexpr (kColumnVec >= 8) {
-        if (p.vec == 8) return go(reduce_columns<T, R, 8>, 8);
+        if (p.vec == 8) return p.ring ? go(reduce_columns<T, R, 8, true>, 8) : go(reduce_columns<T, R, 8, false>, 8);
       }
       return fail(TQ_INTERNAL, "no column kernel for %d elements per thread", p.vec);
     }
