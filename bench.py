@@ -168,15 +168,20 @@ class Step:
         for op in ("sum", "mean", "amax", "argmax"):
             ops.append((f"{op}_cols", lambda op=op: K.launch_reduce(op, x, s[f"{op}_cols"], 1, ROWS, WIDTH, self.device, stream)))
         ops.append(("pack", lambda: self.pack.launch([x.t()], s["pack"], stream)))
-        # softmax / LayerNorm over the view's rows of 32768: pack, then one cluster of CTAs per row
-        ops.append(("softmax_cols", lambda: (self.pack.launch([x.t()], s["pack"], stream),
-                                            K.SoftmaxKernel(-1).launch([s["pack"]], s["softmax_cols"], stream))))
-        ops.append(("layer_norm_cols", lambda: (self.pack.launch([x.t()], s["pack"], stream),
-                                               K.LayerNormKernel(1, 1e-5).launch([s["pack"], s["gamma_t"], s["beta_t"]], s["layer_norm_cols"], stream))))
+        # softmax / LayerNorm over the view's rows of 32768 (two launches each): read in place —
+        # per-column statistics, then one transposing pass that normalises — or, where that is the
+        # faster of the two (kernel.prefers_transposed), packed first and then a cluster of CTAs per row
+        if K.prefers_transposed("softmax", x.dtype):
+            ops.append(("softmax_cols", lambda: K.launch_transposed("softmax", x, None, None, s["softmax_cols"], 1, ROWS, WIDTH, 0.0, self.device, stream)))
+        else:
+            ops.append(("softmax_cols", lambda: (self.pack.launch([x.t()], s["pack"], stream),
+                                                K.SoftmaxKernel(-1).launch([s["pack"]], s["softmax_cols"], stream))))
+        ops.append(("layer_norm_cols", lambda: K.launch_transposed("layer_norm", x, s["gamma_t"], s["beta_t"], s["layer_norm_cols"], 1, ROWS, WIDTH,
+                                                                    1e-5, self.device, stream)))
         return ops
 
     def launches_per_step(self) -> int:
-        # every operation is one kernel, except the two pack-then-row-kernel pairs per type
+        # every operation is one kernel, except the two statistics-then-transpose pairs per type
         return 2 * (13 + 2)
 
     def run(self, stream: int, time_dominant: bool = False) -> None:

@@ -292,6 +292,25 @@ tq_status tq_layer_norm_launch(tq_dtype dtype,
                                int32_t device,
                                void* stream);
 
+/* softmax and LayerNorm over the last axis of a TRANSPOSED view, without packing the view first.
+ * `in` is a packed [batch, rows, cols] tensor; the operation runs over `rows` for every (batch,
+ * column) and the result is written packed as [batch, cols, rows] — i.e. op(in.transpose(-1, -2), -1).
+ * This is what the reference reaches as pack_on_device followed by the row kernel
+ * (python/tessiq/executor.py:201 then csrc/custom_ops/softmax/softmax.cu:19-61 or
+ * csrc/tessiq/codegen/norm.cpp:22-135): four passes over the data; here it is three — per-column
+ * statistics read in place, then one transposing pass that normalises. LayerNorm's weight and bias
+ * (either may be null) have `rows` elements. dtype f32/f16/bf16; rows and cols must be multiples
+ * of 16 / sizeof(element) and the tensors 16-byte aligned, else TQ_UNSUPPORTED (pack, then use the
+ * row entry points). `workspace` must hold tq_transposed_workspace_bytes bytes. */
+tq_status tq_transposed_workspace_bytes(int32_t layer_norm, tq_dtype dtype, int64_t batch, int64_t rows,
+                                        int64_t cols, int32_t device, size_t* bytes);
+tq_status tq_softmax_transposed_launch(tq_dtype dtype, const void* in, void* out, int64_t batch, int64_t rows,
+                                       int64_t cols, void* workspace, size_t workspace_bytes, int32_t device,
+                                       void* stream);
+tq_status tq_layer_norm_transposed_launch(tq_dtype dtype, const void* in, const void* weight, const void* bias,
+                                          void* out, int64_t batch, int64_t rows, int64_t cols, double eps,
+                                          void* workspace, size_t workspace_bytes, int32_t device, void* stream);
+
 /* RMSNorm: y = x * rsqrt(mean(x^2) + eps) * weight (csrc/custom_ops/rms_norm/rms_norm.cu:15-42). */
 tq_status tq_rms_norm_launch(tq_dtype dtype,
                              const void* in,

@@ -80,6 +80,19 @@ inline bool aligned_to(const void* pointer, size_t bytes) {
 // Device-side status word (one per device), written by kernels whose bounded waits give up.
 int32_t* device_status_word(int32_t device);
 
+// reduce.cu: per-slice (max, 1/sum-exp) [kind 0] or (mean, variance) [kind 1] of a packed
+// [outer, reduce, inner] tensor, two floats per slice. Used by the transposed softmax / LayerNorm.
+size_t slice_stats_workspace_bytes(int kind, tq_dtype dtype, long long outer, long long reduce, long long inner, int32_t device);
+tq_status slice_stats_launch(int kind, tq_dtype dtype, const void* in, void* stats, long long outer, long long reduce,
+                             long long inner, void* workspace, size_t workspace_bytes, int32_t device, cudaStream_t stream);
+
+// pack.cu: out[b][c][r] = f(in[b][r][c]) for a packed in[batch, rows, cols] — the tiled transpose
+// with a per-element normalisation. `kind` 0: exp(x - stats[c].max) * stats[c].inv_sum (softmax over
+// rows); `kind` 1: (x - mean_c) * rsqrt(var_c + eps) * weight[r] + bias[r] (LayerNorm over rows).
+// Declines (TQ_UNSUPPORTED) shapes that are not multiples of the 16-byte vector width.
+tq_status transpose_normalize_launch(int kind, tq_dtype dtype, const void* in, void* out, const void* stats, const void* weight,
+                                     const void* bias, long long batch, long long rows, long long cols, float eps, cudaStream_t stream);
+
 }  // namespace tq
 
 // ---------------------------------------------------------------------------------------------

@@ -255,7 +255,103 @@ tq_status run_pack(const View& view, long long total, const void* src, void* dst
   return check_launch("pack_gather_kernel");
 }
 
+// The register-block transpose with a normalisation applied on the way: out[b][c][r] =
+// f(in[b][r][c]). KIND 0: softmax over r with per-column statistics (max, 1/sum); KIND 1:
+// LayerNorm over r with per-column (mean, variance) and weight/bias indexed by r. A thread loads
+// V vectors of V consecutive c (rows r0 .. r0+V-1), and stores V vectors of V consecutive r.
+template <typename T, int V, int KIND>
+__global__ void __launch_bounds__(256)
+transpose_normalize_kernel(const T* __restrict__ in, T* __restrict__ out, const float2* __restrict__ stats,
+                           const T* __restrict__ weight, const T* __restrict__ bias, long long rows, long long cols,
+                           long long row_tiles, long long col_tiles, float eps) {
+  constexpr int kTile = 16 * V;
+  long long tile_id = blockIdx.x;
+  const long long col_tile = tile_id % col_tiles;
+  tile_id /= col_tiles;
+  const long long row_tile = tile_id % row_tiles;
+  const long long batch = tile_id / row_tiles;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c_block = (lane & 7) + 8 * (warp & 1);
+  const int r_block = (lane >> 3) + 4 * (warp >> 1);
+  const long long c0 = col_tile * kTile + c_block * V, r0 = row_tile * kTile + r_block * V;
+  if (r0 >= rows || c0 >= cols) return;
+  const T* source = in + batch * rows * cols;
+  T* target = out + batch * rows * cols;
+
+  Vec<T, V> block[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) block[i] = load_stream<T, V>(source + (r0 + i) * cols + c0);
+
+  float first[V], second[V];   // per column c0 + j
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    const float2 st = __ldg(stats + batch * cols + c0 + j);
+    first[j] = st.x;
+    second[j] = KIND == 0 ? st.y : rsqrtf(st.y + eps);
+  }
+  float scale[V], shift[V];    // per row r0 + i (LayerNorm only); r0 is a multiple of V: one vector each
+  Vec<T, V> weights, biases;
+  if (KIND == 1 && weight != nullptr) weights = *reinterpret_cast<const Vec<T, V>*>(weight + r0);
+  if (KIND == 1 && bias != nullptr) biases = *reinterpret_cast<const Vec<T, V>*>(bias + r0);
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    scale[i] = (KIND == 1 && weight != nullptr) ? to_compute(weights.v[i]) : 1.0f;
+    shift[i] = (KIND == 1 && bias != nullptr) ? to_compute(biases.v[i]) : 0.0f;
+  }
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    Vec<T, V> line;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const float x = to_compute(block[i].v[j]);
+      float y;
+      if constexpr (KIND == 0) {
+        float e;
+        const float t = (x - first[j]) * 1.4426950408889634f;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
+        y = e * second[j];
+      } else {
+        y = (x - first[j]) * second[j] * scale[i] + shift[i];
+      }
+      line.v[i] = from_compute<T, float>(y);
+    }
+    store_stream<T, V>(target + (c0 + j) * rows + r0, line);
+  }
+}
+
+template <typename T, int KIND>
+tq_status run_transpose_normalize(const void* in, void* out, const void* stats, const void* weight, const void* bias,
+                                  long long batch, long long rows, long long cols, float eps, cudaStream_t stream) {
+  constexpr int kV = 16 / sizeof(T);
+  constexpr int kTile = 16 * kV;
+  TQ_REQUIRE(rows % kV == 0 && cols % kV == 0 && aligned_to(in, 16) && aligned_to(out, 16) && aligned_to(stats, 8) &&
+                 (weight == nullptr || aligned_to(weight, 16)) && (bias == nullptr || aligned_to(bias, 16)),
+             TQ_UNSUPPORTED, "the transposing normalisation needs extents that are multiples of %d and 16-byte-aligned tensors", kV);
+  const long long row_tiles = (rows + kTile - 1) / kTile, col_tiles = (cols + kTile - 1) / kTile;
+  const long long blocks = batch * row_tiles * col_tiles;
+  TQ_REQUIRE(blocks <= 0x7fffffffLL, TQ_UNSUPPORTED, "%lld tiles are more than a grid holds", blocks);
+  transpose_normalize_kernel<T, kV, KIND><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      static_cast<const T*>(in), static_cast<T*>(out), static_cast<const float2*>(stats), static_cast<const T*>(weight),
+      static_cast<const T*>(bias), rows, cols, row_tiles, col_tiles, eps);
+  return check_launch("transpose_normalize_kernel");
+}
+
 }  // namespace
+
+tq_status transpose_normalize_launch(int kind, tq_dtype dtype, const void* in, void* out, const void* stats, const void* weight,
+                                     const void* bias, long long batch, long long rows, long long cols, float eps, cudaStream_t stream) {
+#define TQ_TN(T)                                                                                                    \
+  return kind == 0 ? run_transpose_normalize<T, 0>(in, out, stats, weight, bias, batch, rows, cols, eps, stream)      \
+                   : run_transpose_normalize<T, 1>(in, out, stats, weight, bias, batch, rows, cols, eps, stream)
+  switch (dtype) {
+    case TQ_F32: TQ_TN(float);
+    case TQ_F16: TQ_TN(__half);
+    case TQ_BF16: TQ_TN(__nv_bfloat16);
+    default: return fail(TQ_UNSUPPORTED, "the transposing normalisation has no kernel for element type %s", dtype_name(dtype));
+  }
+#undef TQ_TN
+}
+
 }  // namespace tq
 
 extern "C" tq_status tq_pack_launch(int32_t element_bytes, int32_t rank, const int64_t* sizes,

@@ -253,6 +253,125 @@ struct ArgmaxReducer {
   }
 };
 
+
+// ---------------------------------------------------------------------------------------------
+// Two statistics of a slice that later kernels normalise with (softmax and LayerNorm over a
+// transposed view read their columns through the columns kernel below).
+
+constexpr int kOpSoftmaxStat = 100;   // (max, 1 / sum exp(x - max)) per slice
+constexpr int kOpMoments = 101;       // (mean, biased variance) per slice
+
+struct alignas(8) MaxSum {
+  float m;
+  float s;
+};
+
+__device__ __forceinline__ float stat_exp2(float t) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+  return r;
+}
+
+// Online softmax statistics: a running maximum and the sum of exp(x - maximum), rescaled whenever
+// the maximum grows. Equal maxima (also -inf with -inf) need no rescaling, which keeps a slice of
+// all -inf at (-inf, count) instead of NaN; a NaN makes the maximum and the sum NaN.
+template <typename T>
+struct SoftmaxStatReducer {
+  using C = float;
+  using Acc = MaxSum;
+  using Out = MaxSum;
+  static constexpr float kLog2e = 1.4426950408889634f;
+  __device__ static Acc identity() { return Acc{-std::numeric_limits<float>::infinity(), 0.f}; }
+  __device__ static Acc combine(Acc a, Acc b) {
+    const float m = ExtremeReducer<float, true>::combine(a.m, b.m);
+    const float scale_a = a.m == m ? 1.f : stat_exp2((a.m - m) * kLog2e);
+    const float scale_b = b.m == m ? 1.f : stat_exp2((b.m - m) * kLog2e);
+    return Acc{m, a.s * scale_a + b.s * scale_b};
+  }
+  __device__ static Acc shuffle(Acc a, int offset) { return Acc{shfl_xor(a.m, offset), shfl_xor(a.s, offset)}; }
+  template <int VEC> using Local = Acc;
+  template <int VEC> __device__ static Acc local_identity() { return identity(); }
+  // Per element: one maximum, one (rarely taken, three-instruction) rescale, one exponential. The
+  // threads of a warp walk different columns, so a branch with a long body would run for almost
+  // every element; this form keeps the rare part to a predicated multiply.
+  template <int VEC> __device__ static void step(Acc& local, T v, long long) {
+    const float x = to_compute(v);
+    const float m = ExtremeReducer<float, true>::combine(local.m, x);
+    if (m != local.m) {                       // a new maximum (or a NaN, which stays)
+      local.s *= stat_exp2((local.m - m) * kLog2e);
+      local.m = m;
+    }
+    const float t = x == m ? 0.f : (x - m) * kLog2e;   // equal infinities contribute exp(0), not NaN
+    local.s += stat_exp2(t);
+  }
+  template <int VEC> __device__ static void step_vector(Acc& local, const Vec<T, VEC>& x, long long) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) step<VEC>(local, x.v[e], 0);
+  }
+  template <int VEC> __device__ static Acc to_acc(Acc local) { return local; }
+  // A slice whose maximum is +inf is NaN throughout (inf - inf), as the plain three-pass form gives.
+  __device__ static Out finish(Acc a, long long, bool) {
+    const float inverse = a.m == std::numeric_limits<float>::infinity() ? std::numeric_limits<float>::quiet_NaN() : 1.f / a.s;
+    return Out{a.m, inverse};
+  }
+};
+
+struct alignas(16) Moments {
+  float n;
+  float mean;
+  float m2;
+  float unused;
+};
+
+// Mean and sum of squared deviations. A thread sums (x - pivot) and (x - pivot)^2 with the first
+// element it sees as the pivot (two FMAs per element, little cancellation over its few hundred
+// elements); partial results are merged with the pairwise update of Chan et al., which is stable
+// however the slice was cut.
+template <typename T>
+struct MomentsReducer {
+  using C = float;
+  using Acc = Moments;
+  struct Out {
+    float mean;
+    float variance;
+  };
+  __device__ static Acc identity() { return Acc{0.f, 0.f, 0.f, 0.f}; }
+  __device__ static Acc combine(Acc a, Acc b) {
+    if (a.n == 0.f) return b;
+    if (b.n == 0.f) return a;
+    const float n = a.n + b.n;
+    const float delta = b.mean - a.mean;
+    return Acc{n, a.mean + delta * (b.n / n), a.m2 + b.m2 + delta * delta * (a.n * b.n / n), 0.f};
+  }
+  __device__ static Acc shuffle(Acc a, int offset) {
+    return Acc{shfl_xor(a.n, offset), shfl_xor(a.mean, offset), shfl_xor(a.m2, offset), 0.f};
+  }
+  template <int VEC>
+  struct Local {
+    float pivot, s1, s2, n;
+  };
+  template <int VEC> __device__ static Local<VEC> local_identity() { return Local<VEC>{0.f, 0.f, 0.f, 0.f}; }
+  template <int VEC> __device__ static void step(Local<VEC>& local, T v, long long) {
+    const float x = to_compute(v);
+    if (local.n == 0.f) local.pivot = x;
+    const float d = x - local.pivot;
+    local.s1 += d;
+    local.s2 = fmaf(d, d, local.s2);
+    local.n += 1.f;
+  }
+  template <int VEC> __device__ static void step_vector(Local<VEC>& local, const Vec<T, VEC>& x, long long) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) step<VEC>(local, x.v[e], 0);
+  }
+  template <int VEC> __device__ static Acc to_acc(const Local<VEC>& local) {
+    if (local.n == 0.f) return identity();
+    const float shifted_mean = local.s1 / local.n;
+    const float m2 = local.s2 - local.s1 * shifted_mean;
+    return Acc{local.n, local.pivot + shifted_mean, m2 > 0.f || m2 != m2 ? m2 : 0.f, 0.f};
+  }
+  __device__ static Out finish(Acc a, long long, bool) { return Out{a.mean, a.m2 / a.n}; }
+};
+
 // Reads a partial another CTA wrote, from L2 (never a stale L1 line).
 template <typename A>
 __device__ __forceinline__ A load_partial(const A* pointer) {
@@ -620,7 +739,7 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
   const int size = dtype_size(dtype);
   const int sms = sm_count(device);
   const long long target_ctas = static_cast<long long>(sms) * 4;
-  p.acc_bytes = op == TQ_ARGMAX ? 16 : 8;  // upper bound; every Acc fits 8 bytes but Indexed
+  p.acc_bytes = (op == TQ_ARGMAX || op == kOpMoments) ? 16 : 8;  // upper bound; every other Acc fits 8 bytes
   if (inner == 1) {
     const int vec = 16 / size;
     const long long slice_bytes = reduce * size;
@@ -650,14 +769,14 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
     if (vec > 8) vec = 8;
     if (vec < 1) vec = 1;
     while (vec > 1 && inner % vec != 0) vec /= 2;
-    if (op == TQ_ARGMAX && vec > 4) vec = 4;  // its accumulators are 16 bytes each
+    if ((op == TQ_ARGMAX || op == kOpMoments) && vec > 4) vec = 4;  // their per-column state is large
     p.vec = vec;
     long long groups = (inner + vec - 1) / vec;
     // A warp reads 32 vectors (512 bytes) of one row; the CTA's 8 warps read 8 consecutive rows.
     // Measured on B200 at [32768, 4096]: 4-byte sums and extremes are fastest with plain unrolled
     // loads, 64 lanes along `inner` and one wave of CTAs; 2-byte types and argmax (whose state
     // costs registers) with the cp.async ring and 32 lanes.
-    p.ring = size <= 2 || op == TQ_ARGMAX;
+    p.ring = size <= 2 || op == TQ_ARGMAX || op >= kOpSoftmaxStat;
     int lanes = p.ring ? 32 : 64;
     if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_LANES")) {  // tuning override: 1..256, a power of two
       const int value = std::atoi(forced);
@@ -821,6 +940,13 @@ int column_vec_bytes(const void* in, long long inner, int size) {
   return bytes;
 }
 
+template <typename T>
+tq_status run_stats(int kind, const Plan& p, const void* in, void* out, long long outer, long long reduce,
+                    long long inner, void* workspace, cudaStream_t stream) {
+  if (kind == kOpSoftmaxStat) return run<T, SoftmaxStatReducer<T>>(p, in, out, outer, reduce, inner, false, workspace, stream);
+  return run<T, MomentsReducer<T>>(p, in, out, outer, reduce, inner, false, workspace, stream);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Scratch that exists without anyone allocating it, for tq_reduce_launch_static.
 //
@@ -852,6 +978,36 @@ tq_status static_scratch_for(int32_t device, void** address) {
 }
 
 }  // namespace
+
+// Per-slice statistics for the transposed softmax / LayerNorm (rownorm.cu): `kind` 0 writes
+// (max, 1 / sum exp(x - max)), `kind` 1 writes (mean, biased variance), as two floats per slice,
+// for a packed [outer, reduce, inner] input of a floating type (f32, f16, bf16).
+size_t slice_stats_workspace_bytes(int kind, tq_dtype dtype, long long outer, long long reduce, long long inner, int32_t device) {
+  size_t bytes = 0;
+  const int op = kind == 0 ? kOpSoftmaxStat : kOpMoments;
+  for (int limit = 16; limit >= dtype_size(dtype); limit /= 2) {
+    const Plan p = plan(op, dtype, outer, reduce, inner, device, limit);
+    if (p.partial_bytes + p.ticket_bytes > bytes) bytes = p.partial_bytes + p.ticket_bytes;
+  }
+  return bytes;
+}
+
+tq_status slice_stats_launch(int kind, tq_dtype dtype, const void* in, void* stats, long long outer, long long reduce,
+                             long long inner, void* workspace, size_t workspace_bytes, int32_t device, cudaStream_t stream) {
+  const int op = kind == 0 ? kOpSoftmaxStat : kOpMoments;
+  const int size = dtype_size(dtype);
+  const Plan p = plan(op, dtype, outer, reduce, inner, device, inner == 1 ? 16 : column_vec_bytes(in, inner, size));
+  const size_t need = p.partial_bytes + p.ticket_bytes;
+  TQ_REQUIRE(need == 0 || (workspace != nullptr && workspace_bytes >= need && aligned_to(workspace, 16)), TQ_INVALID_ARGUMENT,
+             "the statistics pass needs %zu bytes of 16-byte-aligned scratch and was given %zu", need, workspace_bytes);
+  switch (dtype) {
+    case TQ_F32: return run_stats<float>(op, p, in, stats, outer, reduce, inner, workspace, stream);
+    case TQ_F16: return run_stats<__half>(op, p, in, stats, outer, reduce, inner, workspace, stream);
+    case TQ_BF16: return run_stats<__nv_bfloat16>(op, p, in, stats, outer, reduce, inner, workspace, stream);
+    default: return fail(TQ_UNSUPPORTED, "slice statistics have no kernel for element type %s", dtype_name(dtype));
+  }
+}
+
 }  // namespace tq
 
 extern "C" {

@@ -565,4 +565,61 @@ tq_status tq_rms_norm_launch(tq_dtype dtype, const void* in, const void* weight,
   }
 }
 
+// softmax / LayerNorm over the last axis of the TRANSPOSED view of a packed in[batch, rows, cols]:
+// out[b][c][:] = softmax(in[b][:, c]) (or LayerNorm with weight/bias over `rows`), out packed
+// [batch, cols, rows]. Two launches: per-column statistics read in place (no packed copy is made),
+// then a tiled transpose that normalises on the way: 3 passes over the data instead of the 4 of
+// pack-then-rows. Scratch layout: [batch * cols] float2 statistics, then the reduction's scratch.
+namespace {
+
+size_t stats_bytes(long long batch, long long cols) { return (static_cast<size_t>(batch * cols) * 8 + 255) / 256 * 256; }
+
+tq_status transposed_launch(int kind, tq_dtype dtype, const void* in, const void* weight, const void* bias, void* out,
+                            int64_t batch, int64_t rows, int64_t cols, double eps, void* workspace, size_t workspace_bytes,
+                            int32_t device, void* stream) {
+  TQ_REQUIRE(batch >= 0 && rows >= 0 && cols >= 0, TQ_INVALID_ARGUMENT, "negative extent in [%lld, %lld, %lld]",
+             (long long)batch, (long long)rows, (long long)cols);
+  if (batch == 0 || cols == 0) return TQ_OK;
+  TQ_REQUIRE(rows > 0, TQ_UNSUPPORTED, "a normalisation over no elements has no kernel");
+  TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");
+  TQ_REQUIRE(dtype == TQ_F32 || dtype == TQ_F16 || dtype == TQ_BF16, TQ_UNSUPPORTED,
+             "the transposed normalisations have no kernel for element type %s", tq::dtype_name(dtype));
+  const int vec = 16 / tq::dtype_size(dtype);
+  TQ_REQUIRE(rows % vec == 0 && cols % vec == 0 && tq::aligned_to(in, 16) && tq::aligned_to(out, 16), TQ_UNSUPPORTED,
+             "the transposed normalisations need extents that are multiples of %d and 16-byte-aligned tensors", vec);
+  if (tq_status s = tq::use_device(device)) return s;
+  const size_t stats = stats_bytes(batch, cols);
+  const size_t reduce_scratch = tq::slice_stats_workspace_bytes(kind, dtype, batch, rows, cols, device);
+  TQ_REQUIRE(workspace != nullptr && workspace_bytes >= stats + reduce_scratch && tq::aligned_to(workspace, 16), TQ_INVALID_ARGUMENT,
+             "this call needs %zu bytes of 16-byte-aligned scratch and was given %zu", stats + reduce_scratch, workspace_bytes);
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  unsigned char* scratch = static_cast<unsigned char*>(workspace);
+  if (tq_status s = tq::slice_stats_launch(kind, dtype, in, scratch, batch, rows, cols, scratch + stats, reduce_scratch, device, cuda_stream)) return s;
+  return tq::transpose_normalize_launch(kind, dtype, in, out, scratch, weight, bias, batch, rows, cols, static_cast<float>(eps), cuda_stream);
+}
+
+}  // namespace
+
+tq_status tq_transposed_workspace_bytes(int32_t layer_norm, tq_dtype dtype, int64_t batch, int64_t rows, int64_t cols,
+                                        int32_t device, size_t* bytes) {
+  TQ_REQUIRE(bytes != nullptr, TQ_INVALID_ARGUMENT, "bytes out-pointer is null");
+  TQ_REQUIRE(batch >= 0 && rows >= 0 && cols >= 0, TQ_INVALID_ARGUMENT, "negative extent");
+  TQ_REQUIRE(tq::dtype_size(dtype) != 0, TQ_INVALID_ARGUMENT, "unknown element type %d", dtype);
+  *bytes = 0;
+  if (batch == 0 || cols == 0 || rows == 0) return TQ_OK;
+  *bytes = stats_bytes(batch, cols) + tq::slice_stats_workspace_bytes(layer_norm ? 1 : 0, dtype, batch, rows, cols, device);
+  return TQ_OK;
+}
+
+tq_status tq_softmax_transposed_launch(tq_dtype dtype, const void* in, void* out, int64_t batch, int64_t rows, int64_t cols,
+                                       void* workspace, size_t workspace_bytes, int32_t device, void* stream) {
+  return transposed_launch(0, dtype, in, nullptr, nullptr, out, batch, rows, cols, 0.0, workspace, workspace_bytes, device, stream);
+}
+
+tq_status tq_layer_norm_transposed_launch(tq_dtype dtype, const void* in, const void* weight, const void* bias, void* out,
+                                          int64_t batch, int64_t rows, int64_t cols, double eps, void* workspace,
+                                          size_t workspace_bytes, int32_t device, void* stream) {
+  return transposed_launch(1, dtype, in, weight, bias, out, batch, rows, cols, eps, workspace, workspace_bytes, device, stream);
+}
+
 }  // extern "C"

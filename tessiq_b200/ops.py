@@ -19,7 +19,7 @@ import torch
 
 from . import _lib
 from .kernel import (DTYPE_NAMES, FusedKernel, GemmKernel, LayerNormKernel, PackKernel, SoftmaxKernel, _device_of,
-                     _pointer, _stream, classify_read, dtype_code, launch_reduce)
+                     _pointer, _stream, classify_read, dtype_code, launch_reduce, launch_transposed, prefers_transposed)
 from ._lib import Declined, check, lib
 
 import ctypes
@@ -180,8 +180,34 @@ def argmax(x, dim=None, keepdim=False):
 # Row kernels
 
 
+def _transposed_base(x: torch.Tensor):
+    """(base, batch, rows, cols) when `x` is a packed tensor seen with its last two axes swapped:
+    base = x.transpose(-1, -2) is packed [.., rows, cols] and x is its [.., cols, rows] view."""
+    if x.dim() < 2 or x.is_contiguous() or x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        return None
+    base = x.transpose(-1, -2)
+    if not base.is_contiguous():
+        return None
+    rows, cols = base.shape[-2], base.shape[-1]
+    vec = 16 // x.element_size()
+    if rows % vec or cols % vec or rows * cols == 0 or base.data_ptr() % 16:
+        return None
+    return base, base.numel() // (rows * cols), rows, cols
+
+
 def softmax(x: torch.Tensor, dim: int = -1, half_to_float: bool = False) -> torch.Tensor:
     out_dtype = torch.float32 if half_to_float else x.dtype
+    transposed = _transposed_base(x) if (x.dim() and dim % x.dim() == x.dim() - 1 and not half_to_float and prefers_transposed("softmax", x.dtype)) else None
+    if transposed is not None:
+        # over the last axis of a transposed view: statistics in place, then one transposing pass
+        base, batch, rows, cols = transposed
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        device = _device_of([x])
+        try:
+            launch_transposed("softmax", base, None, None, out, batch, rows, cols, 0.0, device, _stream(None, device))
+            return out
+        except Declined:
+            pass
     x = contiguous(x)
     out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
     if x.numel():
@@ -209,6 +235,17 @@ def native_layer_norm(x, normalized_shape, weight, bias, eps):
 
 
 def layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5):
+    transposed = _transposed_base(x) if len(list(normalized_shape)) == 1 else None
+    if transposed is not None and all(t is None or (t.dtype == x.dtype and t.numel() == x.shape[-1]) for t in (weight, bias)):
+        base, batch, rows, cols = transposed
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        device = _device_of([x])
+        try:
+            launch_transposed("layer_norm", base, None if weight is None else contiguous(weight), None if bias is None else contiguous(bias),
+                              out, batch, rows, cols, eps, device, _stream(None, device))
+            return out
+        except Declined:
+            pass
     x = contiguous(x)
     out = torch.empty_like(x)
     if x.numel():

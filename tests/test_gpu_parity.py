@@ -615,6 +615,48 @@ def test_config_2_full_size_row_kernels(tq):
     close32(tq.softmax(xd.t(), -1)[cols.cuda()], tessiq0.softmax(x.t()[cols], -1), scale=1e-6)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(64, 128), (1000, 264), (8, 8), (4096, 512), (3, 520, 72), (2, 2, 136, 264), (20000, 8)])
+def test_softmax_and_layer_norm_over_a_transposed_view(tq, dtype, shape):
+    # the view is normalised in place: per-column statistics, then one transposing pass
+    g = torch.Generator().manual_seed(sum(shape))
+    x = (torch.randn(*shape, generator=g) * 2 + 0.3).to(dtype)
+    view, view_gpu = x.transpose(-1, -2), dev(x).transpose(-1, -2)
+    rows = shape[-2]
+    w = (1 + torch.randn(rows, generator=g) * 0.1).to(dtype)
+    b = (torch.randn(rows, generator=g) * 0.1).to(dtype)
+    got_softmax = tq.softmax(view_gpu, -1)
+    got_norm = tq.layer_norm(view_gpu, [rows], dev(w), dev(b), 1e-5)
+    got_plain = tq.layer_norm(view_gpu, [rows])
+    assert got_softmax.is_contiguous() and got_softmax.shape == view.shape
+    ref_softmax = tessiq0.softmax(view, -1)
+    ref_norm = tessiq0.native_layer_norm(view, [rows], w, b, 1e-5)[0]
+    ref_plain = tessiq0.native_layer_norm(view, [rows], None, None, 1e-5)[0]
+    if dtype == torch.float32:
+        close32(got_softmax, ref_softmax, scale=1e-6)
+        close32(got_norm, ref_norm, rtol=2e-5, scale=4e-6)
+        close32(got_plain, ref_plain, rtol=2e-5, scale=4e-6)
+    else:
+        close16(got_softmax, ref_softmax)
+        close16(got_norm, ref_norm)
+        close16(got_plain, ref_plain)
+
+
+def test_transposed_normalisations_special_columns_and_fallback(tq):
+    x = torch.randn(512, 64, generator=torch.Generator().manual_seed(5))
+    x[7, 3] = float("nan")
+    x[:, 5] = float("-inf")
+    x[100, 9] = float("inf")
+    x[:, 11] = 1e30
+    got = tq.softmax(dev(x).t(), -1).cpu()
+    torch.testing.assert_close(got, tessiq0.softmax(x.t(), -1), rtol=1e-5, atol=1e-7, equal_nan=True)
+    odd = torch.randn(130, 37, generator=torch.Generator().manual_seed(6))   # not a multiple of the vector width: packs first
+    close32(tq.softmax(dev(odd).t(), -1), tessiq0.softmax(odd.t(), -1), scale=1e-6)
+    close32(tq.layer_norm(dev(odd).t(), [130]), tessiq0.native_layer_norm(odd.t(), [130], None, None, 1e-5)[0], rtol=2e-5, scale=4e-6)
+    shifted = torch.randn(256, 64, generator=torch.Generator().manual_seed(7)) + 1000.0      # a large mean: the variance must survive it
+    close32(tq.layer_norm(dev(shifted).t(), [256]), tessiq0.native_layer_norm(shifted.t(), [256], None, None, 1e-5)[0], rtol=1e-3, scale=1e-3)
+
+
 # ---------------------------------------------------------------------------------------------
 # pack
 
