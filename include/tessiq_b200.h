@@ -383,6 +383,29 @@ tq_status tq_gemm_bias_act_launch(tq_dtype dtype,
                                   int32_t device,
                                   void* stream);
 
+/* ------------------------------------------------------------------------------------------ */
+/* Recipes: a compiled graph's launches, replayed by native code                                */
+/* Replaces the per-call Python interpreter loop of RecipeExecutor                              */
+/* (python/tessiq/executor.py:146-239), to which the reference attributes 42 % + 34 % of a call   */
+/* (README.md:333-337).                                                                         */
+
+/* Between tq_recipe_begin_recording and tq_recipe_end_recording every tq_*_launch call made by the
+ * calling thread is appended to the recipe instead of being launched: scalar arguments and the
+ * small argument arrays (sizes, strides, divisors, layouts, scalars, input pointer lists) are
+ * copied; data pointers, scratch pointers and tq_fused handles are kept as given, so those buffers
+ * and handles must outlive the recipe and stay where they are (plan them in a tq_arena). The
+ * (device, stream) given while recording are ignored. tq_recipe_run launches the recorded steps in
+ * order on its own (device, stream), stopping at the first step that fails; it makes no Python
+ * call and may itself be captured into a CUDA graph. One thread records into one recipe at a
+ * time; a recipe may be run from any thread once recording has ended. */
+typedef struct tq_recipe tq_recipe;
+tq_status tq_recipe_create(tq_recipe** recipe);
+tq_status tq_recipe_destroy(tq_recipe* recipe);
+tq_status tq_recipe_begin_recording(tq_recipe* recipe);
+tq_status tq_recipe_end_recording(tq_recipe* recipe);
+int64_t tq_recipe_steps(const tq_recipe* recipe);
+tq_status tq_recipe_run(const tq_recipe* recipe, int32_t device, void* stream);
+
 /* Reads and clears the device-side status word of `device`: 0 when every bounded wait inside
  * this library's kernels completed, otherwise a code naming the wait that gave up. Synchronises
  * `stream` first. */

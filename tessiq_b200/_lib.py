@@ -82,6 +82,12 @@ SIGNATURES = {
     "tq_gemm_bias_act_launch": (c_int32, [c_int32, c_int32, c_void_p, c_int64, c_int32, c_void_p, c_int64,
                                            c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                            c_int64, c_int64, c_int64, c_int64, c_int32, c_void_p]),
+    "tq_recipe_create": (c_int32, [POINTER(c_void_p)]),
+    "tq_recipe_destroy": (c_int32, [c_void_p]),
+    "tq_recipe_begin_recording": (c_int32, [c_void_p]),
+    "tq_recipe_end_recording": (c_int32, [c_void_p]),
+    "tq_recipe_steps": (c_int64, [c_void_p]),
+    "tq_recipe_run": (c_int32, [c_void_p, c_int32, c_void_p]),
     "tq_status_poll": (c_int32, [c_int32, c_void_p, POINTER(c_int32)]),
 }
 

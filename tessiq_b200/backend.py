@@ -29,13 +29,13 @@ import torch
 from torch import fx
 
 from . import ops
-from .executor import GraphedRecipe, Recipe, Step
+from .executor import GraphedRecipe, NativeRecipe, Recipe, Step
 from .kernel import DTYPE_NAMES, FusedKernel, classify_read
 from ._lib import Declined
 
 aten = torch.ops.aten
 
-OPTIONS = {"device", "rewrites", "math", "cuda_graph"}
+OPTIONS = {"device", "rewrites", "math", "cuda_graph", "native"}
 
 UNARY = {
     aten.abs.default: "abs", aten.neg.default: "neg", aten.relu.default: "relu", aten.sigmoid.default: "sigmoid",
@@ -333,7 +333,7 @@ def _decompositions():
 def compile_graph(gm: fx.GraphModule, example_inputs, *, mode: str | None = None, options: dict | None = None):
     """The dynamo backend. `options`: "device" (a CUDA device, default: the inputs'), "math"
     ("fast" | "precise"), "cuda_graph" (bool: replay the recipe as a CUDA graph once shapes
-    repeat), "rewrites" (accepted for compatibility; the fusions here need no rewrite names)."""
+    repeat), "native" (bool: record the launches once and replay them with tq_recipe_run), "rewrites" (accepted for compatibility; the fusions here need no rewrite names)."""
     if mode not in (None, "default"):
         raise ValueError(f"tessiq has no compile mode {mode!r}")
     options = dict(options or {})
@@ -346,16 +346,18 @@ def compile_graph(gm: fx.GraphModule, example_inputs, *, mode: str | None = None
     from torch._dynamo.backends.common import aot_autograd
     from functorch.compile import make_boxed_func
 
-    compiled = []
+    compiled, runners = [], []
 
     def compile_forward(aten_gm: fx.GraphModule, inputs):
         recipe = build_recipe(aten_gm, math_mode)
         compiled.append(recipe)
-        runner = GraphedRecipe(recipe) if options.get("cuda_graph") else recipe
+        runner = GraphedRecipe(recipe) if options.get("cuda_graph") else NativeRecipe(recipe) if options.get("native") else recipe
+        runners.append(runner)
         return make_boxed_func(lambda *args: runner.run(*args))
 
     fn = aot_autograd(fw_compiler=compile_forward, decompositions=_decompositions())(gm, example_inputs)
     fn.recipes = compiled  # for tests and reports: which kernels a graph became
+    fn.runners = runners
     return fn
 
 

@@ -98,6 +98,9 @@ extern "C" tq_status tq_batch_norm_eval_launch(tq_dtype dtype, tq_dtype param_dt
                                                const void* running_mean, const void* running_var,
                                                void* out, int64_t n, int64_t c, int64_t inner,
                                                double eps, int32_t device, void* stream) {
+  TQ_RECORD_OR_RUN([=](int32_t d, void* s) {
+    return tq_batch_norm_eval_launch(dtype, param_dtype, in, weight, bias, running_mean, running_var, out, n, c, inner, eps, d, s);
+  });
   TQ_REQUIRE(n >= 0 && c >= 0 && inner >= 0, TQ_INVALID_ARGUMENT, "negative extent in [%lld, %lld, %lld]",
              (long long)n, (long long)c, (long long)inner);
   if (n == 0 || c == 0 || inner == 0) return TQ_OK;

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <functional>
 #include <string>
 
 #include "tessiq_b200.h"
@@ -76,6 +77,18 @@ inline const char* dtype_name(tq_dtype dtype) {
 inline bool aligned_to(const void* pointer, size_t bytes) {
   return (reinterpret_cast<uintptr_t>(pointer) % bytes) == 0;
 }
+
+// Recipe recording (runtime.cu). While the calling thread records into a tq_recipe, every launch
+// entry point hands a closure of itself to record() instead of launching; tq_recipe_run calls the
+// closures in order with its own (device, stream).
+using Replay = std::function<tq_status(int32_t device, void* stream)>;
+bool recording();
+tq_status record(Replay step);
+
+#define TQ_RECORD_OR_RUN(...)                                                   \
+  do {                                                                          \
+    if (::tq::recording()) return ::tq::record(__VA_ARGS__);                    \
+  } while (0)
 
 // Device-side status word (one per device), written by kernels whose bounded waits give up.
 int32_t* device_status_word(int32_t device);

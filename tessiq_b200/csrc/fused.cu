@@ -1021,6 +1021,21 @@ tq_status tq_fused_launch(const tq_fused* kernel, const void* const* inputs, voi
                           int32_t device, void* stream) {
   TQ_REQUIRE(kernel != nullptr, TQ_INVALID_ARGUMENT, "null kernel");
   TQ_REQUIRE(elements >= 0, TQ_INVALID_ARGUMENT, "negative element count %lld", (long long)elements);
+  if (tq::recording()) {
+    // Recorded: the argument arrays are copied, the kernel handle and the data pointers are kept.
+    const tq::Program& q = kernel->program;
+    TQ_REQUIRE((q.inputs.empty() || inputs != nullptr) && (q.divisors == 0 || divisors != nullptr) &&
+                   (q.layouts == 0 || layouts != nullptr) && (q.scalars.empty() || scalars != nullptr),
+               TQ_INVALID_ARGUMENT, "a null argument array cannot be recorded");
+    std::vector<const void*> kept_inputs(inputs, inputs + q.inputs.size());
+    std::vector<int64_t> kept_divisors(divisors, divisors + q.divisors);
+    std::vector<tq_layout> kept_layouts(layouts, layouts + q.layouts);
+    std::vector<double> kept_scalars(scalars, scalars + q.scalars.size());
+    return tq::record([=](int32_t d, void* s) {
+      return tq_fused_launch(kernel, kept_inputs.data(), out, elements, kept_divisors.data(), kept_layouts.data(),
+                             kept_scalars.data(), d, s);
+    });
+  }
   if (elements == 0) return TQ_OK;
   const tq::Program& p = kernel->program;
   TQ_REQUIRE(out != nullptr && (p.inputs.empty() || inputs != nullptr), TQ_INVALID_ARGUMENT, "null input or output");

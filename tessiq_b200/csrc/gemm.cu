@@ -749,6 +749,10 @@ extern "C" tq_status tq_gemm_bias_act_launch(tq_dtype dtype, tq_activation activ
                                              const void* bias, void* c, int64_t ldc, int64_t m, int64_t n, int64_t k,
                                              int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_c,
                                              int32_t device, void* stream) {
+  TQ_RECORD_OR_RUN([=](int32_t d, void* s) {
+    return tq_gemm_bias_act_launch(dtype, activation, a, lda, trans_a, b, ldb, trans_b, bias, c, ldc, m, n, k, batch, stride_a,
+                                   stride_b, stride_c, d, s);
+  });
   TQ_REQUIRE(dtype == TQ_BF16 || dtype == TQ_F16, TQ_UNSUPPORTED,
              "the tensor-core GEMM takes bf16 or f16 operands, not %s", tq::dtype_name(dtype));
   TQ_REQUIRE(activation >= TQ_ACT_NONE && activation <= TQ_ACT_GELU_TANH, TQ_INVALID_ARGUMENT, "unknown activation %d", activation);

@@ -13,6 +13,8 @@
 //              32-bit index arithmetic when the element count allows it.
 // The result is what pack_source's kernel writes (csrc/tessiq/codegen/pack.cpp:41-94): element i
 // of the packed buffer is the view's element at the unravelled coordinates of i.
+#include <vector>
+
 #include "common.h"
 
 namespace tq {
@@ -357,6 +359,14 @@ tq_status transpose_normalize_launch(int kind, tq_dtype dtype, const void* in, v
 extern "C" tq_status tq_pack_launch(int32_t element_bytes, int32_t rank, const int64_t* sizes,
                                     const int64_t* strides, const void* src, void* dst,
                                     int32_t device, void* stream) {
+  if (tq::recording()) {
+    TQ_REQUIRE(rank >= 0 && rank <= tq::kMaxRank && (rank == 0 || (sizes != nullptr && strides != nullptr)), TQ_INVALID_ARGUMENT,
+               "a pack of rank %d cannot be recorded", rank);
+    std::vector<int64_t> kept_sizes(sizes, sizes + rank), kept_strides(strides, strides + rank);
+    return tq::record([=](int32_t d, void* s) {
+      return tq_pack_launch(element_bytes, rank, kept_sizes.data(), kept_strides.data(), src, dst, d, s);
+    });
+  }
   TQ_REQUIRE(rank >= 0, TQ_INVALID_ARGUMENT, "negative rank %d", rank);
   TQ_REQUIRE(rank <= tq::kMaxRank, TQ_UNSUPPORTED, "the pack kernel takes up to %d axes, not %d", tq::kMaxRank, rank);
   TQ_REQUIRE(rank == 0 || (sizes != nullptr && strides != nullptr), TQ_INVALID_ARGUMENT, "null sizes or strides");

@@ -1030,6 +1030,9 @@ tq_status tq_reduce_workspace_bytes(tq_reduce_op op, tq_dtype dtype, int64_t out
 tq_status tq_reduce_launch(tq_reduce_op op, tq_dtype dtype, const void* in, void* out, int64_t outer,
                            int64_t reduce, int64_t inner, void* workspace, size_t workspace_bytes,
                            int32_t device, void* stream) {
+  TQ_RECORD_OR_RUN([=](int32_t d, void* s) {
+    return tq_reduce_launch(op, dtype, in, out, outer, reduce, inner, workspace, workspace_bytes, d, s);
+  });
   if (tq_status s = tq::validate(op, dtype, outer, reduce, inner)) return s;
   if (outer == 0 || inner == 0) return TQ_OK;
   TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");

@@ -494,6 +494,7 @@ extern "C" {
 tq_status tq_softmax_launch(tq_dtype dtype, tq_dtype out_dtype, const void* in, void* out,
                             int64_t outer, int64_t extent, int64_t inner, int32_t device,
                             void* stream) {
+  TQ_RECORD_OR_RUN([=](int32_t d, void* s) { return tq_softmax_launch(dtype, out_dtype, in, out, outer, extent, inner, d, s); });
   TQ_REQUIRE(outer >= 0 && extent >= 0 && inner >= 0, TQ_INVALID_ARGUMENT,
              "negative extent in [%lld, %lld, %lld]", (long long)outer, (long long)extent, (long long)inner);
   if (outer == 0 || extent == 0 || inner == 0) return TQ_OK;
@@ -512,6 +513,9 @@ tq_status tq_softmax_launch(tq_dtype dtype, tq_dtype out_dtype, const void* in, 
 tq_status tq_layer_norm_launch(tq_dtype dtype, const void* in, const void* weight, const void* bias,
                                void* out, void* mean, void* rstd, tq_dtype stat_dtype, int64_t rows,
                                int64_t width, double eps, int32_t device, void* stream) {
+  TQ_RECORD_OR_RUN([=](int32_t d, void* s) {
+    return tq_layer_norm_launch(dtype, in, weight, bias, out, mean, rstd, stat_dtype, rows, width, eps, d, s);
+  });
   TQ_REQUIRE(rows >= 0 && width >= 0, TQ_INVALID_ARGUMENT, "negative extent in [%lld, %lld]", (long long)rows, (long long)width);
   if (rows == 0) return TQ_OK;
   TQ_REQUIRE(width > 0, TQ_UNSUPPORTED, "LayerNorm over no elements has no kernel");
@@ -542,6 +546,7 @@ tq_status tq_layer_norm_launch(tq_dtype dtype, const void* in, const void* weigh
 
 tq_status tq_rms_norm_launch(tq_dtype dtype, const void* in, const void* weight, void* out,
                              int64_t rows, int64_t width, double eps, int32_t device, void* stream) {
+  TQ_RECORD_OR_RUN([=](int32_t d, void* s) { return tq_rms_norm_launch(dtype, in, weight, out, rows, width, eps, d, s); });
   TQ_REQUIRE(rows >= 0 && width >= 0, TQ_INVALID_ARGUMENT, "negative extent in [%lld, %lld]", (long long)rows, (long long)width);
   if (rows == 0) return TQ_OK;
   TQ_REQUIRE(width > 0, TQ_UNSUPPORTED, "RMSNorm over no elements has no kernel");
@@ -613,12 +618,18 @@ tq_status tq_transposed_workspace_bytes(int32_t layer_norm, tq_dtype dtype, int6
 
 tq_status tq_softmax_transposed_launch(tq_dtype dtype, const void* in, void* out, int64_t batch, int64_t rows, int64_t cols,
                                        void* workspace, size_t workspace_bytes, int32_t device, void* stream) {
+  TQ_RECORD_OR_RUN([=](int32_t d, void* s) {
+    return tq_softmax_transposed_launch(dtype, in, out, batch, rows, cols, workspace, workspace_bytes, d, s);
+  });
   return transposed_launch(0, dtype, in, nullptr, nullptr, out, batch, rows, cols, 0.0, workspace, workspace_bytes, device, stream);
 }
 
 tq_status tq_layer_norm_transposed_launch(tq_dtype dtype, const void* in, const void* weight, const void* bias, void* out,
                                           int64_t batch, int64_t rows, int64_t cols, double eps, void* workspace,
                                           size_t workspace_bytes, int32_t device, void* stream) {
+  TQ_RECORD_OR_RUN([=](int32_t d, void* s) {
+    return tq_layer_norm_transposed_launch(dtype, in, weight, bias, out, batch, rows, cols, eps, workspace, workspace_bytes, d, s);
+  });
   return transposed_launch(1, dtype, in, weight, bias, out, batch, rows, cols, eps, workspace, workspace_bytes, device, stream);
 }
 

@@ -67,6 +67,21 @@ int32_t* device_status_word(int32_t device) {
 
 }  // namespace tq
 
+struct tq_recipe {
+  std::vector<tq::Replay> steps;
+};
+
+namespace tq {
+namespace {
+thread_local tq_recipe* g_recording = nullptr;
+}
+bool recording() { return g_recording != nullptr; }
+tq_status record(Replay step) {
+  g_recording->steps.push_back(std::move(step));
+  return TQ_OK;
+}
+}  // namespace tq
+
 struct tq_arena {
   int32_t device;
   size_t bytes;
@@ -145,6 +160,42 @@ tq_status tq_arena_at(const tq_arena* arena, size_t offset, size_t bytes, void**
 }
 
 size_t tq_arena_bytes(const tq_arena* arena) { return arena ? arena->bytes : 0; }
+
+tq_status tq_recipe_create(tq_recipe** recipe) {
+  TQ_REQUIRE(recipe != nullptr, TQ_INVALID_ARGUMENT, "recipe out-pointer is null");
+  *recipe = new tq_recipe();
+  return TQ_OK;
+}
+
+tq_status tq_recipe_destroy(tq_recipe* recipe) {
+  TQ_REQUIRE(recipe == nullptr || tq::g_recording != recipe, TQ_INVALID_ARGUMENT, "the recipe is still recording");
+  delete recipe;
+  return TQ_OK;
+}
+
+tq_status tq_recipe_begin_recording(tq_recipe* recipe) {
+  TQ_REQUIRE(recipe != nullptr, TQ_INVALID_ARGUMENT, "null recipe");
+  TQ_REQUIRE(tq::g_recording == nullptr, TQ_INVALID_ARGUMENT, "this thread is already recording a recipe");
+  tq::g_recording = recipe;
+  return TQ_OK;
+}
+
+tq_status tq_recipe_end_recording(tq_recipe* recipe) {
+  TQ_REQUIRE(recipe != nullptr && tq::g_recording == recipe, TQ_INVALID_ARGUMENT, "this thread is not recording that recipe");
+  tq::g_recording = nullptr;
+  return TQ_OK;
+}
+
+int64_t tq_recipe_steps(const tq_recipe* recipe) { return recipe ? static_cast<int64_t>(recipe->steps.size()) : 0; }
+
+tq_status tq_recipe_run(const tq_recipe* recipe, int32_t device, void* stream) {
+  TQ_REQUIRE(recipe != nullptr, TQ_INVALID_ARGUMENT, "null recipe");
+  TQ_REQUIRE(tq::g_recording == nullptr, TQ_INVALID_ARGUMENT, "a recipe cannot run while this thread is recording");
+  for (size_t i = 0; i < recipe->steps.size(); ++i) {
+    if (tq_status s = recipe->steps[i](device, stream)) return s;   // the step's own message stays in tq_last_error
+  }
+  return TQ_OK;
+}
 
 tq_status tq_status_poll(int32_t device, void* stream, int32_t* device_status) {
   TQ_REQUIRE(device_status != nullptr, TQ_INVALID_ARGUMENT, "status out-pointer is null");

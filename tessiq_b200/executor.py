@@ -59,12 +59,17 @@ class Recipe:
         """The nodes that have no kernel here and run as PyTorch operators."""
         return [step.note for step in self.steps if step.kind == "interpreted"]
 
-    def run(self, *args):
+    def run(self, *args, keep: list | None = None):
+        """Runs the steps in order. With `keep`, every value a step produces is appended to it
+        instead of being dropped after its last reader (a recorder needs the buffers to stay)."""
         if len(args) != len(self.inputs):
             raise ValueError(f"the recipe takes {len(self.inputs)} inputs, not {len(args)}")
         env = dict(zip(self.inputs, args))
         for step, dead in zip(self.steps, self._dead_after):
             env[step.output] = step.run(env)
+            if keep is not None:
+                keep.append(env[step.output])
+                continue
             for name in dead:
                 env.pop(name, None)
         return fx.node.map_arg(self.outputs, lambda n: env[n.name])
@@ -115,4 +120,57 @@ class GraphedRecipe:
         torch.cuda.current_stream().wait_stream(side)
         self._graphs[key] = (graph, static_inputs, outputs)
         graph.replay()
+        return outputs
+
+
+class NativeRecipe:
+    """Replays a recipe's kernel launches from native code (tq_recipe_run): the recipe is run once
+    per signature of input shapes with the library in recording mode, which turns every C-ABI
+    launch into a recorded step bound to the buffers that run allocated; from then on a call
+    copies the inputs into the recorded input buffers and makes ONE call into the library. Recipes
+    with interpreted steps (PyTorch operators, which the library cannot record) run eagerly."""
+
+    def __init__(self, recipe: Recipe):
+        from . import _lib
+
+        self.recipe = recipe
+        self._lib = _lib
+        self._recorded: dict = {}
+        self.recordable = not recipe.interpreted
+
+    def __del__(self):
+        for handle, *_ in getattr(self, "_recorded", {}).values():
+            self._lib.lib.tq_recipe_destroy(handle)
+
+    def steps(self, *args) -> int:
+        entry = self._recorded.get(GraphedRecipe._signature(args))
+        return 0 if entry is None else int(self._lib.lib.tq_recipe_steps(entry[0]))
+
+    def run(self, *args):
+        import ctypes
+
+        if not self.recordable or not all(isinstance(a, torch.Tensor) and a.is_cuda for a in args):
+            return self.recipe.run(*args)
+        key = GraphedRecipe._signature(args)
+        entry = self._recorded.get(key)
+        if entry is None:
+            self.recipe.run(*args)  # an eager run first: modules loaded, scratch allocated
+            static_inputs = [a.clone() for a in args]
+            handle = ctypes.c_void_p()
+            self._lib.check(self._lib.lib.tq_recipe_create(ctypes.byref(handle)))
+            kept: list = []
+            self._lib.check(self._lib.lib.tq_recipe_begin_recording(handle))
+            try:
+                outputs = self.recipe.run(*static_inputs, keep=kept)
+            finally:
+                self._lib.check(self._lib.lib.tq_recipe_end_recording(handle))
+            entry = (handle, static_inputs, outputs, kept)
+            self._recorded[key] = entry
+        handle, static_inputs, outputs, _ = entry
+        for static, arg in zip(static_inputs, args):
+            if static.data_ptr() != arg.data_ptr():
+                static.copy_(arg)
+        device = args[0].device.index if args else torch.cuda.current_device()
+        stream = torch.cuda.current_stream(device).cuda_stream
+        self._lib.check(self._lib.lib.tq_recipe_run(handle, device, ctypes.c_void_p(stream)))
         return outputs

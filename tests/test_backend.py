@@ -181,3 +181,59 @@ def test_decoder_block_matches_eager_cpu(graphed):
         for _ in range(3):  # eager, capture, replay
             got = compiled(x.cuda())
         torch.testing.assert_close(got.cpu().float(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
+
+
+def test_native_recipe_records_without_a_gpu_launch():
+    # recording turns launches into steps: no GPU is touched, so this runs anywhere
+    import ctypes
+
+    from tessiq_b200 import _lib
+
+    handle = ctypes.c_void_p()
+    _lib.check(_lib.lib.tq_recipe_create(ctypes.byref(handle)))
+    _lib.check(_lib.lib.tq_recipe_begin_recording(handle))
+    with pytest.raises(ValueError):
+        _lib.check(_lib.lib.tq_recipe_begin_recording(handle))          # one recording per thread
+    fake = ctypes.c_void_p(0x1000)
+    assert _lib.lib.tq_softmax_launch(_lib.F32, _lib.F32, fake, fake, 4, 8, 1, 0, None) == 0
+    assert _lib.lib.tq_reduce_launch(_lib.SUM, _lib.F32, fake, fake, 4, 8, 1, None, 0, 0, None) == 0
+    sizes = (ctypes.c_int64 * 2)(4, 8)
+    strides = (ctypes.c_int64 * 2)(1, 4)
+    assert _lib.lib.tq_pack_launch(4, 2, sizes, strides, fake, fake, 0, None) == 0
+    sizes[0] = 999                                                        # the arrays were copied at record time
+    _lib.check(_lib.lib.tq_recipe_end_recording(handle))
+    assert _lib.lib.tq_recipe_steps(handle) == 3
+    with pytest.raises(ValueError):
+        _lib.check(_lib.lib.tq_recipe_end_recording(handle))            # not recording any more
+    _lib.check(_lib.lib.tq_recipe_destroy(handle))
+
+
+@pytest.mark.gpu
+def test_native_recipe_replays_the_recorded_launches():
+    from oracle import tessiq0
+    from tessiq_b200.backend import compile_graph
+
+    def model(x, w, b):
+        y = F.layer_norm(x, (256,), w, b, 1e-5)
+        z = F.gelu(y + b, approximate="tanh") * torch.sigmoid(y)
+        return torch.softmax(z, -1), z.sum(-1), z.t().contiguous()
+
+    holder = {}
+
+    def backend(gm, inputs):
+        holder["fn"] = compile_graph(gm, inputs, options={"native": True})
+        return holder["fn"]
+
+    compiled = torch.compile(model, backend=backend)
+    g = torch.Generator().manual_seed(3)
+    w, b = 1 + torch.randn(256, generator=g) * 0.1, torch.randn(256, generator=g) * 0.1
+    for seed in range(3):      # eager + record, then two native replays with new data
+        x = torch.randn(512, 256, generator=torch.Generator().manual_seed(seed))
+        got = compiled(x.cuda(), w.cuda(), b.cuda())
+        y = tessiq0.native_layer_norm(x, [256], w, b, 1e-5)[0]
+        z = F.gelu(y + b, approximate="tanh") * torch.sigmoid(y)
+        torch.testing.assert_close(got[0].cpu(), torch.softmax(z, -1), rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(got[1].cpu(), z.sum(-1), rtol=1e-5, atol=1e-3)
+        torch.testing.assert_close(got[2].cpu(), z.t().contiguous(), rtol=1e-5, atol=2e-5)
+    runner = holder["fn"].runners[0]
+    assert runner.recordable and runner.steps(x.cuda(), w.cuda(), b.cuda()) >= 5
