@@ -384,6 +384,45 @@ tq_status tq_gemm_bias_act_launch(tq_dtype dtype,
                                   void* stream);
 
 /* ------------------------------------------------------------------------------------------ */
+/* Fused attention                                                                              */
+/* The reference has no attention kernel. This entry point replaces the sequence its compiler   */
+/* emits for `softmax(q @ k.T * scale [masked]) @ v` (the pattern of                            */
+/* tests/python/test_models.py:64-67): a bmm through launch_gemm                                */
+/* (csrc/tessiq/codegen/gemm.cpp:100-175), host-side mask operators, the softmax custom op      */
+/* (csrc/custom_ops/softmax/softmax.cu:19-61), a second bmm, and the pack kernels around them    */
+/* (csrc/tessiq/codegen/pack.cpp:41-94), with the [batch, heads, T, T] scores in device memory. */
+
+/* out[b,h,i,:] = sum_j softmax_j(scale * q[b,h,i,:] . k[b,h,j,:]) * v[b,h,j,:], over j <= i when
+ * causal != 0 (a lower-triangular mask aligned at the first query and the first key), else over
+ * every key. bf16 or f16; scores, maxima and sums in f32; one rounding of the result.
+ *   q is [batch, heads, q_tokens, head_dim], k and v are [batch, heads, k_tokens, head_dim], out is
+ *   [batch, heads, q_tokens, head_dim]; each is addressed through three ELEMENT strides
+ *   {batch, head, token} and its head_dim elements are contiguous — so the slices of a fused QKV
+ *   projection are read where they lie and the result can be written in [batch, token, head, dim]
+ *   order.
+ * Declines (TQ_UNSUPPORTED): head_dim != 64, a scale that is not positive and finite, q/k/v that
+ * are not 16-byte aligned or whose strides are not positive multiples of 8 elements (TMA's rules).
+ * Bounded waits report through tq_status_poll like the GEMM's. */
+tq_status tq_attention_launch(tq_dtype dtype,
+                              const void* q,
+                              const void* k,
+                              const void* v,
+                              void* out,
+                              int64_t batch,
+                              int64_t heads,
+                              int64_t q_tokens,
+                              int64_t k_tokens,
+                              int64_t head_dim,
+                              const int64_t* q_strides,
+                              const int64_t* k_strides,
+                              const int64_t* v_strides,
+                              const int64_t* out_strides,
+                              double scale,
+                              int32_t causal,
+                              int32_t device,
+                              void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
 /* Recipes: a compiled graph's launches, replayed by native code                                */
 /* Replaces the per-call Python interpreter loop of RecipeExecutor                              */
 /* (python/tessiq/executor.py:146-239), to which the reference attributes 42 % + 34 % of a call   */

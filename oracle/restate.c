@@ -14,6 +14,7 @@
  */
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #define TQ_EXPORT __attribute__((visibility("default")))
@@ -298,4 +299,37 @@ TQ_EXPORT void tq_oracle_gemm_bias_act_f64(const double* a, const double* b, con
       c[i * n + j] = acc;
     }
   }
+}
+
+/* ---- attention ------------------------------------------------------------------------------ */
+/* out[i,:] = sum_j softmax_j(scale * q[i,:] . k[j,:]) v[j,:] for ONE head in double, keys j <= i
+ * only when causal. This is the mathematical value of the node sequence the reference runs for
+ * tests/python/test_models.py:64-67 — bmm (csrc/tessiq/codegen/gemm.cpp:100-175), the scaling,
+ * an optional lower-triangular mask, softmax over the last axis with the row maximum subtracted
+ * (csrc/custom_ops/softmax/softmax.cu:19-61), bmm — without the roundings between the nodes. */
+TQ_EXPORT void tq_oracle_attention_f64(const double* q, const double* k, const double* v, double* out,
+                                       int64_t q_tokens, int64_t k_tokens, int64_t width, double scale,
+                                       int causal) {
+  double* scores = (double*)malloc(sizeof(double) * (size_t)(k_tokens > 0 ? k_tokens : 1));
+  for (int64_t i = 0; i < q_tokens; ++i) {
+    const int64_t keys = causal ? (i + 1 < k_tokens ? i + 1 : k_tokens) : k_tokens;
+    double top = -INFINITY;
+    for (int64_t j = 0; j < keys; ++j) {
+      double dot = 0.0;
+      for (int64_t d = 0; d < width; ++d) dot += q[i * width + d] * k[j * width + d];
+      scores[j] = dot * scale;
+      if (scores[j] > top) top = scores[j];
+    }
+    double total = 0.0;
+    for (int64_t j = 0; j < keys; ++j) {
+      scores[j] = exp(scores[j] - top);
+      total += scores[j];
+    }
+    for (int64_t d = 0; d < width; ++d) {
+      double acc = 0.0;
+      for (int64_t j = 0; j < keys; ++j) acc += scores[j] * v[j * width + d];
+      out[i * width + d] = acc / total;
+    }
+  }
+  free(scores);
 }

@@ -145,3 +145,18 @@ def gemm_bias_act(a, b, bias, trans_b: bool, act: int):
     lib().tq_oracle_gemm_bias_act_f64(_p(a), _p(b), _p(bias), _p(c), ctypes.c_int64(m), ctypes.c_int64(n),
                                       ctypes.c_int64(k), int(trans_b), act)
     return c
+
+
+def attention(q, k, v, scale: float, causal: bool):
+    """float64 attention of [..., tokens, width] operands, head by head."""
+    q = np.ascontiguousarray(q, dtype=np.float64)
+    k = np.ascontiguousarray(k, dtype=np.float64)
+    v = np.ascontiguousarray(v, dtype=np.float64)
+    out = np.empty_like(q)
+    q_tokens, width = q.shape[-2:]
+    k_tokens = k.shape[-2]
+    q3, k3, v3, o3 = q.reshape(-1, q_tokens, width), k.reshape(-1, k_tokens, width), v.reshape(-1, k_tokens, width), out.reshape(-1, q_tokens, width)
+    for head in range(q3.shape[0]):
+        lib().tq_oracle_attention_f64(_p(q3[head]), _p(k3[head]), _p(v3[head]), _p(o3[head]), ctypes.c_int64(q_tokens),
+                                      ctypes.c_int64(k_tokens), ctypes.c_int64(width), ctypes.c_double(scale), int(causal))
+    return out

@@ -142,3 +142,16 @@ def matmul_bias_gelu_tanh(a, b, bias):
     result is rounded after each."""
     _cpu(a, b, bias)
     return F.gelu(torch.add(torch.mm(a, b), bias), approximate="tanh")
+
+
+def attention(q, k, v, scale, causal):
+    """softmax(q @ k.T * scale [lower-triangular mask]) @ v as an imported graph runs it on
+    `tessiq:0`: bmm, mul, where, _softmax, bmm — five nodes, each rounded to the storage type
+    (the pattern of tests/python/test_models.py:64-67 with GPT-2's causal mask added)."""
+    _cpu(q, k, v)
+    scores = torch.matmul(q, k.transpose(-1, -2))
+    scores = torch.mul(scores, scale)
+    if causal:
+        allowed = torch.tril(torch.ones(q.shape[-2], k.shape[-2], dtype=torch.bool))
+        scores = torch.where(allowed, scores, float("-inf"))
+    return torch.matmul(torch.softmax(scores, -1), v)

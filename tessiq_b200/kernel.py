@@ -507,3 +507,47 @@ class GemmKernel(Kernel):
         check(lib.tq_gemm_bias_act_launch(dtype_code(a.dtype), self.activation, _pointer(a), lda, trans_a, _pointer(b),
                                           ldb, trans_b, _pointer(bias), _pointer(out), n, m, n, k, batch, stride_a,
                                           stride_b, m * n, device, ctypes.c_void_p(_stream(stream, device))))
+
+
+class AttentionKernel(Kernel):
+    """out = softmax(scale * q @ k.T [causal]) @ v in one launch, the scores kept on the SM.
+    `launch` takes [q, k, v], each [batch, heads, tokens, 64] in any layout whose last axis is
+    contiguous (views of a fused QKV projection are read in place, `packs_inputs` is False); `out`
+    is [batch, heads, tokens, 64] in any such layout too — e.g. a transposed view of a
+    [batch, tokens, heads * 64] buffer, which is what the projection after it reads. The reference
+    runs bmm, mask, softmax, bmm with the scores in memory (csrc/tessiq/codegen/gemm.cpp:100-175,
+    csrc/custom_ops/softmax/softmax.cu:19-61)."""
+
+    kind = "attention"
+    packs_inputs = False
+
+    def __init__(self, scale: float, causal: bool, inputs=None, output: str = "out"):
+        super().__init__(list(inputs) if inputs is not None else ["q", "k", "v"], output)
+        self.scale, self.causal = float(scale), bool(causal)
+
+    def output_shape(self, inputs):
+        return list(inputs[0].shape)
+
+    @staticmethod
+    def _strides(t: torch.Tensor):
+        if t.dim() != 4:
+            raise _lib.Declined("fused attention takes [batch, heads, tokens, head_dim] operands")
+        if t.shape[-1] != 1 and t.stride(-1) != 1:
+            raise _lib.Declined("the head_dim axis of an attention operand must be contiguous")
+        return (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+    def launch(self, inputs, out, stream=0):
+        self._check_count(inputs)
+        q, k, v = inputs
+        device = _device_of([q, k, v, out])
+        if not (q.dtype == k.dtype == v.dtype == out.dtype):
+            raise _lib.Declined("attention operands and result must share one element type")
+        strides = [self._strides(t) for t in (q, k, v, out)]
+        batch, heads, q_tokens, head_dim = q.shape
+        if tuple(k.shape) != tuple(v.shape) or k.shape[0] != batch or k.shape[1] != heads or k.shape[3] != head_dim:
+            raise ValueError(f"attention shapes do not agree: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}")
+        if tuple(out.shape) != tuple(q.shape):
+            raise ValueError("the attention result has the shape of q")
+        check(lib.tq_attention_launch(dtype_code(q.dtype), _pointer(q), _pointer(k), _pointer(v), _pointer(out), batch, heads,
+                                      q_tokens, k.shape[2], head_dim, *strides, self.scale, int(self.causal), device,
+                                      ctypes.c_void_p(_stream(stream, device))))

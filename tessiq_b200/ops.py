@@ -18,7 +18,7 @@ from typing import Sequence
 import torch
 
 from . import _lib
-from .kernel import (DTYPE_NAMES, FusedKernel, GemmKernel, LayerNormKernel, PackKernel, SoftmaxKernel, _device_of,
+from .kernel import (DTYPE_NAMES, AttentionKernel, FusedKernel, GemmKernel, LayerNormKernel, PackKernel, SoftmaxKernel, _device_of,
                      _pointer, _stream, classify_read, dtype_code, launch_reduce, launch_transposed, prefers_transposed)
 from ._lib import Declined, check, lib
 
@@ -334,6 +334,18 @@ def gemm_bias_gelu(x, weight, bias):
 def matmul_bias_gelu_tanh(a, b, bias):
     """gelu_tanh(a @ b + bias) with b in [k, n] layout: the `A @ B` form."""
     return _gemm(a, b, bias, "gelu_tanh")
+
+
+def attention(q, k, v, scale=None, causal=False):
+    """softmax(scale * q @ k.T [causal]) @ v for [batch, heads, tokens, 64] operands, one kernel.
+    The result is a [batch, heads, tokens, 64] view of a packed [batch, tokens, heads, 64] buffer,
+    so `.transpose(1, 2).reshape(batch, tokens, heads * 64)` after it is free."""
+    batch, heads, tokens, width = q.shape
+    scale = 1.0 / math.sqrt(width) if scale is None else scale
+    out = torch.empty([batch, tokens, heads, width], dtype=q.dtype, device=q.device).transpose(1, 2)
+    if out.numel():
+        AttentionKernel(scale, causal).launch([q, k, v], out, stream=None)
+    return out
 
 
 # ---------------------------------------------------------------------------------------------

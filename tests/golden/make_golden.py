@@ -97,6 +97,12 @@ def main() -> None:
     out["gemm_gelu_erf"] = tessiq0.gemm_bias_gelu(ga, gw, gb).numpy()
     out["gemm_gelu_tanh_bf16"] = bits(tessiq0.matmul_bias_gelu_tanh(ga.bfloat16(), gw.t().contiguous().bfloat16(), gb.bfloat16()))
 
+    # causal attention, 2 heads of 64 over 160 tokens, bf16 (drawn last so the arrays above keep their bits)
+    aq, ak, av = (torch.randn(1, 2, 160, 64, generator=g).bfloat16() for _ in range(3))
+    out["attn_q"], out["attn_k"], out["attn_v"] = bits(aq), bits(ak), bits(av)
+    out["attn_causal_bf16"] = bits(tessiq0.attention(aq, ak, av, 0.125, True))
+    out["attn_full_bf16"] = bits(tessiq0.attention(aq, ak, av, 0.125, False))
+
     target = Path(__file__).resolve().parent / "hotpath.npz"
     np.savez_compressed(target, **out)
     print(target, target.stat().st_size, "bytes,", len(out), "arrays")

@@ -1,0 +1,158 @@
+"""Parity of the fused tcgen05 attention kernel with the oracle, through the C ABI.
+
+Bars. Against the float64 value (oracle/restate.c): one rounding of the result (2^-8 relative for
+bf16, 2^-11 for f16) plus the rounding of the probabilities to the storage type before the second
+product (2^-8 / 2^-11 of sum_j p_ij |v_j|) plus 2e-5 of the largest value for ex2.approx and f32
+sums. Against the oracle's own half-precision result (five nodes, each rounded): rtol 1e-2, atol
+1e-2 * max|ref|, the tolerance stated for bf16 on this path.
+"""
+
+import ctypes
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import restate, tessiq0  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def tq():
+    if not torch.cuda.is_available():
+        pytest.fail("the gpu tests need a CUDA device")
+    from tessiq_b200 import ops
+
+    return ops
+
+
+def poll(device=0):
+    from tessiq_b200 import _lib
+
+    status = ctypes.c_int32(-1)
+    _lib.check(_lib.lib.tq_status_poll(device, None, ctypes.byref(status)))
+    return status.value
+
+
+def draw(shape, dtype, seed, spread=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * spread).to(dtype)
+
+
+def check(got, q, k, v, scale, causal):
+    dtype = q.dtype
+    ulp = 2.0**-8 if dtype == torch.bfloat16 else 2.0**-11
+    q64, k64, v64 = (t.double().numpy() for t in (q, k, v))
+    exact = restate.attention(q64, k64, v64, scale, causal)
+    weight = restate.attention(q64, k64, np.abs(v64), scale, causal)    # sum_j p_ij |v_j|
+    bound = ulp * np.abs(exact) + ulp * weight + 2e-5 * np.abs(exact).max() + 1e-30
+    error = np.abs(got.detach().cpu().double().numpy() - exact)
+    worst = (error / bound).max()
+    assert worst <= 1.0, f"error {error.max():.3e} exceeds the float64 bound by {worst:.2f}x"
+    ref = tessiq0.attention(q, k, v, scale, causal).float()
+    torch.testing.assert_close(got.detach().cpu().float(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
+
+
+SHAPES = [  # batch, heads, q_tokens, k_tokens
+    (1, 1, 128, 128), (1, 1, 256, 256), (2, 3, 256, 256), (1, 2, 1024, 1024), (1, 1, 1, 1), (1, 1, 100, 100),
+    (1, 2, 130, 130), (1, 1, 257, 300), (1, 1, 200, 333), (1, 1, 333, 200), (3, 1, 384, 512), (1, 1, 640, 129),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("causal", [True, False], ids=["causal", "full"])
+def test_attention_matches_oracle(tq, shape, causal):
+    batch, heads, tq_, tk = shape
+    q = draw((batch, heads, tq_, 64), torch.bfloat16, 1)
+    k = draw((batch, heads, tk, 64), torch.bfloat16, 2)
+    v = draw((batch, heads, tk, 64), torch.bfloat16, 3)
+    got = tq.attention(q.cuda(), k.cuda(), v.cuda(), 0.125, causal)
+    assert got.shape == q.shape
+    check(got, q, k, v, 0.125, causal)
+    assert poll() == 0
+
+
+def test_attention_golden(tq, golden):
+    q, k, v = (torch.from_numpy(golden[n].copy()).view(torch.bfloat16) for n in ("attn_q", "attn_k", "attn_v"))
+    for causal, name in ((True, "attn_causal_bf16"), (False, "attn_full_bf16")):
+        ref = torch.from_numpy(golden[name].copy()).view(torch.bfloat16).float()
+        got = tq.attention(q.cuda(), k.cuda(), v.cuda(), 0.125, causal).cpu().float()
+        torch.testing.assert_close(got, ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
+
+
+def test_attention_f16_and_large_scores(tq):
+    q = draw((1, 2, 300, 64), torch.float16, 4, spread=3.0)
+    k = draw((1, 2, 300, 64), torch.float16, 5, spread=3.0)
+    v = draw((1, 2, 300, 64), torch.float16, 6)
+    for causal in (True, False):
+        got = tq.attention(q.cuda(), k.cuda(), v.cuda(), 1.0 / 8, causal)   # scores up to ~ +-100: sharp rows
+        check(got, q, k, v, 1.0 / 8, causal)
+
+
+def test_attention_reads_a_fused_qkv_projection_in_place_and_writes_token_major(tq):
+    batch, tokens, heads = 2, 320, 4
+    qkv = draw((batch, tokens, 3 * heads * 64), torch.bfloat16, 7).cuda()
+    q, k, v = (z.view(batch, tokens, heads, 64).transpose(1, 2) for z in qkv.split(heads * 64, dim=-1))
+    assert not q.is_contiguous()
+    got = tq.attention(q, k, v, None, True)
+    # the result is a view of a packed [batch, tokens, heads, 64] buffer
+    assert got.transpose(1, 2).is_contiguous()
+    check(got, q.cpu(), k.cpu(), v.cpu(), 1.0 / 8, True)
+
+
+def test_attention_properties_at_the_decoder_block_size(tq):
+    """BASELINE config 4's attention shape (batch 64 is cut to 8 to bound the test's memory):
+    with v = 1 every output is 1 (the probabilities of a row sum to one); under the causal mask
+    row 0 returns v[0]; and shifting every key by a constant vector changes nothing for rows whose
+    query is orthogonal to it — here checked through q = 0, which gives the running mean of v."""
+    batch, heads, tokens = 8, 12, 1024
+    q = draw((batch, heads, tokens, 64), torch.bfloat16, 8).cuda()
+    k = draw((batch, heads, tokens, 64), torch.bfloat16, 9).cuda()
+    v = draw((batch, heads, tokens, 64), torch.bfloat16, 10).cuda()
+    ones = torch.ones_like(v)
+    out = tq.attention(q, k, ones, None, True).float()
+    assert (out - 1).abs().max().item() <= 2.0**-7
+    out = tq.attention(q, k, v, None, True)
+    assert torch.equal(out[:, :, 0], v[:, :, 0])
+    mean = tq.attention(torch.zeros_like(q), k, v, None, True).float()
+    running = v.float().cumsum(2) / torch.arange(1, tokens + 1, device="cuda").view(1, 1, -1, 1)
+    assert (mean - running).abs().max().item() <= 2.0**-7 * running.abs().max().item() + 2.0**-8
+    assert poll() == 0
+
+
+def test_attention_declines_what_it_has_no_kernel_for(tq):
+    from tessiq_b200._lib import Declined
+
+    q = torch.zeros(1, 1, 16, 32, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(Declined):
+        tq.attention(q, q, q, None, True)             # heads of 32 elements
+    q = torch.zeros(1, 1, 16, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(Declined):
+        tq.attention(q, q, q, -1.0, True)             # a negative scale turns the maximum into a minimum
+    with pytest.raises(Declined):
+        tq.attention(q.float(), q.float(), q.float(), None, True)
+    shifted = torch.zeros(16 * 64 + 8, dtype=torch.bfloat16, device="cuda")[4:4 + 16 * 64].view(1, 1, 16, 64)
+    with pytest.raises(Declined):
+        tq.attention(shifted, q, q, None, True)       # a base that is not 16-byte aligned
+    empty = tq.attention(q[:, :, :0], q, q, None, True)
+    assert empty.shape == (1, 1, 0, 64)
+
+
+def test_attention_under_stream_capture(tq):
+    q = draw((1, 2, 256, 64), torch.bfloat16, 11).cuda()
+    k = draw((1, 2, 256, 64), torch.bfloat16, 12).cuda()
+    v = draw((1, 2, 256, 64), torch.bfloat16, 13).cuda()
+    eager = tq.attention(q, k, v, None, True)
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        tq.attention(q, k, v, None, True)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            captured = tq.attention(q, k, v, None, True)
+    captured.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(captured, eager)

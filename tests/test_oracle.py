@@ -112,3 +112,29 @@ def test_relu_keeps_nan_and_negative_zero():
     x = np.array([float("nan"), -0.0, 0.0, -1.0, 2.0], dtype=np.float32)
     got = restate.unary("relu", x)
     assert np.isnan(got[0]) and np.signbit(got[1]) and not np.signbit(got[2]) and got[3] == 0 and got[4] == 2
+
+
+def _bf16(array):
+    return torch.from_numpy(array.copy()).view(torch.bfloat16)
+
+
+def test_attention_oracle_reproduces_golden_and_agrees_with_the_restatement(golden):
+    q, k, v = (_bf16(golden[name]) for name in ("attn_q", "attn_k", "attn_v"))
+    for causal, name in ((True, "attn_causal_bf16"), (False, "attn_full_bf16")):
+        got = tessiq0.attention(q, k, v, 0.125, causal)
+        assert np.array_equal(got.view(torch.int16).numpy(), golden[name])
+        exact = restate.attention(q.float().numpy(), k.float().numpy(), v.float().numpy(), 0.125, causal)
+        # the graph rounds to bf16 after each of its five nodes: 1e-2 of the largest value covers it
+        assert np.abs(got.float().numpy() - exact).max() <= 1e-2 * np.abs(exact).max()
+
+
+def test_restated_attention_first_row_is_the_first_value_under_a_causal_mask():
+    rng = np.random.default_rng(5)
+    q, k, v = (rng.standard_normal((3, 7, 16)) for _ in range(3))
+    out = restate.attention(q, k, v, 0.25, True)
+    assert np.allclose(out[:, 0], v[:, 0])
+    full = restate.attention(q, k, v, 0.25, False)
+    scores = np.einsum("hid,hjd->hij", q, k) * 0.25
+    weights = np.exp(scores - scores.max(-1, keepdims=True))
+    weights /= weights.sum(-1, keepdims=True)
+    assert np.allclose(full, weights @ v)
