@@ -14,6 +14,13 @@ What `compile_kernels` does in the reference (csrc/tessiq/torch/fused.cpp:470-68
     `gelu(approximate="tanh")` fuse like anything else (the reference leaves those on its host);
   * `sum/mean/amax/amin/argmax`, `_softmax`, `native_layer_norm`, `mm/addmm/bmm`, `clone` of a
     strided view map onto the reduction, row, GEMM and pack kernels;
+  * `bmm -> scale -> [mask] -> _softmax -> bmm` (and the `_scaled_dot_product_*_attention`
+    operators) become ONE fused attention kernel that reads Q, K and V where the projection left
+    them; `addmm -> gelu` becomes the GEMM with the activation in its epilogue; the reference
+    has rewrite patterns for the second (csrc/custom_ops/gemm_bias_gelu_tanh/*.pattern.tsr) and
+    nothing for the first;
+  * nodes that depend on no input (a causal mask built from `arange`) are computed once and kept;
+    nodes nobody reads after these rewrites are dropped;
   * views are metadata; whatever is left runs as the PyTorch operator on the same GPU and is
     counted in `Recipe.interpreted` (the reference counts its host fallbacks the same way).
 """
@@ -27,6 +34,7 @@ from typing import Any, Callable
 
 import torch
 from torch import fx
+from torch.utils._python_dispatch import _disable_current_modes
 
 from . import ops
 from .executor import GraphedRecipe, NativeRecipe, Recipe, Step
@@ -107,10 +115,11 @@ class Group:
     members: list[fx.Node] = field(default_factory=list)
 
 
-def _fusion_groups(graph: fx.Graph) -> dict[fx.Node, Group]:
+def _fusion_groups(graph: fx.Graph, exclude: set | None = None) -> dict[fx.Node, Group]:
     """root node -> its group. A node absorbs each elementwise producer that it alone reads and
     that has its shape (a broadcast producer needs its own, smaller loop)."""
-    elementwise = {n for n in graph.nodes if _elementwise_name(n) and _supported_dtypes(n)}
+    exclude = exclude or set()
+    elementwise = {n for n in graph.nodes if n not in exclude and _elementwise_name(n) and _supported_dtypes(n)}
     owner: dict[fx.Node, fx.Node] = {n: n for n in elementwise}
 
     def find(n):
@@ -198,14 +207,337 @@ def _program_for(group: Group, math_mode: str) -> tuple[str, list[fx.Node]]:
 
 
 # ---------------------------------------------------------------------------------------------
+# Graph rewrites: fused attention, GEMM + activation, constants, dead nodes
+
+_SHAPE_ONLY = {aten.view.default, aten._unsafe_view.default, aten.reshape.default, aten.expand.default, aten.clone.default,
+               aten.alias.default, aten.detach.default}
+
+
+def _shape(node: fx.Node) -> tuple:
+    value = node.meta.get("val")
+    return tuple(value.shape) if isinstance(value, torch.Tensor) else ()
+
+
+def _peel(node: fx.Node, path: list[fx.Node]) -> fx.Node:
+    """Walks up through nodes that only regroup the leading axes (view, expand to the same
+    shape, clone), appending them to `path`; stops at the first node that does anything else."""
+    while node.op == "call_function" and node.target in _SHAPE_ONLY:
+        source = node.args[0]
+        if not _is_tensor_node(source):
+            break
+        a, b = _shape(source), _shape(node)
+        if len(a) < 2 or len(b) < 2 or a[-2:] != b[-2:] or math.prod(a) != math.prod(b):
+            break
+        path.append(node)
+        node = source
+    return node
+
+
+def _constant_nodes(graph: fx.Graph) -> set[fx.Node]:
+    """Nodes whose value depends on no graph input."""
+    constant: set[fx.Node] = set()
+    for node in graph.nodes:
+        if node.op == "call_function" and all(a in constant for a in node.all_input_nodes) and \
+                not getattr(node.target, "_nondeterministic_seeded", False) and "rand" not in str(node.target):
+            constant.add(node)
+    return constant
+
+
+def _evaluate_constant(node: fx.Node, cache: dict) -> Any:
+    """The value of a constant node, computed on the CPU at compile time (masks are small)."""
+    if node not in cache:
+        args = fx.node.map_arg(node.args, lambda n: _evaluate_constant(n, cache))
+        kwargs = dict(fx.node.map_arg(node.kwargs, lambda n: _evaluate_constant(n, cache)))
+        if "device" in kwargs:
+            kwargs["device"] = "cpu"
+        cache[node] = node.target(*args, **kwargs)
+    return cache[node]
+
+
+def _mask_kind(allowed: torch.Tensor, q_tokens: int, k_tokens: int) -> str | None:
+    """"full" when every key is allowed, "causal" for the lower triangle, None for anything else."""
+    if allowed.dtype != torch.bool:
+        return None
+    while allowed.dim() > 2 and allowed.shape[0] == 1:
+        allowed = allowed[0]
+    if allowed.dim() > 2:
+        return None
+    allowed = allowed.expand(q_tokens, k_tokens)
+    if bool(allowed.all()):
+        return "full"
+    if torch.equal(allowed, torch.tril(torch.ones(q_tokens, k_tokens, dtype=torch.bool))):
+        return "causal"
+    return None
+
+
+@dataclass
+class Attention:
+    anchor: fx.Node            # the node whose value the fused kernel produces
+    q: fx.Node
+    k: fx.Node
+    v: fx.Node
+    scale: float
+    causal: bool
+    absorbed: list[fx.Node]    # every node between q/k/v and the anchor
+
+
+class _NoMatch(Exception):
+    """Why a rewrite does not apply; kept in `Recipe.notes`."""
+
+
+def _match_attention(last: fx.Node, constant: set[fx.Node], folded: dict) -> Attention:
+    """`last` is the second bmm of softmax(scale * q @ k.T [mask]) @ v. Returns the match when the
+    whole pattern hangs on this node alone (no intermediate value has another reader); raises
+    `_NoMatch` with the reason otherwise."""
+    if last.target is not aten.bmm.default or _shape(last) == ():
+        raise _NoMatch("not a bmm")
+    path: list[fx.Node] = []
+    softmax = _peel(last.args[0], path)
+    if softmax.op != "call_function" or softmax.target is not aten._softmax.default:
+        raise _NoMatch("the first operand is not a softmax")
+    width = len(_shape(softmax))
+    if softmax.args[1] not in (-1, width - 1) or softmax.args[2]:
+        raise _NoMatch("the softmax is not over the key axis")
+    path.append(softmax)
+    scores = softmax.args[0]
+    causal = False
+    if scores.op == "call_function" and scores.target is aten.where.self:
+        condition, a, b = scores.args
+        if condition not in constant:
+            raise _NoMatch(f"the mask {condition.name} depends on an input")
+
+        def is_minus_infinity(value) -> bool:
+            if isinstance(value, (int, float)):
+                return value == float("-inf")
+            if isinstance(value, fx.Node) and value in constant:
+                tensor = _evaluate_constant(value, folded)
+                return isinstance(tensor, torch.Tensor) and tensor.numel() == 1 and float(tensor) == float("-inf")
+            return False
+
+        q_tokens, k_tokens = _shape(softmax)[-2:]
+        allowed = _evaluate_constant(condition, folded)
+        if not isinstance(allowed, torch.Tensor):
+            raise _NoMatch("the mask is not a tensor")
+        if is_minus_infinity(a) and _is_tensor_node(b):
+            allowed, inner = ~allowed if allowed.dtype == torch.bool else allowed, b
+        elif is_minus_infinity(b) and _is_tensor_node(a):
+            inner = a
+        else:
+            raise _NoMatch("the masked value is not -inf")
+        kind = _mask_kind(allowed, q_tokens, k_tokens)
+        if kind is None:
+            raise _NoMatch("the mask is neither empty nor lower-triangular")
+        causal = kind == "causal"
+        path.append(scores)
+        scores = inner
+    scale = 1.0
+    if scores.op == "call_function" and scores.target in (aten.div.Tensor, aten.mul.Tensor, aten.div.Scalar, aten.mul.Scalar) and \
+            isinstance(scores.args[1], (int, float)) and not scores.kwargs.get("rounding_mode"):
+        scale = 1.0 / scores.args[1] if scores.target in (aten.div.Tensor, aten.div.Scalar) else float(scores.args[1])
+        path.append(scores)
+        scores = scores.args[0]
+    first = _peel(scores, path)
+    if first.op != "call_function" or first.target is not aten.bmm.default:
+        raise _NoMatch(f"the scores come from {first.target}, not a bmm")
+    path.append(first)
+    q = _peel(first.args[0], path)
+    transposed = _peel(first.args[1], path)
+    if transposed.op != "call_function" or transposed.target not in (aten.permute.default, aten.transpose.int):
+        raise _NoMatch(f"the keys reach the bmm through {transposed.target}, not a transpose")
+    rank = len(_shape(transposed))
+    if transposed.target is aten.permute.default:
+        order = [d % rank for d in transposed.args[1]]
+        if order != list(range(rank - 2)) + [rank - 1, rank - 2]:
+            raise _NoMatch("the keys are permuted, not transposed")
+    elif {transposed.args[1] % rank, transposed.args[2] % rank} != {rank - 1, rank - 2}:
+        raise _NoMatch("the keys are not transposed over their last two axes")
+    path.append(transposed)
+    k = transposed.args[0]
+    v = _peel(last.args[1], path)
+    shapes = [_shape(n) for n in (q, k, v)]
+    if any(len(sh) not in (3, 4) for sh in shapes) or len({len(sh) for sh in shapes}) != 1:
+        raise _NoMatch(f"operand ranks {shapes}")
+    if shapes[1] != shapes[2] or shapes[0][:-2] != shapes[1][:-2] or shapes[0][-1] != shapes[1][-1]:
+        raise _NoMatch(f"operand shapes {shapes}")
+    dtypes = {n.meta["val"].dtype for n in (q, k, v, last)}
+    if len(dtypes) != 1 or dtypes.pop() not in (torch.bfloat16, torch.float16) or shapes[0][-1] != 64 or not scale > 0:
+        raise _NoMatch(f"no kernel for heads of {shapes[0][-1]} elements in this type, or a scale that is not positive")
+    if any(len(n.users) != 1 for n in path):          # an intermediate value has another reader
+        raise _NoMatch("an intermediate value has another reader: " + ", ".join(n.name for n in path if len(n.users) != 1))
+    # the result: [batch * heads, tokens, 64]; when its only reader regroups it to
+    # [batch, heads, tokens, 64], produce that directly (the kernel writes token-major rows)
+    anchor, absorbed = last, list(path)
+    if len(shapes[0]) == 4 and len(last.users) == 1:
+        reader = next(iter(last.users))
+        if reader.op == "call_function" and reader.target in (aten.view.default, aten._unsafe_view.default, aten.reshape.default) and \
+                _shape(reader) == shapes[0]:
+            anchor, absorbed = reader, absorbed + [last]
+    return Attention(anchor, q, k, v, scale, causal, absorbed)
+
+
+def _sdpa_targets() -> dict:
+    """ATen's fused attention operators -> (position of attn_bias or None, position of is_causal)."""
+    table = {}
+    for name, bias_at, causal_at in (("_scaled_dot_product_flash_attention", None, 4),
+                                     ("_scaled_dot_product_flash_attention_for_cpu", None, 4),
+                                     ("_scaled_dot_product_efficient_attention", 3, 6),
+                                     ("_scaled_dot_product_cudnn_attention", 3, 6)):
+        packet = getattr(aten, name, None)
+        if packet is not None and hasattr(packet, "default"):
+            table[packet.default] = (bias_at, causal_at)
+    return table
+
+
+SDPA = _sdpa_targets()
+
+
+def _attention_step(match: Attention) -> Step:
+    scale, causal = match.scale, match.causal
+    names = [match.q.name, match.k.name, match.v.name]
+    regrouped = match.anchor.target is not aten.bmm.default    # the anchor is the [batch, heads, tokens, 64] view of the bmm
+
+    def run(env):
+        q, k, v = (env[name] for name in names)
+        folded = q.dim() == 3
+        if folded:
+            q, k, v = q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0)
+        try:
+            out = ops.attention(q, k, v, scale, causal)
+        except Declined:  # a layout TMA cannot describe: packed copies can always be described
+            out = ops.attention(ops.contiguous(q), ops.contiguous(k), ops.contiguous(v), scale, causal)
+        if folded:
+            return out[0]
+        return out if regrouped else out.reshape(-1, out.shape[2], out.shape[3])
+
+    return Step("attention", match.anchor.name, run, names)
+
+
+def _sdpa_step(node: fx.Node) -> Step | None:
+    """One of ATen's fused attention operators, when only its first result is read and it asks for
+    nothing the kernel lacks (dropout, a bias, a head width other than 64)."""
+    bias_at, causal_at = SDPA[node.target]
+    args = list(node.args)
+    q, k, v = args[:3]
+    if bias_at is not None and len(args) > bias_at and args[bias_at] is not None:
+        return None
+    dropout_at = causal_at - 1
+    if len(args) > dropout_at and args[dropout_at] not in (0, 0.0) or node.kwargs.get("dropout_p", 0.0) not in (0, 0.0):
+        return None
+    causal = bool(args[causal_at]) if len(args) > causal_at else bool(node.kwargs.get("is_causal", False))
+    shapes = [_shape(n) for n in (q, k, v)]
+    if any(len(sh) != 4 for sh in shapes) or shapes[0][-1] != 64 or shapes[1] != shapes[2] or shapes[0][:2] != shapes[1][:2]:
+        return None
+    if q.meta["val"].dtype not in (torch.bfloat16, torch.float16):
+        return None
+    for user in node.users:
+        if not (user.op == "call_function" and user.target is operator.getitem and (user.args[1] == 0 or not user.users)):
+            return None
+    scale = node.kwargs.get("scale")
+    scale = 1.0 / math.sqrt(shapes[0][-1]) if scale is None else float(scale)
+    if not scale > 0:
+        return None
+    names = [q.name, k.name, v.name]
+    count = len(node.meta["val"]) if isinstance(node.meta.get("val"), (tuple, list)) else 1
+
+    def run(env):
+        a, b, c = (env[name] for name in names)
+        try:
+            out = ops.attention(a, b, c, scale, causal)
+        except Declined:
+            out = ops.attention(ops.contiguous(a), ops.contiguous(b), ops.contiguous(c), scale, causal)
+        return (out,) + (None,) * (count - 1)
+
+    return Step("attention", node.name, run, names)
+
+
+def _match_gemm_activation(node: fx.Node) -> tuple[fx.Node, str] | None:
+    """`node` is a gelu whose operand is (a regrouping view of) an addmm nobody else reads: returns
+    (addmm, activation). The addmm then runs with the activation in its epilogue and the gelu
+    node hands its operand through."""
+    if node.target is not aten.gelu.default or not _is_tensor_node(node.args[0]):
+        return None
+    path: list[fx.Node] = []
+    source = node.args[0]
+    while source.op == "call_function" and source.target in (aten.view.default, aten._unsafe_view.default, aten.reshape.default):
+        path.append(source)
+        source = source.args[0]
+    if source.op != "call_function" or source.target is not aten.addmm.default:
+        return None
+    bias = source.args[0].meta.get("val")
+    if source.kwargs.get("beta", 1) != 1 or source.kwargs.get("alpha", 1) != 1 or bias is None or bias.dim() != 1:
+        return None
+    if source.meta["val"].dtype not in (torch.bfloat16, torch.float16):
+        return None
+    if any(len(n.users) != 1 for n in path + [source]):
+        return None
+    return source, "gelu_tanh" if node.kwargs.get("approximate", "none") == "tanh" else "gelu_erf"
 
 
 def build_recipe(gm: fx.GraphModule, math_mode: str = "fast") -> Recipe:
     """Turns an ATen-level FX graph into a recipe of kernel steps."""
     graph = gm.graph
-    groups = _fusion_groups(graph)
+    constant = _constant_nodes(graph)
+    folded: dict = {}
+    groups = _fusion_groups(graph, exclude=constant)
     member_of = {m: g for g in groups.values() for m in g.members}
+
+    # rewrites: which node stands for a whole pattern, and which nodes that pattern swallows
+    attention_at: dict[fx.Node, Attention] = {}
+    gemm_act_at: dict[fx.Node, str] = {}        # addmm -> the activation in its epilogue
+    passes_through: set[fx.Node] = set()       # the activation nodes those epilogues made redundant
+    absorbed: set[fx.Node] = set()
+    notes: list[str] = []
+    for node in graph.nodes:
+        if node.op != "call_function" or node in absorbed:
+            continue
+        if node.target is aten.bmm.default:
+            try:
+                # the compiler runs inside AOTAutograd's fake-tensor mode; reading the mask needs real values
+                with _disable_current_modes():
+                    match = _match_attention(node, constant, folded)
+            except _NoMatch as reason:
+                notes.append(f"{node.name}: no fused attention: {reason}")
+                match = None
+            except Exception as error:  # e.g. a constant that cannot be evaluated at compile time
+                notes.append(f"{node.name}: no fused attention: {type(error).__name__}: {error}")
+                match = None
+            if match is not None and not absorbed.intersection(match.absorbed):
+                attention_at[match.anchor] = match
+                absorbed.update(match.absorbed)
+        elif node.target is aten.gelu.default and node in member_of and len(member_of[node].members) == 1:
+            found = _match_gemm_activation(node)
+            if found is not None and found[0] not in absorbed:
+                gemm_act_at[found[0]] = found[1]
+                passes_through.add(node)
+
+    def reads_of(node: fx.Node) -> list[fx.Node]:
+        if node in attention_at:
+            match = attention_at[node]
+            return [match.q, match.k, match.v]
+        if node in passes_through:
+            return [node.args[0]]
+        if node in constant:
+            return []
+        if node in member_of:
+            members = set(member_of[node].members)
+            return [a for m in member_of[node].members for a in m.all_input_nodes if a not in members]
+        return list(node.all_input_nodes)
+
+    # liveness after the rewrites: a node is emitted when the output (transitively) reads it
+    output = next(n for n in graph.nodes if n.op == "output")
+    live: set[fx.Node] = set()
+    stack = list(output.all_input_nodes)
+    while stack:
+        node = stack.pop()
+        if node in member_of and node not in passes_through:
+            node = member_of[node].root
+        if node in live:
+            continue
+        live.add(node)
+        stack.extend(reads_of(node))
+
     recipe = Recipe()
+    recipe.notes = notes
     for node in graph.nodes:
         if node.op == "placeholder":
             recipe.inputs.append(node.name)
@@ -213,8 +545,22 @@ def build_recipe(gm: fx.GraphModule, math_mode: str = "fast") -> Recipe:
         if node.op == "output":
             recipe.outputs = node.args[0]
             continue
+        if node not in live or node in absorbed:
+            continue
         if node.op == "get_attr":
             recipe.steps.append(Step("constant", node.name, lambda env, node=node, gm=gm: getattr(gm, node.target), []))
+            continue
+        if node in constant:
+            recipe.steps.append(_constant_step(node))
+            continue
+        if node in attention_at:
+            recipe.steps.append(_attention_step(attention_at[node]))
+            continue
+        if node in gemm_act_at:
+            recipe.steps.append(_gemm_activation_step(node, gemm_act_at[node]))
+            continue
+        if node in passes_through:
+            recipe.steps.append(Step("view", node.name, lambda env, name=node.args[0].name: env[name], [node.args[0].name]))
             continue
         if node in member_of:
             group = member_of[node]
@@ -230,24 +576,80 @@ def build_recipe(gm: fx.GraphModule, math_mode: str = "fast") -> Recipe:
             recipe.steps.append(_fused_step(node, kernel, inputs))
             recipe.kernels.append(kernel)
             continue
+        if node.target in SDPA:
+            step = _sdpa_step(node)
+            if step is not None:
+                recipe.steps.append(step)
+                continue
         recipe.steps.append(_kernel_step(node) or _interpreted(node, "no kernel"))
     recipe.finish()
     return recipe
 
 
+def _constant_step(node: fx.Node) -> Step:
+    """A value that depends on no input: computed by PyTorch on the first run, kept from then on."""
+    memo: list = []
+
+    def run(env):
+        if not memo:
+            cache: dict = {}
+
+            def value(n: fx.Node):
+                if n not in cache:
+                    cache[n] = n.target(*fx.node.map_arg(n.args, value), **fx.node.map_arg(n.kwargs, value))
+                return cache[n]
+
+            memo.append(value(node))
+        return memo[0]
+
+    return Step("constant", node.name, run, [])
+
+
+def _gemm_activation_step(addmm: fx.Node, activation: str) -> Step:
+    """act(bias + a @ b) with the activation in the GEMM's epilogue."""
+    bias, a, b = addmm.args[:3]
+    names = [bias.name, a.name, b.name]
+    fallback = (lambda t: torch.nn.functional.gelu(t, approximate="tanh")) if activation == "gelu_tanh" else torch.nn.functional.gelu
+
+    def run(env):
+        bias_t, a_t, b_t = (env[name] for name in names)
+        try:
+            return ops.gemm(a_t, b_t, bias_t, activation)
+        except Declined:
+            return fallback(torch.addmm(bias_t, a_t, b_t))
+
+    return Step("gemm", addmm.name, run, names)
+
+
 def _fused_step(node: fx.Node, kernel: FusedKernel, inputs: list[fx.Node]) -> Step:
-    meta = node.meta["val"]
-    shape, dtype = tuple(meta.shape), meta.dtype
+    dtype = node.meta["val"].dtype
     strided = [read == "strided" for read in kernel.reads]
 
     def run(env):
         tensors = [env[i.name] for i in inputs]
         tensors = [t if (s or t.is_contiguous()) else ops.contiguous(t) for t, s in zip(tensors, strided)]
-        out = torch.empty(shape, dtype=dtype, device=tensors[0].device if tensors else "cuda")
+        shape = torch.broadcast_shapes(*[t.shape for t in tensors])   # from the operands, so one recipe serves every size
+        out = torch.empty(shape, dtype=dtype, device=tensors[0].device)
         kernel.launch(tensors, out, stream=None)
         return out
 
     return Step("fused", node.name, run, [i.name for i in inputs], kernel=kernel)
+
+
+def _escapes(node: fx.Node) -> bool:
+    """True when the node's value, or a view of it, is one of the graph's results."""
+    stack, seen = [node], set()
+    while stack:
+        current = stack.pop()
+        if current in seen:
+            continue
+        seen.add(current)
+        for user in current.users:
+            if user.op == "output":
+                return True
+            if user.op == "call_function" and user.target in VIEWS:
+                stack.append(user)
+    return False
 
 
 def _kernel_step(node: fx.Node) -> Step | None:
@@ -284,7 +686,10 @@ def _kernel_step(node: fx.Node) -> Step | None:
     if target is aten.native_layer_norm.default and first is not None and first.dtype != torch.float64:
         return step("custom", lambda x, shape, w, b, eps: ops.native_layer_norm(x, shape, w, b, eps))
     if target is aten.clone.default:
-        return step("pack", lambda x, memory_format=None: ops.clone(x))
+        # A packed value is not copied again (the graph is functional: nothing writes into it),
+        # unless the clone — or a view of it — is handed to the caller.
+        private = not _escapes(node)
+        return step("pack", lambda x, memory_format=None: x if private and x.is_contiguous() else ops.clone(x))
     half = first is not None and first.dtype in (torch.bfloat16, torch.float16)
     if target is aten.mm.default and half:
         return step("gemm", _or_torch(ops.mm, target))

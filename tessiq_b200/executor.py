@@ -34,6 +34,7 @@ class Recipe:
     steps: list[Step] = field(default_factory=list)
     outputs: Any = None
     kernels: list[Any] = field(default_factory=list)
+    notes: list[str] = field(default_factory=list)   # why a rewrite (fused attention, ...) did not apply
     _dead_after: list[list[str]] = field(default_factory=list)
 
     def finish(self) -> None:

@@ -306,6 +306,11 @@ def _gemm(a, b, bias, activation):
     return out
 
 
+def gemm(a, b, bias=None, activation="none"):
+    """act(a @ b + bias): the GEMM kernel with any of its epilogues ("none", "gelu_erf", "gelu_tanh")."""
+    return _gemm(a, b, bias, activation)
+
+
 def mm(a, b):
     return _gemm(a, b, None, "none")
 

@@ -118,6 +118,79 @@ def test_recipe_frees_values_after_their_last_reader():
     assert not x_alive and value == 8     # x was dropped once step a had read it
 
 
+class DecoderBlock(torch.nn.Module):
+    """Config 4's pre-LN decoder block with the attention written out (bmm, mask, softmax, bmm)."""
+
+    def __init__(self, d, heads):
+        super().__init__()
+        self.d, self.heads = d, heads
+        self.ln1, self.ln2 = torch.nn.LayerNorm(d), torch.nn.LayerNorm(d)
+        self.qkv, self.proj = torch.nn.Linear(d, 3 * d), torch.nn.Linear(d, d)
+        self.fc, self.out = torch.nn.Linear(d, 4 * d), torch.nn.Linear(4 * d, d)
+
+    def forward(self, x):
+        b, n, d = x.shape
+        q, k, v = self.qkv(self.ln1(x)).split(d, dim=-1)
+        q, k, v = (z.view(b, n, self.heads, d // self.heads).transpose(1, 2) for z in (q, k, v))
+        scores = (q @ k.transpose(-1, -2)) / (d // self.heads) ** 0.5
+        mask = torch.tril(torch.ones(n, n, dtype=torch.bool, device=x.device))
+        scores = scores.masked_fill(~mask, float("-inf"))
+        y = (torch.softmax(scores, -1) @ v).transpose(1, 2).reshape(b, n, d)
+        x = x + self.proj(y)
+        return x + self.out(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
+
+
+def test_decoder_block_becomes_attention_and_epilogue_kernels():
+    from tessiq_b200.backend import build_recipe
+    from torch.func import functional_call
+
+    block = DecoderBlock(256, 4).eval().bfloat16()
+    params = dict(block.named_parameters())
+    with torch.no_grad():
+        gm = trace(lambda p, x: functional_call(block, p, (x,)), params, torch.randn(2, 128, 256).bfloat16())
+    recipe = build_recipe(gm)
+    counts = recipe.counts()
+    # bmm, mask, softmax, bmm and the four packing copies around them are one attention kernel;
+    # fc + gelu is one GEMM; the two residual adds are the only fused elementwise kernels left
+    assert counts["attention"] == 1 and counts["gemm"] == 4 and counts["fused"] == 2 and counts["custom"] == 2
+    assert recipe.interpreted == []
+    names = " ".join(step.output for step in recipe.steps)
+    assert "softmax" not in names and "where" not in names and "bmm" not in names and "arange" not in names
+    assert counts.get("pack", 0) == 1   # only the token-major regrouping after attention, which finds its operand packed
+
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():   # AOTAutograd calls the compiler inside its fake-tensor mode: the mask must still be read
+        assert build_recipe(gm).counts()["attention"] == 1
+
+    narrow = DecoderBlock(128, 4).eval().bfloat16()   # heads of 32: no attention kernel, the pattern stays as it was
+    with torch.no_grad():
+        gm = trace(lambda p, x: functional_call(narrow, p, (x,)), dict(narrow.named_parameters()), torch.randn(2, 64, 128).bfloat16())
+    recipe = build_recipe(gm)
+    assert "attention" not in recipe.counts() and recipe.counts()["gemm"] == 6 and recipe.interpreted == []
+    assert recipe.counts()["constant"] >= 1   # the mask is computed once, not on every call
+
+
+def test_only_a_lower_triangular_or_empty_mask_is_taken_for_attention():
+    from tessiq_b200.backend import build_recipe
+
+    def attend(q, k, v, mask):
+        scores = (q @ k.transpose(-1, -2)) * 0.125
+        if mask is not None:
+            scores = scores.masked_fill(~mask, float("-inf"))
+        return torch.softmax(scores, -1) @ v
+
+    q = torch.randn(2, 3, 128, 64).bfloat16()
+    band = lambda: torch.tril(torch.ones(128, 128, dtype=torch.bool)) & ~torch.tril(torch.ones(128, 128, dtype=torch.bool), -5)
+    for mask_fn, expected in ((None, True), (lambda: torch.tril(torch.ones(128, 128, dtype=torch.bool)), True), (band, False)):
+        gm = trace(lambda q, k, v: attend(q, k, v, None if mask_fn is None else mask_fn()), q, q, q)
+        counts = build_recipe(gm).counts()
+        assert ("attention" in counts) == expected, (counts, expected)
+    # a probability matrix somebody else reads stays in memory
+    gm = trace(lambda q, k, v: (lambda p: (p @ v, p.sum()))(torch.softmax((q @ k.transpose(-1, -2)) * 0.125, -1)), q, q, q)
+    assert "attention" not in build_recipe(gm).counts()
+
+
 # ---------------------------------------------------------------------------------------------
 # on the GPU
 
@@ -143,44 +216,64 @@ def test_compiled_functions_match_the_oracle():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("graphed", [False, True])
-def test_decoder_block_matches_eager_cpu(graphed):
-    # config 4's shape of work at a reduced size: pre-LN decoder block, bf16, causal attention
+@pytest.mark.parametrize("d,heads,t", [(128, 4, 64), (256, 4, 200), (768, 12, 256)], ids=["heads32", "heads64", "gpt2"])
+def test_decoder_block_matches_eager_cpu(graphed, d, heads, t):
+    # config 4's shape of work at a reduced size: pre-LN decoder block, bf16, causal attention;
+    # heads of 64 take the fused attention kernel, heads of 32 the bmm / softmax / bmm kernels
     from tessiq_b200.backend import compile_graph
 
+    torch._dynamo.reset()   # each shape compiles for itself: no symbolic sizes carried over from the last case
     torch.manual_seed(0)
-    d, heads, t, batch = 128, 4, 64, 8
-
-    class Block(torch.nn.Module):
-        def __init__(self):
-            super().__init__()
-            self.ln1, self.ln2 = torch.nn.LayerNorm(d), torch.nn.LayerNorm(d)
-            self.qkv, self.proj = torch.nn.Linear(d, 3 * d), torch.nn.Linear(d, d)
-            self.fc, self.out = torch.nn.Linear(d, 4 * d), torch.nn.Linear(4 * d, d)
-
-        def forward(self, x):
-            b, n, _ = x.shape
-            q, k, v = self.qkv(self.ln1(x)).split(d, dim=-1)
-            q, k, v = (z.view(b, n, heads, d // heads).transpose(1, 2) for z in (q, k, v))
-            scores = (q @ k.transpose(-1, -2)) / (d // heads) ** 0.5
-            mask = torch.tril(torch.ones(n, n, dtype=torch.bool, device=x.device))
-            scores = scores.masked_fill(~mask, float("-inf"))
-            y = (torch.softmax(scores, -1) @ v).transpose(1, 2).reshape(b, n, d)
-            x = x + self.proj(y)
-            return x + self.out(F.gelu(self.fc(self.ln2(x)), approximate="tanh"))
-
-    block = Block().eval().bfloat16()
+    batch = 8
+    block = DecoderBlock(d, heads).eval().bfloat16()
     for p in block.parameters():
         if p.dim() > 1:
             torch.nn.init.normal_(p, 0, 0.02)
     x = torch.randn(batch, t, d).bfloat16()
+    holder = {}
+
+    def backend(gm, inputs):
+        holder["fn"] = compile_graph(gm, inputs, options={"cuda_graph": graphed})
+        return holder["fn"]
+
     with torch.no_grad():
         ref = block(x).float()
-        gpu_block = Block().eval().bfloat16().cuda()
+        gpu_block = DecoderBlock(d, heads).eval().bfloat16().cuda()
         gpu_block.load_state_dict(block.state_dict())
-        compiled = torch.compile(gpu_block, backend=lambda gm, inputs: compile_graph(gm, inputs, options={"cuda_graph": graphed}))
+        compiled = torch.compile(gpu_block, backend=backend)
         for _ in range(3):  # eager, capture, replay
             got = compiled(x.cuda())
         torch.testing.assert_close(got.cpu().float(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
+    counts = holder["fn"].recipes[0].counts()
+    assert ("attention" in counts) == (d // heads == 64) and holder["fn"].recipes[0].interpreted == []
+
+
+@pytest.mark.gpu
+def test_one_compiled_graph_serves_changing_sizes():
+    # symbolic sizes: extents are launch arguments, not part of the kernels (the reference's
+    # tests/python/test_dynamic_shapes.py holds its kernels to the same)
+    from oracle import tessiq0
+    from tessiq_b200.backend import compile_graph
+
+    torch._dynamo.reset()
+    seen = []
+
+    def backend(gm, inputs):
+        seen.append(gm)
+        return compile_graph(gm, inputs)
+
+    def fn(x, b):
+        return torch.softmax(chain1(x, b), -1)
+
+    compiled = torch.compile(fn, backend=backend, dynamic=True)
+    g = torch.Generator().manual_seed(1)
+    b = torch.randn(512, generator=g) * 0.02
+    for rows in (64, 200, 33):
+        x = torch.randn(rows, 512, generator=g)
+        got = compiled(x.cuda(), b.cuda())
+        ref = tessiq0.softmax(tessiq0.chain_gelu_sigmoid(x, b), -1)
+        torch.testing.assert_close(got.cpu(), ref, rtol=1e-5, atol=1e-6)
+    assert len(seen) == 1
 
 
 def test_native_recipe_records_without_a_gpu_launch():
