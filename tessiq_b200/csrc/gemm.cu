@@ -2,16 +2,17 @@
 //
 //   C[b] = act(op(A[b]) @ op(B[b]) + bias)      bf16 or f16 operands, f32 accumulation, one rounding
 //
-// One persistent CTA per SM walks 128 x 256 output tiles. Inside a CTA, six warps have three jobs:
+// One persistent CTA per SM walks 128 x 256 output tiles. Inside a CTA, ten warps have three jobs:
 //
 //   warp 0, one lane   producer: TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of a
-//                      128 x 64 slice of A and a 256 x 64 slice of B into a 4-stage ring in
+//                      128 x 64 slice of A and a 256 x 64 slice of B into a 3-stage ring in
 //                      shared memory, each stage announced on an mbarrier by its byte count;
 //   warp 1, one lane   issuer: for every stage four tcgen05.mma (128 x 256 x 16) accumulating in
 //                      tensor memory; tcgen05.commit hands the stage back to the producer and, after
 //                      the last slice of a tile, hands the accumulator to the epilogue;
-//   warps 2..5         epilogue: tcgen05.ld of the f32 accumulator (each warp its own 32 lanes of
-//                      tensor memory), + bias, activation in f32, one rounding, 128-bit stores.
+//   warps 2..9         epilogue: tcgen05.ld of the f32 accumulator (each warp 32 lanes of tensor
+//                      memory by half of the columns), + bias, activation in f32, one rounding, a
+//                      regrouping through shared memory, whole-line 128-bit stores.
 //
 // Tensor memory holds two 128 x 256 f32 accumulators (all 512 columns), so the epilogue of tile i
 // runs under the MMAs of tile i+1. Either operand may be K-major (row-major A, nn.Linear weight
@@ -41,10 +42,13 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kTileN = 256;
 constexpr int kTileK = 64;    // 64 two-byte elements = one 128-byte swizzle row
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int kMmaK = 16;
-constexpr int kThreads = 192;
-constexpr int kEpilogueThreads = 128;
+constexpr int kThreads = 320;           // producer warp, issuer warp, eight epilogue warps
+constexpr int kEpilogueThreads = 256;
+constexpr int kEpilogueWarps = kEpilogueThreads / 32;
+constexpr int kStoreColumns = 64;       // columns an epilogue warp regroups at a time
+constexpr uint32_t kStoreBytes = 32 * kStoreColumns * 2;   // 4 KiB of staging per epilogue warp
 constexpr uint32_t kBytesA = kTileM * kTileK * 2;   // 16 KiB
 constexpr uint32_t kBytesB = kTileN * kTileK * 2;   // 32 KiB
 constexpr uint32_t kStageBytes = kBytesA + kBytesB;
@@ -52,7 +56,7 @@ constexpr uint32_t kChunkBytes = 64 * kTileK * 2;   // one 64-wide MN chunk of a
 constexpr uint32_t kTmemColumns = 512;
 
 constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + static_cast<size_t>(kStages) * kStageBytes +
-                              2 * kTileN * sizeof(float) /*bias*/ + 256 /*barriers, tmem slot*/;
+                              2 * kTileN * sizeof(float) /*bias*/ + 256 /*barriers, tmem slot*/ + kEpilogueWarps * kStoreBytes;
 
 enum WaitCode { kWaitEmpty = 101, kWaitFull = 102, kWaitTmemEmpty = 103, kWaitTmemFull = 104 };
 
@@ -97,6 +101,69 @@ __device__ __forceinline__ void tile_coordinates(long long tile, const GemmParam
   const int rows = min(kGroup, p.tiles_m - first_m);
   tile_m = first_m + (t % group_span) % rows;
   tile_n = (t % group_span) / rows;
+}
+
+// One epilogue warp's share of a 128 x 256 accumulator: the 32 rows of its tensor-memory lanes by
+// the 128 columns of its half. Per 64 columns: tcgen05.ld (lane i holds row i), + bias, activation,
+// one rounding, then the 32 x 64 block goes through 4 KiB of this warp's shared memory (16-byte
+// units XOR-swizzled by row, conflict-free both ways) so that each store instruction writes four
+// whole 128-byte lines of C instead of 32 scattered 16-byte pieces.
+template <typename T>
+__device__ __forceinline__ void epilogue_rows(uint32_t tmem_accumulator, int quarter, int half, int lane, const float* bias_tile,
+                                              T* c_tile, long long ldc, int rows_left, int columns_left, int activation,
+                                              unsigned char* staging, bool vector_ok) {
+  const int row = quarter * 32 + lane;
+  const uint32_t staging_address = smem_address(staging);
+#pragma unroll 1
+  for (int step = 0; step < (kTileN / 2) / kStoreColumns; ++step) {
+    const int column0 = half * (kTileN / 2) + step * kStoreColumns;
+    uint32_t r0[32], r1[32];
+    tmem_load_32(tmem_accumulator + column0 + (static_cast<uint32_t>(quarter * 32) << 16), r0);
+    tmem_load_32(tmem_accumulator + column0 + 32 + (static_cast<uint32_t>(quarter * 32) << 16), r1);
+    tmem_load_wait();
+    if (vector_ok) {
+#pragma unroll
+      for (int unit = 0; unit < 8; ++unit) {
+        Vec<T, 8> out;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int j = unit * 8 + e;
+          const float value = __uint_as_float(j < 32 ? r0[j] : r1[j - 32]) + bias_tile[column0 + j];
+          out.v[e] = from_compute<T, float>(activate(value, activation));
+        }
+        const uint4 word = *reinterpret_cast<const uint4*>(&out);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(staging_address + lane * 128 + ((unit ^ (lane & 7)) << 4)),
+                     "r"(word.x), "r"(word.y), "r"(word.z), "r"(word.w)
+                     : "memory");
+      }
+      __syncwarp();
+      const int unit = lane & 7;
+      if (column0 + unit * 8 < columns_left) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = i * 4 + (lane >> 3);
+          uint4 word;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(word.x), "=r"(word.y), "=r"(word.z), "=r"(word.w)
+                       : "r"(staging_address + r * 128 + ((unit ^ (r & 7)) << 4))
+                       : "memory");
+          if (quarter * 32 + r < rows_left) {
+            *reinterpret_cast<uint4*>(c_tile + static_cast<long long>(quarter * 32 + r) * ldc + column0 + unit * 8) = word;
+          }
+        }
+      }
+      __syncwarp();
+    } else if (row < rows_left) {
+      T* c_row = c_tile + static_cast<long long>(row) * ldc + column0;
+#pragma unroll
+      for (int j = 0; j < 64; ++j) {
+        if (column0 + j < columns_left) {
+          const float value = __uint_as_float(j < 32 ? r0[j] : r1[j - 32]) + bias_tile[column0 + j];
+          c_row[j] = from_compute<T, float>(activate(value, activation));
+        }
+      }
+    }
+  }
 }
 
 template <typename T, bool A_MN, bool B_MN>
@@ -204,9 +271,12 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       }
     }
   } else {
-    // ---- epilogue: warps 2..5; warp w owns tensor-memory lanes 32 (w % 4) .. +31 -----------
+    // ---- epilogue: warps 2..9; warp w owns tensor-memory lanes 32 (w % 4) .. +31 and the
+    // columns of half (w - 2) / 4 ---------------------------------------------------------------
     const int epilogue_thread = threadIdx.x - 64;
-    const int quarter = warp & 3;
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    unsigned char* staging = aligned + kStages * kStageBytes + 2 * kTileN * sizeof(float) + 256 + (warp - 2) * kStoreBytes;
+    const bool vector_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (p.stride_c % 8 == 0) && (p.n % 8 == 0);
     uint32_t local_tile = 0;
     for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++local_tile) {
       int batch, tile_m, tile_n;
@@ -224,41 +294,12 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       tcgen05_fence_after();
       asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");   // bias_tile is complete
 
-      const int row = tile_m * kTileM + quarter * 32 + lane;
-      T* c_row = static_cast<T*>(p.c) + static_cast<long long>(batch) * p.stride_c + static_cast<long long>(row) * p.ldc + n0;
-      const bool vector_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (p.stride_c % 8 == 0);
-#pragma unroll 1
-      for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
-        uint32_t r[32];
-        tmem_load_32(tmem_base + acc * kTileN + chunk * 32 + (static_cast<uint32_t>(quarter * 32) << 16), r);
-        tmem_load_wait();
-        if (row < p.m) {
-          const int column = n0 + chunk * 32;
-          if (vector_ok && column + 32 <= p.n) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              Vec<T, 8> out;
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const float value = __uint_as_float(r[v * 8 + e]) + bias_tile[chunk * 32 + v * 8 + e];
-                out.v[e] = from_compute<T, float>(activate(value, p.activation));
-              }
-              *reinterpret_cast<uint4*>(c_row + chunk * 32 + v * 8) = *reinterpret_cast<const uint4*>(&out);
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              if (column + e < p.n) {
-                const float value = __uint_as_float(r[e]) + bias_tile[chunk * 32 + e];
-                c_row[chunk * 32 + e] = from_compute<T, float>(activate(value, p.activation));
-              }
-            }
-          }
-        }
-      }
+      T* c_tile = static_cast<T*>(p.c) + static_cast<long long>(batch) * p.stride_c + static_cast<long long>(tile_m) * kTileM * p.ldc + n0;
+      epilogue_rows<T>(tmem_base + acc * kTileN, quarter, half, lane, bias_tile, c_tile, p.ldc, p.m - tile_m * kTileM, p.n - n0,
+                       p.activation, staging, vector_ok);
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) barrier_arrive(tmem_empty_bar(acc));   // this warp has read its lanes of the accumulator
+      if (lane == 0) barrier_arrive(tmem_empty_bar(acc));   // this warp has read its part of the accumulator
     }
   }
 
@@ -281,11 +322,12 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 // bytes of both CTAs' TMA loads (the loads name the leader's barrier; they are plain loads, no
 // multicast); tcgen05.commit reports to the barriers of both CTAs.
 
-constexpr int kPairStages = 6;
+constexpr int kPairStages = 5;
 constexpr int kPairTileM = 256;
 constexpr uint32_t kPairBytesB = (kTileN / 2) * kTileK * 2;     // 16 KiB: this CTA's half of B
 constexpr uint32_t kPairStageBytes = kBytesA + kPairBytesB;      // 32 KiB per CTA per stage
-constexpr size_t kPairSmemBytes = 1024 + static_cast<size_t>(kPairStages) * kPairStageBytes + 2 * kTileN * sizeof(float) + 256;
+constexpr size_t kPairSmemBytes = 1024 + static_cast<size_t>(kPairStages) * kPairStageBytes + 2 * kTileN * sizeof(float) + 256 +
+                                  kEpilogueWarps * kStoreBytes;
 
 __host__ __device__ constexpr uint32_t pair_instruction_descriptor(bool bf16, bool a_mn_major, bool b_mn_major) {
   return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
@@ -402,9 +444,11 @@ gemm_bias_act_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       }
     }
   } else {
-    // ---- epilogue: this CTA's 128 rows of the pair's tile ------------------------------------
+    // ---- epilogue: this CTA's 128 rows of the pair's tile, eight warps -------------------------
     const int epilogue_thread = threadIdx.x - 64;
-    const int quarter = warp & 3;
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    unsigned char* staging = aligned + kPairStages * kPairStageBytes + 2 * kTileN * sizeof(float) + 256 + (warp - 2) * kStoreBytes;
+    const bool vector_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (p.stride_c % 8 == 0) && (p.n % 8 == 0);
     uint32_t local_tile = 0;
     for (long long tile = pair; tile < p.num_tiles; tile += pairs, ++local_tile) {
       int batch, tile_m, tile_n;
@@ -422,41 +466,13 @@ gemm_bias_act_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       tcgen05_fence_after();
       asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
 
-      const int row = tile_m * kPairTileM + static_cast<int>(rank) * kTileM + quarter * 32 + lane;
-      T* c_row = static_cast<T*>(p.c) + static_cast<long long>(batch) * p.stride_c + static_cast<long long>(row) * p.ldc + n0;
-      const bool vector_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (p.stride_c % 8 == 0);
-#pragma unroll 1
-      for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
-        uint32_t r[32];
-        tmem_load_32(tmem_base + acc * kTileN + chunk * 32 + (static_cast<uint32_t>(quarter * 32) << 16), r);
-        tmem_load_wait();
-        if (row < p.m) {
-          const int column = n0 + chunk * 32;
-          if (vector_ok && column + 32 <= p.n) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              Vec<T, 8> out;
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const float value = __uint_as_float(r[v * 8 + e]) + bias_tile[chunk * 32 + v * 8 + e];
-                out.v[e] = from_compute<T, float>(activate(value, p.activation));
-              }
-              *reinterpret_cast<uint4*>(c_row + chunk * 32 + v * 8) = *reinterpret_cast<const uint4*>(&out);
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              if (column + e < p.n) {
-                const float value = __uint_as_float(r[e]) + bias_tile[chunk * 32 + e];
-                c_row[chunk * 32 + e] = from_compute<T, float>(activate(value, p.activation));
-              }
-            }
-          }
-        }
-      }
+      const int row0 = tile_m * kPairTileM + static_cast<int>(rank) * kTileM;
+      T* c_tile = static_cast<T*>(p.c) + static_cast<long long>(batch) * p.stride_c + static_cast<long long>(row0) * p.ldc + n0;
+      epilogue_rows<T>(tmem_base + acc * kTileN, quarter, half, lane, bias_tile, c_tile, p.ldc, p.m - row0, p.n - n0, p.activation,
+                       staging, vector_ok);
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) remote_arrive(peer_address(tmem_empty_bar(acc), 0));   // tell the leader: these lanes are drained
+      if (lane == 0) remote_arrive(peer_address(tmem_empty_bar(acc), 0));   // tell the leader: this part is drained
     }
   }
 
