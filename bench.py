@@ -540,6 +540,17 @@ def run_profile(args) -> None:
             ops.matmul_bias_gelu_tanh(a, b, bias)
         torch.cuda.synchronize()
         return
+    if args.profile == "attention":
+        # config 4's causal attention at an eighth of its batch: 8 x 12 heads x 1024 tokens x 64,
+        # Q, K and V read in place from a fused [batch, tokens, 3 * 768] projection
+        from tessiq_b200 import ops
+
+        qkv = torch.randn(8, 1024, 3 * 768, device="cuda").bfloat16()
+        q, k, v = (z.view(8, 1024, 12, 64).transpose(1, 2) for z in qkv.split(768, dim=-1))
+        for _ in range(args.warmup + args.steps):
+            ops.attention(q, k, v, None, True)
+        torch.cuda.synchronize()
+        return
     step = Step(0)
     stream = torch.cuda.Stream(device=0)
     with torch.cuda.stream(stream):

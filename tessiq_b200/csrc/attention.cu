@@ -7,16 +7,25 @@
 // walks the keys 128 at a time with a running row maximum and row sum (the online form of softmax).
 //
 //   warps 0..3 / 4..7   one softmax group per query tile, one thread per query row: tcgen05.ld of
-//                       the f32 scores from tensor memory, row maximum, ex2, row sum; the
-//                       probabilities go to shared memory as a K-major swizzled bf16/f16 tile (the
-//                       A operand of the second product); the partial result of the previous
-//                       step is read from tensor memory and accumulated in registers.
-//   warp 8, one lane    producer: TMA loads (128-byte swizzle) of the two query tiles once, then
-//                       one 128 x 64 key tile and one value tile per step into two 3-stage rings.
-//   warp 9, one lane    issuer: S = Q K^T (128 x 128 x 64, both operands K-major) and
-//                       O = P V (128 x 64 x 128, V consumed MN-major exactly as it lies in memory).
+//                       the row's 128 f32 scores (held in registers for both the maximum and the
+//                       exponentials), ex2, row sum; the probabilities go back into tensor memory
+//                       with tcgen05.st as packed bf16/f16 pairs — the A operand of the second
+//                       product — and the partial result of the previous step is read from tensor
+//                       memory and folded into the row's 64 accumulators with one FMA each.
+//   warp 8, one lane    producer: TMA loads (128-byte swizzle) of the two query tiles once, then one
+//                       128 x 64 key tile and one value tile per step into two 4-stage rings; the
+//                       first loads leave before the CTA's set-up barrier.
+//   warps 9 and 10,     issuers, one per group: S = Q K^T (128 x 128 x 64, both operands K-major in
+//   one lane each       shared memory) and O = P V (128 x 64 x 128, P from tensor memory, V consumed
+//                       MN-major exactly as it lies in memory). A tcgen05.mma costs its issuing
+//                       thread about a hundred cycles and a step needs twelve, so one thread for
+//                       both groups was the bottleneck; with one each, no group waits for the other.
 //
-// While one group runs its softmax the tensor core computes the other group's products. Q, K, V and
+// Each group has two 128-column buffers of tensor memory: the scores of step j sit in buffer j % 2;
+// once the group holds them in registers it writes the probabilities over columns 64..127, and the
+// second product writes the step's partial result over columns 0..63. So the scores of step j + 1
+// are computed while the group is still working on step j. The softmax groups run with 224
+// registers per thread, the other four warps with 56 (setmaxnreg). Q, K, V and
 // the result are addressed through (batch, head, token) strides, so the three slices of a fused QKV
 // projection are read in place and the result is written directly in [batch, token, head, 64] order:
 // none of the four packing copies around `bmm -> where -> softmax -> bmm` remains.
@@ -43,21 +52,20 @@ constexpr int kHeadDim = 64;
 constexpr int kRows = 128;            // query rows per softmax group
 constexpr int kGroups = 2;            // query tiles per CTA
 constexpr int kKeys = 128;            // keys per step
-constexpr int kRing = 3;              // stages of the key ring and of the value ring
-constexpr int kAttnThreads = 320;     // 8 softmax warps + producer + issuer
+constexpr int kRing = 4;              // stages of the key ring and of the value ring
+constexpr int kAttnThreads = 384;     // 8 softmax warps; producer and issuer in a third group of four warps
+constexpr int kSoftmaxRegisters = 224, kOtherRegisters = 56;   // 256 x 224 + 128 x 56 = the 64 K registers of an SM
 constexpr uint32_t kTileBytes = kRows * kHeadDim * 2;       // 16 KiB: a Q, K or V tile
-constexpr uint32_t kProbBytes = kRows * kKeys * 2;          // 32 KiB: one group's probabilities
 constexpr uint32_t kOffsetQ = 0;
 constexpr uint32_t kOffsetK = kOffsetQ + kGroups * kTileBytes;
 constexpr uint32_t kOffsetV = kOffsetK + kRing * kTileBytes;
-constexpr uint32_t kOffsetP = kOffsetV + kRing * kTileBytes;
-constexpr uint32_t kOffsetBarriers = kOffsetP + kGroups * kProbBytes;
+constexpr uint32_t kOffsetBarriers = kOffsetV + kRing * kTileBytes;
 constexpr size_t kAttnSmemBytes = 1024 + kOffsetBarriers + 256;
-constexpr uint32_t kAttnTmemColumns = 512;   // S0 | S1 | O0 | O1 = 128 + 128 + 64 + 64, rounded to a power of two
-constexpr uint32_t kColumnS = 0, kColumnO = 256;
+constexpr uint32_t kAttnTmemColumns = 512;   // two groups x two buffers x 128 columns
+constexpr uint32_t kColumnP = 64;            // in a buffer whose scores are spent: O in columns 0..63, P (packed pairs) in 64..127
 
 enum AttnWait { kWaitQ = 201, kWaitKeyEmpty = 202, kWaitValueEmpty = 203, kWaitKeyFull = 204, kWaitValueFull = 205,
-                kWaitScores = 206, kWaitProbabilities = 207, kWaitPartial = 208 };
+                kWaitScores = 206, kWaitProbabilities = 207, kWaitPartial = 208, kWaitBufferFree = 209 };
 
 struct AttnParams {
   int batch, heads, q_tokens, k_tokens;
@@ -95,10 +103,6 @@ __device__ __forceinline__ uint32_t pack_pair(float low, float high) {
   }
 }
 
-__device__ __forceinline__ void store_shared_16(uint32_t address, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-
 template <typename T>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -113,10 +117,11 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   auto k_empty = [&](int s) { return barriers + 8u * (1 + kRing + s); };
   auto v_full = [&](int s) { return barriers + 8u * (1 + 2 * kRing + s); };
   auto v_empty = [&](int s) { return barriers + 8u * (1 + 3 * kRing + s); };
-  auto s_full = [&](int g) { return barriers + 8u * (1 + 4 * kRing + g); };
-  auto p_full = [&](int g) { return barriers + 8u * (1 + 4 * kRing + kGroups + g); };
-  auto o_full = [&](int g) { return barriers + 8u * (1 + 4 * kRing + 2 * kGroups + g); };
-  constexpr int kBarrierCount = 1 + 4 * kRing + 3 * kGroups;
+  auto s_full = [&](int g, int b) { return barriers + 8u * (1 + 4 * kRing + 2 * g + b); };
+  auto o_full = [&](int g, int b) { return barriers + 8u * (1 + 4 * kRing + 2 * kGroups + 2 * g + b); };
+  auto p_full = [&](int g) { return barriers + 8u * (1 + 4 * kRing + 4 * kGroups + g); };
+  auto buffer_free = [&](int g) { return barriers + 8u * (1 + 4 * kRing + 5 * kGroups + g); };
+  constexpr int kBarrierCount = 1 + 4 * kRing + 6 * kGroups;
   const uint32_t tmem_slot = barriers + 8u * kBarrierCount;
   volatile uint32_t* tmem_slot_pointer = reinterpret_cast<volatile uint32_t*>(aligned + kOffsetBarriers + 8 * kBarrierCount);
 
@@ -138,20 +143,42 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   }
   const int total_steps = max(steps[0], steps[1]);
 
-  if (threadIdx.x == 0) {
+  // The producer lane sets the barriers up and sends the first loads (both query tiles, the first
+  // key and value tiles) on their way before the CTA meets: their latency runs under the
+  // tensor-memory allocation and the barrier.
+  const bool producer = threadIdx.x == 8 * 32;
+  if (producer) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     barrier_init(q_full, 1);
     for (int s = 0; s < kRing; ++s) {
       barrier_init(k_full(s), 1);
-      barrier_init(k_empty(s), 1);
+      barrier_init(k_empty(s), kGroups);      // each group hands a tile back once its product has read it
       barrier_init(v_full(s), 1);
-      barrier_init(v_empty(s), 1);
+      barrier_init(v_empty(s), kGroups);
     }
     for (int g = 0; g < kGroups; ++g) {
-      barrier_init(s_full(g), 1);
-      barrier_init(p_full(g), kRows);
-      barrier_init(o_full(g), 1);
+      for (int b = 0; b < 2; ++b) {
+        barrier_init(s_full(g, b), 1);
+        barrier_init(o_full(g, b), 1);
+      }
+      barrier_init(p_full(g), kRows / 32);          // one arrival per warp of the group
+      barrier_init(buffer_free(g), kRows / 32);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (total_steps > 0) {
+      int valid = 0;
+      for (int g = 0; g < kGroups; ++g) valid += steps[g] > 0 ? 1 : 0;
+      barrier_expect_tx(q_full, valid * kTileBytes);
+      for (int g = 0; g < kGroups; ++g) {
+        if (steps[g] > 0) tma_load_4d(base + kOffsetQ + g * kTileBytes, &map_q, q_full, 0, q0 + g * kRows, head, batch);
+      }
+      barrier_expect_tx(k_full(0), kTileBytes);
+      tma_load_4d(base + kOffsetK, &map_k, k_full(0), 0, 0, head, batch);
+      barrier_expect_tx(v_full(0), kTileBytes);
+      tma_load_4d(base + kOffsetV, &map_v, v_full(0), 0, 0, head, batch);
+    }
   }
   if (warp == 9) tmem_alloc(tmem_slot, kAttnTmemColumns);
   tcgen05_fence_before();
@@ -159,16 +186,11 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_pointer;
 
+  if (warp >= 8) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegisters));
   if (warp == 8) {
-    // ---- producer ----------------------------------------------------------------------------
+    // ---- producer: the tiles of step 1 onwards (step 0's went out before the CTA met) ------------
     if (lane == 0) {
-      int valid = 0;
-      for (int g = 0; g < kGroups; ++g) valid += steps[g] > 0 ? 1 : 0;
-      barrier_expect_tx(q_full, valid * kTileBytes);
-      for (int g = 0; g < kGroups; ++g) {
-        if (steps[g] > 0) tma_load_4d(base + kOffsetQ + g * kTileBytes, &map_q, q_full, 0, q0 + g * kRows, head, batch);
-      }
-      for (int j = 0; j < total_steps; ++j) {
+      for (int j = 1; j < total_steps; ++j) {
         const int s = j % kRing;
         const uint32_t phase = (j / kRing) & 1;
         if (!barrier_wait(k_empty(s), phase ^ 1, p.status, kWaitKeyEmpty)) break;
@@ -179,65 +201,64 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         tma_load_4d(base + kOffsetV + s * kTileBytes, &map_v, v_full(s), 0, j * kKeys, head, batch);
       }
     }
-  } else if (warp == 9) {
-    // ---- issuer ------------------------------------------------------------------------------
-    if (lane == 0 && total_steps > 0) {
+  } else if (warp == 9 || warp == 10) {
+    // ---- issuers: warp 9 for group 0, warp 10 for group 1 -------------------------------------
+    // A tcgen05.mma costs its issuing thread on the order of a hundred cycles here, and a step is
+    // 12 of them plus two commits: one thread for both groups was the kernel's bottleneck. Each
+    // group's issuer follows its own group only, so neither group waits for the other.
+    const int g = warp - 9;
+    if (lane == 0 && steps[g] > 0) {
       constexpr uint32_t idesc_s = attn_instruction_descriptor<T>(kKeys, false);
       constexpr uint32_t idesc_o = attn_instruction_descriptor<T>(kHeadDim, true);
-      // S_g = Q_g K^T: both K-major, 8-row groups 1024 B apart, 16 elements of K = 32 B in the swizzle row
-      auto scores = [&](int g, int stage) {
-        const uint32_t smem_q = base + kOffsetQ + g * kTileBytes, smem_k = base + kOffsetK + stage * kTileBytes;
+      // Descriptors as (low, high) words: the high word is one constant (stride offset 1024, version
+      // 1, 128-byte swizzle), the low word is (address >> 4) | leading offset, stepped by adds.
+      constexpr uint32_t kHighWord = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t low_q = (base + kOffsetQ + g * kTileBytes) >> 4, low_k = (base + kOffsetK) >> 4;
+      const uint32_t low_v = ((base + kOffsetV) >> 4) | ((kTileBytes >> 4) << 16);
+      const uint32_t buffers = tmem_base + static_cast<uint32_t>(2 * g * kKeys);     // buffer b at + 128 b
+      // S(i) = Q K_i^T into buffer i % 2: both operands K-major, 16 elements of K = 32 B in the swizzle row
+      auto scores = [&](int i) {
+        const uint32_t k = low_k + (i % kRing) * (kTileBytes >> 4), d = buffers + (i & 1) * kKeys;
 #pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-          mma_f16(tmem_base + kColumnS + g * kKeys, smem_descriptor(smem_q + kk * 32, 0, 1024),
-                  smem_descriptor(smem_k + kk * 32, 0, 1024), idesc_s, kk != 0 ? 1u : 0u);
-        }
-        mma_commit(s_full(g));
+        for (int kk = 0; kk < kHeadDim / 16; ++kk) mma_f16_split(d, low_q + kk * 2, kHighWord, k + kk * 2, kHighWord, idesc_s, kk != 0);
+        mma_commit(s_full(g, i & 1));
       };
-      // O_g = P_g V: P K-major in two 64-key halves 16 KiB apart; V MN-major, 16 keys = 2048 B
-      auto partial = [&](int g, int stage) {
-        const uint32_t smem_p = base + kOffsetP + g * kProbBytes, smem_v = base + kOffsetV + stage * kTileBytes;
+      // O(i) = P_i V_i over columns 0..63 of buffer i % 2: P from tensor memory (columns 64..127, 16
+      // keys = 8 columns), V MN-major from shared memory (16 keys = 2048 B)
+      auto partial = [&](int i) {
+        const uint32_t v = low_v + (i % kRing) * (kTileBytes >> 4), d = buffers + (i & 1) * kKeys;
 #pragma unroll
-        for (int kk = 0; kk < kKeys / 16; ++kk) {
-          mma_f16(tmem_base + kColumnO + g * kHeadDim, smem_descriptor(smem_p + (kk >> 2) * (kProbBytes / 2) + (kk & 3) * 32, 0, 1024),
-                  smem_descriptor(smem_v + kk * 2048, kTileBytes, 1024), idesc_o, kk != 0 ? 1u : 0u);
-        }
-        mma_commit(o_full(g));
+        for (int kk = 0; kk < kKeys / 16; ++kk) mma_f16_tmem_a(d, d + kColumnP + kk * 8, v + kk * (2048 >> 4), kHighWord, idesc_o, kk != 0);
+        mma_commit(o_full(g, i & 1));
       };
       bool alive = barrier_wait(q_full, 0, p.status, kWaitQ) && barrier_wait(k_full(0), 0, p.status, kWaitKeyFull);
       if (alive) {
         tcgen05_fence_after();
-        for (int g = 0; g < kGroups; ++g) {
-          if (steps[g] > 0) scores(g, 0);
-        }
-        mma_commit(k_empty(0));
+        scores(0);
       }
-      for (int j = 0; alive && j < total_steps; ++j) {
-        const int s = j % kRing, next = (j + 1) % kRing;
-        if (!barrier_wait(v_full(s), (j / kRing) & 1, p.status, kWaitValueFull)) break;
-        if (j + 1 < total_steps && !barrier_wait(k_full(next), ((j + 1) / kRing) & 1, p.status, kWaitKeyFull)) break;
-        for (int g = 0; g < kGroups; ++g) {
-          if (j >= steps[g]) continue;
-          if (!barrier_wait(p_full(g), j & 1, p.status, kWaitProbabilities)) { alive = false; break; }
+      for (int i = 0; alive && i < steps[g]; ++i) {
+        // the scores of step i + 1, once the group has taken O(i-1) out of that buffer (its i-th arrival)
+        if (i + 1 < steps[g]) {
+          if (!barrier_wait(k_full((i + 1) % kRing), ((i + 1) / kRing) & 1, p.status, kWaitKeyFull)) break;
+          if (!barrier_wait(buffer_free(g), i & 1, p.status, kWaitBufferFree)) break;
           tcgen05_fence_after();
-          partial(g, s);
-          if (j + 1 < steps[g]) scores(g, next);
+          scores(i + 1);
         }
-        if (!alive) break;
-        mma_commit(v_empty(s));
-        if (j + 1 < total_steps) mma_commit(k_empty(next));
+        // the partial result of step i, once the group's probabilities are in tensor memory
+        if (!barrier_wait(v_full(i % kRing), (i / kRing) & 1, p.status, kWaitValueFull)) break;
+        if (!barrier_wait(p_full(g), i & 1, p.status, kWaitProbabilities)) break;
+        tcgen05_fence_after();
+        partial(i);
       }
     }
-  } else {
+  } else if (warp < 8) {
     // ---- softmax groups: warp w of a group owns tensor-memory lanes 32 (w % 4) .. +31 ---------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegisters));
     const int g = warp >> 2, quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const int query = q0 + g * kRows + row;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t tmem_s = tmem_base + kColumnS + g * kKeys + lane_base;
-    const uint32_t tmem_o = tmem_base + kColumnO + g * kHeadDim + lane_base;
-    const uint32_t smem_p_row = base + kOffsetP + g * kProbBytes + row * 128;
-    const uint32_t swizzle = static_cast<uint32_t>(row & 7);
+    const uint32_t tmem_group = tmem_base + static_cast<uint32_t>(2 * g * kKeys) + lane_base;   // buffer b at + 128 b
     const int my_steps = steps[g];
     float acc[kHeadDim];
 #pragma unroll
@@ -246,104 +267,116 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     bool alive = true;
     const int last_allowed = p.causal ? min(query, p.k_tokens - 1) : p.k_tokens - 1;   // the last key this row may see
 
-    auto add_partial = [&]() {
+    // acc <- acc * scale + (the partial result in buffer b): one FMA per element
+    auto add_partial = [&](int b, float scale) {
       uint32_t r0[32], r1[32];
-      tmem_load_32(tmem_o, r0);
-      tmem_load_32(tmem_o + 32, r1);
+      tmem_load_32(tmem_group + b * kKeys, r0);
+      tmem_load_32(tmem_group + b * kKeys + 32, r1);
       tmem_load_wait();
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        acc[i] += __uint_as_float(r0[i]);
-        acc[32 + i] += __uint_as_float(r1[i]);
+        acc[i] = fmaf(acc[i], scale, __uint_as_float(r0[i]));
+        acc[32 + i] = fmaf(acc[32 + i], scale, __uint_as_float(r1[i]));
+      }
+    };
+    // one row of scores: 128 columns, one wait
+    auto load_row = [&](uint32_t address, uint32_t (&r)[kKeys], bool edge, int limit) {
+#pragma unroll
+      for (int c = 0; c < kKeys / 32; ++c) tmem_load_32(address + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+      tmem_load_wait();
+      if (edge) {
+#pragma unroll
+        for (int i = 0; i < kKeys; ++i) {
+          if (i > limit) r[i] = 0xff800000u;   // -inf
+        }
       }
     };
 
+    // With m_j the running maximum after step j and alpha_j = exp2((m_{j-1} - m_j) scale), the result
+    // obeys A_j = A_{j-1} alpha_j + O_j. O_j leaves the tensor core one step late, so the group
+    // keeps alpha_j and applies it when it takes O_j out of tensor memory (step j + 1, or the end).
+    float alpha_previous = 0.f;
     for (int j = 0; j < my_steps; ++j) {
-      if (j > 0) {
-        if (!barrier_wait(o_full(g), (j - 1) & 1, p.status, kWaitPartial)) { alive = false; break; }
-        tcgen05_fence_after();
-        add_partial();
-      }
-      if (!barrier_wait(s_full(g), j & 1, p.status, kWaitScores)) { alive = false; break; }
+      const uint32_t tmem_s = tmem_group + (j & 1) * kKeys;
+      if (!barrier_wait(s_full(g, j & 1), (j >> 1) & 1, p.status, kWaitScores)) { alive = false; break; }
       tcgen05_fence_after();
+      if (threadIdx.x == g * kRows) {      // the first product has read key tile j: hand it back (for the other group too, if it has no step j)
+        barrier_arrive(k_empty(j % kRing));
+        if (j >= steps[1 - g]) barrier_arrive(k_empty(j % kRing));
+      }
+      // the partial result of step j - 1 (A_{j-1} = A_{j-2} alpha_{j-1} + O_{j-1}); after it that
+      // buffer is free for step j + 1's scores
+      if (j > 0) {
+        if (!barrier_wait(o_full(g, (j - 1) & 1), ((j - 1) >> 1) & 1, p.status, kWaitPartial)) { alive = false; break; }
+        tcgen05_fence_after();
+        if (threadIdx.x == g * kRows) {    // the second product has read value tile j - 1
+          barrier_arrive(v_empty((j - 1) % kRing));
+          if (j - 1 >= steps[1 - g]) barrier_arrive(v_empty((j - 1) % kRing));
+        }
+        add_partial((j - 1) & 1, alpha_previous);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) barrier_arrive(buffer_free(g));
+
+      // this step's scores: one row per thread, held in registers for both the maximum and the exponentials
       const int key0 = j * kKeys;
       const int limit = last_allowed - key0;                       // columns > limit are masked for this row
       const bool edge = key0 + kKeys - 1 > (p.causal ? min(q0 + g * kRows, p.k_tokens - 1) : p.k_tokens - 1);   // uniform in the group
-
-      // pass 1: the row maximum of this step's scores
-      float step_max = -INFINITY;
+      uint32_t r[kKeys];
+      load_row(tmem_s, r, edge, limit);
+      float m0 = row_max, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t r0[32], r1[32];
-        tmem_load_32(tmem_s + half * 64, r0);
-        tmem_load_32(tmem_s + half * 64 + 32, r1);
-        tmem_load_wait();
-        if (edge) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (half * 64 + i > limit) r0[i] = 0xff800000u;
-            if (half * 64 + 32 + i > limit) r1[i] = 0xff800000u;
-          }
-        }
-        float m0 = -INFINITY, m1 = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          m0 = fmaxf(m0, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r0[i + 1])));
-          m1 = fmaxf(m1, fmaxf(__uint_as_float(r1[i]), __uint_as_float(r1[i + 1])));
-        }
-        step_max = fmaxf(step_max, fmaxf(m0, m1));
+      for (int i = 0; i < kKeys; i += 8) {
+        m0 = fmaxf(fmaxf(m0, __uint_as_float(r[i])), __uint_as_float(r[i + 1]));
+        m1 = fmaxf(fmaxf(m1, __uint_as_float(r[i + 2])), __uint_as_float(r[i + 3]));
+        m2 = fmaxf(fmaxf(m2, __uint_as_float(r[i + 4])), __uint_as_float(r[i + 5]));
+        m3 = fmaxf(fmaxf(m3, __uint_as_float(r[i + 6])), __uint_as_float(r[i + 7]));
       }
-      const float new_max = fmaxf(row_max, step_max);
+      const float new_max = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
       const float alpha = exp2_ftz((row_max - new_max) * p.scale_log2);
       row_max = new_max;
-      if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll
-        for (int i = 0; i < kHeadDim; ++i) acc[i] *= alpha;
-      }
+      alpha_previous = alpha;
       const float shift = -new_max * p.scale_log2;
 
-      // pass 2: probabilities, their sum, and the K-major swizzled tile for the second product
-      float sum0 = 0.f, sum1 = 0.f;
+      // probabilities and their sum; the probabilities go back into tensor memory as the A operand of
+      // the second product (16-bit pairs over columns 64..127 of this step's buffer)
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+      {
+        uint32_t packed[kKeys / 2];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t r0[32], r1[32];
-        tmem_load_32(tmem_s + half * 64, r0);
-        tmem_load_32(tmem_s + half * 64 + 32, r1);
-        tmem_load_wait();
-        if (edge) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (half * 64 + i > limit) r0[i] = 0xff800000u;
-            if (half * 64 + 32 + i > limit) r1[i] = 0xff800000u;
-          }
+        for (int chunk = 0; chunk < kKeys / 8; ++chunk) {
+          const float p0 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 0]), p.scale_log2, shift));
+          const float p1 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 1]), p.scale_log2, shift));
+          const float p2 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 2]), p.scale_log2, shift));
+          const float p3 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 3]), p.scale_log2, shift));
+          const float p4 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 4]), p.scale_log2, shift));
+          const float p5 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 5]), p.scale_log2, shift));
+          const float p6 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 6]), p.scale_log2, shift));
+          const float p7 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 7]), p.scale_log2, shift));
+          sum0 += p0 + p4;
+          sum1 += p1 + p5;
+          sum2 += p2 + p6;
+          sum3 += p3 + p7;
+          packed[chunk * 4 + 0] = pack_pair<T>(p0, p1);
+          packed[chunk * 4 + 1] = pack_pair<T>(p2, p3);
+          packed[chunk * 4 + 2] = pack_pair<T>(p4, p5);
+          packed[chunk * 4 + 3] = pack_pair<T>(p6, p7);
         }
-        const uint32_t half_base = smem_p_row + half * (kProbBytes / 2);
-#pragma unroll
-        for (int chunk = 0; chunk < 8; ++chunk) {     // 8 keys = 16 bytes
-          uint32_t packed[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = chunk * 8 + e * 2;
-            const uint32_t a = i < 32 ? r0[i] : r1[i - 32], b = i < 32 ? r0[i + 1] : r1[i - 31];
-            const float pa = exp2_ftz(fmaf(__uint_as_float(a), p.scale_log2, shift));
-            const float pb = exp2_ftz(fmaf(__uint_as_float(b), p.scale_log2, shift));
-            sum0 += pa;
-            sum1 += pb;
-            packed[e] = pack_pair<T>(pa, pb);
-          }
-          store_shared_16(half_base + ((static_cast<uint32_t>(chunk) ^ swizzle) << 4), packed[0], packed[1], packed[2], packed[3]);
-        }
+        tmem_store_32(tmem_s + kColumnP, *reinterpret_cast<const uint32_t(*)[32]>(&packed[0]));
+        tmem_store_32(tmem_s + kColumnP + 32, *reinterpret_cast<const uint32_t(*)[32]>(&packed[32]));
+        tmem_store_wait();
       }
-      row_sum = row_sum * alpha + (sum0 + sum1);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tile is read by the tensor core's proxy
+      row_sum = row_sum * alpha + ((sum0 + sum1) + (sum2 + sum3));
       tcgen05_fence_before();
-      barrier_arrive(p_full(g));
+      __syncwarp();
+      if (lane == 0) barrier_arrive(p_full(g));
     }
 
     if (alive && my_steps > 0) {
-      if (barrier_wait(o_full(g), (my_steps - 1) & 1, p.status, kWaitPartial)) {
+      if (barrier_wait(o_full(g, (my_steps - 1) & 1), ((my_steps - 1) >> 1) & 1, p.status, kWaitPartial)) {
         tcgen05_fence_after();
-        add_partial();
+        add_partial((my_steps - 1) & 1, alpha_previous);
         if (query < p.q_tokens) {
           const float inverse = 1.0f / row_sum;
           T* out_row = static_cast<T*>(p.out) + batch * p.out_batch + head * p.out_head + static_cast<long long>(query) * p.out_token;

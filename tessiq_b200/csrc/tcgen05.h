@@ -43,6 +43,19 @@ __device__ __forceinline__ bool barrier_try_wait(uint32_t bar, uint32_t parity) 
 // Waits for the phase of `bar` with the given parity, for a bounded number of polls. When the
 // bound runs out (or another thread's already did) the status word gets `code` and the caller
 // must leave its loop.
+// One non-blocking look at the phase of `bar` with the given parity (for a thread that polls
+// several barriers in turn).
+__device__ __forceinline__ bool barrier_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
 __device__ __forceinline__ bool barrier_wait(uint32_t bar, uint32_t parity, int* status, int code) {
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
     if (barrier_try_wait(bar, parity)) return true;
@@ -81,6 +94,52 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64
       : "memory");
 }
 
+// The same, with each descriptor given as its constant high word and its low word (start address
+// and leading offset), so that stepping through a tile is one 32-bit add per operand.
+__device__ __forceinline__ void mma_f16_split(uint32_t tmem_d, uint32_t a_low, uint32_t a_high, uint32_t b_low, uint32_t b_high,
+                                              uint32_t idesc, bool accumulate) {
+  if (accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, 1, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_low), "r"(a_high), "r"(b_low), "r"(b_high), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_low), "r"(a_high), "r"(b_low), "r"(b_high), "r"(idesc)
+        : "memory");
+  }
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand lies in tensor memory, one row per lane, two 16-bit
+// elements of K per 32-bit column (16 elements of K = 8 columns).
+__device__ __forceinline__ void mma_f16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_low, uint32_t b_high, uint32_t idesc,
+                                               bool accumulate) {
+  if (accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, 1, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(b_low), "r"(b_high), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(b_low), "r"(b_high), "r"(idesc)
+        : "memory");
+  }
+}
+
 // The mbarrier gets one arrival when every tcgen05 operation this thread issued so far is done.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -100,6 +159,20 @@ __device__ __forceinline__ void tmem_load_32(uint32_t address, uint32_t (&r)[32]
       : "memory");
 }
 __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// The reverse: lane i of the warp writes 32 consecutive columns of row i.
+__device__ __forceinline__ void tmem_store_32(uint32_t address, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(address), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, 128-byte swizzle. Bits: [0,14) start address >> 4,
 // [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4, [46,48) version = 1,
