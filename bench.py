@@ -444,6 +444,15 @@ def other_configs(device: int, stream) -> dict:
     out["config5_six_op_chain_f32_to_bf16"] = {"us": round(seconds * 1e6, 1), "gbs": round(n * 10 / seconds / 1e9, 1),
                                                "frac_of_measured_hbm": round(n * 10 / seconds / 1e9 / peak_hbm, 4)}
     del p, q, y
+    # config 4's attention alone: causal, batch 64 x 12 heads x 1024 tokens x 64, Q/K/V read in place from the fused projection
+    qkv = torch.randn(64, 1024, 3 * 768, device=dev).bfloat16()
+    q, k, v = (z.view(64, 1024, 12, 64).transpose(1, 2) for z in qkv.split(768, dim=-1))
+    with torch.cuda.stream(stream):
+        seconds = timed(lambda: ops.attention(q, k, v, None, True), 10)
+    masked_flop = 4 * 64 * 12 * 1024 * 1024 * 64 / 2
+    out["config4_causal_attention_bf16"] = {"us": round(seconds * 1e6, 1), "tflops_causal": round(masked_flop / seconds / 1e12, 1),
+                                            "note": "one fused kernel; flop counted over the lower triangle only"}
+    del qkv, q, k, v
     out["config4_decoder_block_bf16"] = decoder_block(dev, stream)
     return out
 
