@@ -571,6 +571,95 @@ def run_profile(args) -> None:
         stream.synchronize()
 
 
+def run_sweep(args) -> dict:
+    """BASELINE config 5 on this rank's GPU: for fp32, bf16 and fp16 tensors of 2^20 .. 2^30 elements
+    (per GPU: weak scaling), the six-op chain (add, mul, exp, tanh, where on a > 0, cast), the [R,1]
+    row broadcast `x + r` with 4096-wide rows, and the global sum / amax whose per-GPU partials are
+    all-reduced. Device time per launch from CUDA events around a CUDA-graph replay of 10 launches;
+    bytes are the algorithmic ones (every operand read once, the result written once). Tensors of
+    less than about 2^24 elements stay in the 126 MB L2 between launches and say so."""
+    import torch
+    import torch.distributed as dist
+
+    from tessiq_b200 import sharding
+    from tessiq_b200.kernel import FusedKernel
+
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    stream = torch.cuda.Stream(device=local)
+    names = {torch.float32: "f32", torch.bfloat16: "bf16", torch.float16: "f16"}
+
+    def timed(fn, graph_ok=True):
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                fn()
+            stream.synchronize()
+            replay = fn
+            launches = 1
+            if graph_ok:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for _ in range(10):
+                        fn()
+                replay, launches = graph.replay, 10
+            replay()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(5):
+                replay()
+            b.record(stream)
+            stream.synchronize()
+        us = torch.tensor([a.elapsed_time(b) / (5 * launches) * 1e3], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(us, op=dist.ReduceOp.MAX)
+        return us.item()
+
+    rows = []
+    raw = stream.cuda_stream
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        name, size = names[dtype], torch.empty(0, dtype=dtype).element_size()
+        out_dtype = torch.bfloat16 if dtype == torch.float32 else torch.float32
+        chain = FusedKernel(f"in a {name} same\nin b {name} same\nt0 = add a b\nt1 = exp t0\nt2 = mul t1 b\nt3 = tanh t2\nc = gt a 0\n"
+                            f"w = where c t3 a\ny = cast w {names[out_dtype]}\nout y {names[out_dtype]}\n")
+        broadcast = FusedKernel(f"in x {name} same\nin r {name} repeated\nv = add x r\nout v {name}\n")
+        for log2n in range(20, 31, 2):
+            n = 1 << log2n
+            g = torch.Generator(device=dev).manual_seed(log2n)
+            a = (torch.rand(n, device=dev, generator=g) * 2 - 1).to(dtype)
+            b = (torch.rand(n, device=dev, generator=g) * 2 - 1).to(dtype)
+            y = torch.empty(n, dtype=out_dtype, device=dev)
+            us = timed(lambda: chain.launch([a, b], y, stream=raw))
+            chain_bytes = n * (2 * size + y.element_size())
+            del y
+            x2, r = a.view(-1, 4096), b[: n // 4096].view(-1, 1)
+            z = torch.empty_like(x2)
+            us_b = timed(lambda: broadcast.launch([x2, r], z, stream=raw))
+            broadcast_bytes = 2 * n * size + (n // 4096) * size
+            del z
+            entry = {"dtype": name, "log2_elements_per_gpu": log2n, "l2_resident": 3 * n * size < 100e6,
+                     "chain_us": round(us, 2), "chain_gbs": round(world * chain_bytes / us / 1e3, 1),
+                     "row_broadcast_us": round(us_b, 2), "row_broadcast_gbs": round(world * broadcast_bytes / us_b / 1e3, 1)}
+            for op in ("sum", "amax"):
+                with torch.cuda.stream(stream):
+                    us_r = timed(lambda: sharding.global_reduce(op, a, offset=rank * n, total=world * n), graph_ok=world == 1)
+                entry[f"global_{op}_us"] = round(us_r, 2)
+                entry[f"global_{op}_gbs"] = round(world * n * size / us_r / 1e3, 1)
+            rows.append(entry)
+            del a, b, x2, r
+            torch.cuda.empty_cache()
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return {}
+    peak, peak_kind = peaks()
+    return {"sweep": "config 5: six-op chain, [R,1] row broadcast, global sum/amax", "n_gpus": world, "scaling": "weak",
+            "collective": "none" if world == 1 else f"all-reduce of per-GPU partials over {world} ranks (NCCL), inside the timed region",
+            "peak_hbm_gbs": peak, "peak_kind": peak_kind, "rows": rows}
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per full launch, from one
 # ncu capture at 16384 rows scaled by two (profiles/softmax_rows_f32_row_cluster_kernel.md); the
 # traffic grows in proportion to the rows. Below the 1 073 741 824 algorithmic bytes only because
@@ -680,10 +769,17 @@ def main() -> None:
     parser.add_argument("--profile", metavar="OP", default=None,
                         help="for ncu: run only eager launches of OP (e.g. softmax_rows_f32, or `all`), "
                              "W warm-up + K steps, and print nothing else")
+    parser.add_argument("--sweep", action="store_true",
+                        help="BASELINE config 5's size sweep (2^20 .. 2^30 elements, three element types) instead of the bench line")
     args = parser.parse_args()
     globals()["ROWS"] = args.rows
     if args.profile:
         run_profile(args)
+        return
+    if args.sweep:
+        table = run_sweep(args)
+        if table:
+            print(json.dumps(table), flush=True)
         return
     line = run_reference(args) if args.impl == "reference" else run_ours(args)
     if line:

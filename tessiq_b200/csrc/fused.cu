@@ -697,6 +697,10 @@ int unroll_for(const Program& p, int vec) {
   }
   // Measured on config 1 (two 4-byte operands, 8 words): 2 tiles of loads per thread beat 4
   // (23.0 us against 24.4 us) — smaller CTAs retire and refill at a finer grain.
+  // Vectors of 8 or 16 narrow elements already mean 8-16 conversions and results per load: one tile
+  // per thread measured best for them at 2^28 elements (bf16 six-op chain 6.84 against 6.13 TB/s with
+  // two, row broadcast 5.94 against 5.28, plain add 6.88 against 6.83).
+  if (vec >= 8) return 1;
   if (words <= 4) return 4;
   if (words <= 24) return 2;
   return 1;
