@@ -220,7 +220,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       auto scores = [&](int i) {
         const uint32_t k = low_k + (i % kRing) * (kTileBytes >> 4), d = buffers + (i & 1) * kKeys;
 #pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk) mma_f16_split(d, low_q + kk * 2, kHighWord, k + kk * 2, kHighWord, idesc_s, kk != 0);
+        for (int kk = 0; kk < kHeadDim / 16; ++kk) mma_f16_split(d, low_q + kk * 2, kHighWord, k + kk * 2, kHighWord, idesc_s, kk != 0 ? 1u : 0u);
         mma_commit(s_full(g, i & 1));
       };
       // O(i) = P_i V_i over columns 0..63 of buffer i % 2: P from tensor memory (columns 64..127, 16
@@ -228,7 +228,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       auto partial = [&](int i) {
         const uint32_t v = low_v + (i % kRing) * (kTileBytes >> 4), d = buffers + (i & 1) * kKeys;
 #pragma unroll
-        for (int kk = 0; kk < kKeys / 16; ++kk) mma_f16_tmem_a(d, d + kColumnP + kk * 8, v + kk * (2048 >> 4), kHighWord, idesc_o, kk != 0);
+        for (int kk = 0; kk < kKeys / 16; ++kk) mma_f16_tmem_a(d, d + kColumnP + kk * 8, v + kk * (2048 >> 4), kHighWord, idesc_o, kk != 0 ? 1u : 0u);
         mma_commit(o_full(g, i & 1));
       };
       bool alive = barrier_wait(q_full, 0, p.status, kWaitQ) && barrier_wait(k_full(0), 0, p.status, kWaitKeyFull);

@@ -242,8 +242,12 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       // K-major: 8-row groups are 1024 B apart; a step of 16 along K is 32 B inside the swizzle row.
       // MN-major: 64-wide chunks are kChunkBytes apart, groups of 8 K-rows 1024 B; 16 K-rows = 2048 B.
       constexpr uint32_t lead_a = A_MN ? kChunkBytes : 0, lead_b = B_MN ? kChunkBytes : 0;
-      constexpr uint32_t step_a = A_MN ? 2048 : 32, step_b = B_MN ? 2048 : 32;
-      uint32_t iteration = 0;
+      constexpr uint32_t step_a16 = (A_MN ? 2048 : 32) >> 4, step_b16 = (B_MN ? 2048 : 32) >> 4;
+      // Descriptors as (low, high) words stepped by one add, stage and phase as counters, no
+      // tcgen05 fence per k-block: what this lane does between two k-blocks is time the pipe can run dry.
+      constexpr uint32_t kHigh = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t low_a0 = (base >> 4) | ((lead_a >> 4) << 16), low_b0 = ((base + kBytesA) >> 4) | ((lead_b >> 4) << 16);
+      uint32_t s = 0, phase = 0;
       uint32_t local_tile = 0;
       bool alive = true;
       for (long long tile = blockIdx.x; alive && tile < p.num_tiles; tile += gridDim.x, ++local_tile) {
@@ -252,22 +256,19 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         if (!barrier_wait(tmem_empty_bar(acc), acc_phase ^ 1, p.status, kWaitTmemEmpty)) break;
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + acc * kTileN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++iteration) {
-          const int s = iteration % kStages;
-          const uint32_t phase = (iteration / kStages) & 1;
+        uint32_t accumulate = 0;
+        for (int kb = 0; kb < k_blocks; ++kb) {
           if (!barrier_wait(full_bar(s), phase, p.status, kWaitFull)) { alive = false; break; }
-          tcgen05_fence_after();
-          const uint32_t smem_a = base + s * kStageBytes;
-          const uint32_t smem_b = smem_a + kBytesA;
+          const uint32_t low_a = low_a0 + s * (kStageBytes >> 4), low_b = low_b0 + s * (kStageBytes >> 4);
 #pragma unroll
           for (int kk = 0; kk < kTileK / kMmaK; ++kk) {
-            const uint64_t desc_a = smem_descriptor(smem_a + kk * step_a, lead_a, 1024);
-            const uint64_t desc_b = smem_descriptor(smem_b + kk * step_b, lead_b, 1024);
-            mma_f16(tmem_d, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+            mma_f16_split(tmem_d, low_a + kk * step_a16, kHigh, low_b + kk * step_b16, kHigh, idesc, accumulate);
+            accumulate = 1;
           }
           mma_commit(empty_bar(s));                        // the stage is free once these MMAs have read it
-          if (kb == k_blocks - 1) mma_commit(tmem_full_bar(acc));  // and the tile is complete
+          if (++s == kStages) { s = 0; phase ^= 1; }
         }
+        if (alive) mma_commit(tmem_full_bar(acc));         // the tile is complete
       }
     }
   } else {
@@ -416,31 +417,36 @@ gemm_bias_act_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       constexpr uint32_t idesc = pair_instruction_descriptor(std::is_same_v<T, __nv_bfloat16>, A_MN, B_MN);
       constexpr uint32_t lead_a = A_MN ? kChunkBytes : 0, lead_b = B_MN ? kChunkBytes : 0;
       constexpr uint32_t step_a = A_MN ? 2048 : 32, step_b = B_MN ? 2048 : 32;
-      uint32_t iteration = 0;
       uint32_t local_tile = 0;
       bool alive = true;
+      // The tensor pipe holds only a couple of MMAs ahead of the one it executes, so whatever this
+      // lane does between the last MMA of one k-block and the first of the next is time the pipe
+      // can run dry: descriptors are (low, high) words stepped by one add, the stage and its
+      // phase are counters (no division), and there is no tcgen05 fence per k-block — the
+      // operands come from TMA through the full barrier, not from another thread's tcgen05 work.
+      constexpr uint32_t kHigh = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t step_a16 = step_a >> 4, step_b16 = step_b >> 4;
+      const uint32_t low_a0 = (base >> 4) | ((lead_a >> 4) << 16), low_b0 = ((base + kBytesA) >> 4) | ((lead_b >> 4) << 16);
+      uint32_t s = 0, phase = 0;
       for (long long tile = pair; alive && tile < p.num_tiles; tile += pairs, ++local_tile) {
         const uint32_t acc = local_tile & 1;
         const uint32_t acc_phase = (local_tile >> 1) & 1;
         if (!barrier_wait(tmem_empty_bar(acc), acc_phase ^ 1, p.status, kWaitTmemEmpty)) break;
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + acc * kTileN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++iteration) {
-          const int s = iteration % kPairStages;
-          const uint32_t phase = (iteration / kPairStages) & 1;
+        uint32_t accumulate = 0;
+        for (int kb = 0; kb < k_blocks; ++kb) {
           if (!barrier_wait(full_bar(s), phase, p.status, kWaitFull)) { alive = false; break; }
-          tcgen05_fence_after();
-          const uint32_t smem_a = base + s * kPairStageBytes;
-          const uint32_t smem_b = smem_a + kBytesA;
+          const uint32_t low_a = low_a0 + s * (kPairStageBytes >> 4), low_b = low_b0 + s * (kPairStageBytes >> 4);
 #pragma unroll
           for (int kk = 0; kk < kTileK / kMmaK; ++kk) {
-            const uint64_t desc_a = smem_descriptor(smem_a + kk * step_a, lead_a, 1024);
-            const uint64_t desc_b = smem_descriptor(smem_b + kk * step_b, lead_b, 1024);
-            mma_f16_pair(tmem_d, desc_a, desc_b, idesc, (kb | kk) != 0 ? 1u : 0u);
+            mma_f16_pair_split(tmem_d, low_a + kk * step_a16, kHigh, low_b + kk * step_b16, kHigh, idesc, accumulate);
+            accumulate = 1;
           }
           mma_commit_pair(empty_bar(s));
-          if (kb == k_blocks - 1) mma_commit_pair(tmem_full_bar(acc));
+          if (++s == kPairStages) { s = 0; phase ^= 1; }
         }
+        if (alive) mma_commit_pair(tmem_full_bar(acc));
       }
     }
   } else {

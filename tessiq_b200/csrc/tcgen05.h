@@ -97,47 +97,27 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64
 // The same, with each descriptor given as its constant high word and its low word (start address
 // and leading offset), so that stepping through a tile is one 32-bit add per operand.
 __device__ __forceinline__ void mma_f16_split(uint32_t tmem_d, uint32_t a_low, uint32_t a_high, uint32_t b_low, uint32_t b_high,
-                                              uint32_t idesc, bool accumulate) {
-  if (accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-        "setp.ne.b32 p, 1, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
-        ::"r"(tmem_d), "r"(a_low), "r"(a_high), "r"(b_low), "r"(b_high), "r"(idesc)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-        "setp.ne.b32 p, 0, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
-        ::"r"(tmem_d), "r"(a_low), "r"(a_high), "r"(b_low), "r"(b_high), "r"(idesc)
-        : "memory");
-  }
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_low), "r"(a_high), "r"(b_low), "r"(b_high), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 
 // D[tmem] (+)= A[tmem] * B[smem]: the A operand lies in tensor memory, one row per lane, two 16-bit
 // elements of K per 32-bit column (16 elements of K = 8 columns).
 __device__ __forceinline__ void mma_f16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_low, uint32_t b_high, uint32_t idesc,
-                                               bool accumulate) {
-  if (accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
-        "mov.b64 db, {%2, %3};\n\t"
-        "setp.ne.b32 p, 1, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
-        ::"r"(tmem_d), "r"(tmem_a), "r"(b_low), "r"(b_high), "r"(idesc)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
-        "mov.b64 db, {%2, %3};\n\t"
-        "setp.ne.b32 p, 0, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
-        ::"r"(tmem_d), "r"(tmem_a), "r"(b_low), "r"(b_high), "r"(idesc)
-        : "memory");
-  }
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "r"(b_low), "r"(b_high), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 
 // The mbarrier gets one arrival when every tcgen05 operation this thread issued so far is done.
@@ -251,6 +231,19 @@ __device__ __forceinline__ void mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, u
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// The same with each descriptor as (low, high) words and the accumulate flag as a predicate set
+// from a register: stepping through a tile is one 32-bit add per operand.
+__device__ __forceinline__ void mma_f16_pair_split(uint32_t tmem_d, uint32_t a_low, uint32_t a_high, uint32_t b_low, uint32_t b_high,
+                                                   uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_low), "r"(a_high), "r"(b_low), "r"(b_high), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
