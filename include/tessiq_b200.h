@@ -383,6 +383,36 @@ tq_status tq_gemm_bias_act_launch(tq_dtype dtype,
                                   int32_t device,
                                   void* stream);
 
+/* The same with a residual added after the activation and before the one rounding:
+ *   C[b] = act(op(A[b]) @ op(B[b]) + bias) + R[b]
+ * R is row-major [m,n] with leading dimension ldr and batch stride stride_r (elements), of C's type,
+ * or null (then this is tq_gemm_bias_act_launch). It replaces the elementwise `add` kernel the
+ * reference launches after a projection for `x + linear(y)` (a fused group of
+ * csrc/tessiq/codegen/cuda_emitter.cpp:212-255 reading the GEMM's result back from memory). */
+tq_status tq_gemm_bias_act_residual_launch(tq_dtype dtype,
+                                           tq_activation activation,
+                                           const void* a,
+                                           int64_t lda,
+                                           int32_t trans_a,
+                                           const void* b,
+                                           int64_t ldb,
+                                           int32_t trans_b,
+                                           const void* bias,
+                                           const void* residual,
+                                           int64_t ldr,
+                                           int64_t stride_r,
+                                           void* c,
+                                           int64_t ldc,
+                                           int64_t m,
+                                           int64_t n,
+                                           int64_t k,
+                                           int64_t batch,
+                                           int64_t stride_a,
+                                           int64_t stride_b,
+                                           int64_t stride_c,
+                                           int32_t device,
+                                           void* stream);
+
 /* ------------------------------------------------------------------------------------------ */
 /* Fused attention                                                                              */
 /* The reference has no attention kernel. This entry point replaces the sequence its compiler   */

@@ -82,6 +82,9 @@ SIGNATURES = {
     "tq_gemm_bias_act_launch": (c_int32, [c_int32, c_int32, c_void_p, c_int64, c_int32, c_void_p, c_int64,
                                            c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                            c_int64, c_int64, c_int64, c_int64, c_int32, c_void_p]),
+    "tq_gemm_bias_act_residual_launch": (c_int32, [c_int32, c_int32, c_void_p, c_int64, c_int32, c_void_p, c_int64, c_int32, c_void_p,
+                                                    c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                                    c_int64, c_int64, c_int64, c_int32, c_void_p]),
     "tq_attention_launch": (c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                        POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), POINTER(c_int64), c_double, c_int32,
                                        c_int32, c_void_p]),

@@ -16,9 +16,9 @@ What `compile_kernels` does in the reference (csrc/tessiq/torch/fused.cpp:470-68
     strided view map onto the reduction, row, GEMM and pack kernels;
   * `bmm -> scale -> [mask] -> _softmax -> bmm` (and the `_scaled_dot_product_*_attention`
     operators) become ONE fused attention kernel that reads Q, K and V where the projection left
-    them; `addmm -> gelu` becomes the GEMM with the activation in its epilogue; the reference
-    has rewrite patterns for the second (csrc/custom_ops/gemm_bias_gelu_tanh/*.pattern.tsr) and
-    nothing for the first;
+    them; `addmm -> gelu` becomes the GEMM with the activation in its epilogue and
+    `x + addmm(...)` the GEMM with the residual added there; the reference has a rewrite pattern
+    for the GELU one (csrc/custom_ops/gemm_bias_gelu_tanh/*.pattern.tsr) and nothing for the others;
   * nodes that depend on no input (a causal mask built from `arange`) are computed once and kept;
     nodes nobody reads after these rewrites are dropped;
   * views are metadata; whatever is left runs as the PyTorch operator on the same GPU and is
@@ -473,6 +473,35 @@ def _match_gemm_activation(node: fx.Node) -> tuple[fx.Node, str] | None:
     return source, "gelu_tanh" if node.kwargs.get("approximate", "none") == "tanh" else "gelu_erf"
 
 
+def _match_gemm_residual(node: fx.Node, order: dict) -> tuple[fx.Node, fx.Node, fx.Node] | None:
+    """`node` is `x + linear(y)` with the projection's result read by nobody else: returns
+    (addmm, residual operand, the operand that is the view of the addmm). The residual must exist
+    before the addmm runs, have the result's shape and type, and the add must be a plain one."""
+    if node.target is not aten.add.Tensor or node.kwargs.get("alpha", 1) != 1 or len(node.args) != 2:
+        return None
+    for through, other in ((node.args[0], node.args[1]), (node.args[1], node.args[0])):
+        if not (_is_tensor_node(through) and _is_tensor_node(other)):
+            continue
+        path: list[fx.Node] = []
+        source = through
+        while source.op == "call_function" and source.target in (aten.view.default, aten._unsafe_view.default, aten.reshape.default):
+            path.append(source)
+            source = source.args[0]
+        if source.op != "call_function" or source.target is not aten.addmm.default:
+            continue
+        bias = source.args[0].meta.get("val")
+        if source.kwargs.get("beta", 1) != 1 or source.kwargs.get("alpha", 1) != 1 or bias is None or bias.dim() != 1:
+            continue
+        value, result = other.meta["val"], node.meta["val"]
+        if source.meta["val"].dtype not in (torch.bfloat16, torch.float16) or value.dtype != result.dtype or \
+                tuple(value.shape) != tuple(result.shape) or tuple(through.meta["val"].shape) != tuple(result.shape):
+            continue
+        if any(len(n.users) != 1 for n in path + [source]) or order[other] > order[source]:
+            continue
+        return source, other, through
+    return None
+
+
 def build_recipe(gm: fx.GraphModule, math_mode: str = "fast") -> Recipe:
     """Turns an ATen-level FX graph into a recipe of kernel steps."""
     graph = gm.graph
@@ -484,7 +513,9 @@ def build_recipe(gm: fx.GraphModule, math_mode: str = "fast") -> Recipe:
     # rewrites: which node stands for a whole pattern, and which nodes that pattern swallows
     attention_at: dict[fx.Node, Attention] = {}
     gemm_act_at: dict[fx.Node, str] = {}        # addmm -> the activation in its epilogue
-    passes_through: set[fx.Node] = set()       # the activation nodes those epilogues made redundant
+    gemm_residual_at: dict[fx.Node, fx.Node] = {}   # addmm -> the tensor its epilogue adds
+    passes_through: dict[fx.Node, fx.Node] = {}     # activation / add nodes those epilogues made redundant -> the operand they hand on
+    order = {n: i for i, n in enumerate(graph.nodes)}
     absorbed: set[fx.Node] = set()
     notes: list[str] = []
     for node in graph.nodes:
@@ -508,14 +539,21 @@ def build_recipe(gm: fx.GraphModule, math_mode: str = "fast") -> Recipe:
             found = _match_gemm_activation(node)
             if found is not None and found[0] not in absorbed:
                 gemm_act_at[found[0]] = found[1]
-                passes_through.add(node)
+                passes_through[node] = node.args[0]
+        elif node.target is aten.add.Tensor and node in member_of and len(member_of[node].members) == 1:
+            found = _match_gemm_residual(node, order)
+            if found is not None and found[0] not in absorbed and found[0] not in gemm_act_at and found[0] not in gemm_residual_at:
+                gemm_residual_at[found[0]] = found[1]
+                passes_through[node] = found[2]
 
     def reads_of(node: fx.Node) -> list[fx.Node]:
         if node in attention_at:
             match = attention_at[node]
             return [match.q, match.k, match.v]
         if node in passes_through:
-            return [node.args[0]]
+            return [passes_through[node]]
+        if node in gemm_residual_at:
+            return list(node.all_input_nodes) + [gemm_residual_at[node]]
         if node in constant:
             return []
         if node in member_of:
@@ -556,11 +594,11 @@ def build_recipe(gm: fx.GraphModule, math_mode: str = "fast") -> Recipe:
         if node in attention_at:
             recipe.steps.append(_attention_step(attention_at[node]))
             continue
-        if node in gemm_act_at:
-            recipe.steps.append(_gemm_activation_step(node, gemm_act_at[node]))
+        if node in gemm_act_at or node in gemm_residual_at:
+            recipe.steps.append(_gemm_epilogue_step(node, gemm_act_at.get(node, "none"), gemm_residual_at.get(node)))
             continue
         if node in passes_through:
-            recipe.steps.append(Step("view", node.name, lambda env, name=node.args[0].name: env[name], [node.args[0].name]))
+            recipe.steps.append(Step("view", node.name, lambda env, name=passes_through[node].name: env[name], [passes_through[node].name]))
             continue
         if node in member_of:
             group = member_of[node]
@@ -605,18 +643,21 @@ def _constant_step(node: fx.Node) -> Step:
     return Step("constant", node.name, run, [])
 
 
-def _gemm_activation_step(addmm: fx.Node, activation: str) -> Step:
-    """act(bias + a @ b) with the activation in the GEMM's epilogue."""
+def _gemm_epilogue_step(addmm: fx.Node, activation: str, residual: fx.Node | None) -> Step:
+    """act(bias + a @ b) + residual with the activation and the addition in the GEMM's epilogue."""
     bias, a, b = addmm.args[:3]
-    names = [bias.name, a.name, b.name]
-    fallback = (lambda t: torch.nn.functional.gelu(t, approximate="tanh")) if activation == "gelu_tanh" else torch.nn.functional.gelu
+    names = [bias.name, a.name, b.name] + ([residual.name] if residual is not None else [])
+    fallback = {"gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh"), "gelu_erf": torch.nn.functional.gelu,
+                "none": lambda t: t}[activation]
 
     def run(env):
-        bias_t, a_t, b_t = (env[name] for name in names)
+        bias_t, a_t, b_t = (env[name] for name in names[:3])
+        extra = env[names[3]] if residual is not None else None
         try:
-            return ops.gemm(a_t, b_t, bias_t, activation)
+            return ops.gemm(a_t, b_t, bias_t, activation, None if extra is None else ops.contiguous(extra))
         except Declined:
-            return fallback(torch.addmm(bias_t, a_t, b_t))
+            out = fallback(torch.addmm(bias_t, a_t, b_t))
+            return out if extra is None else out + extra.reshape(out.shape)
 
     return Step("gemm", addmm.name, run, names)
 

@@ -65,6 +65,8 @@ struct GemmParams {
   int tiles_m, tiles_n;
   long long num_tiles;
   const void* bias;
+  const void* residual;            // added after the activation, or null
+  long long ldr, stride_r;
   void* c;
   long long ldc, stride_c;
   int activation;
@@ -107,29 +109,63 @@ __device__ __forceinline__ void tile_coordinates(long long tile, const GemmParam
 // the 128 columns of its half. Per 64 columns: tcgen05.ld (lane i holds row i), + bias, activation,
 // one rounding, then the 32 x 64 block goes through 4 KiB of this warp's shared memory (16-byte
 // units XOR-swizzled by row, conflict-free both ways) so that each store instruction writes four
-// whole 128-byte lines of C instead of 32 scattered 16-byte pieces.
+// whole 128-byte lines of C instead of 32 scattered 16-byte pieces. A residual tile (added after
+// the activation, before the one rounding) takes the same road the other way: whole lines from
+// global memory into the staging block, then each thread picks up its own row.
 template <typename T>
 __device__ __forceinline__ void epilogue_rows(uint32_t tmem_accumulator, int quarter, int half, int lane, const float* bias_tile,
-                                              T* c_tile, long long ldc, int rows_left, int columns_left, int activation,
-                                              unsigned char* staging, bool vector_ok) {
+                                              T* c_tile, long long ldc, const T* residual_tile, long long ldr, int rows_left,
+                                              int columns_left, int activation, unsigned char* staging, bool vector_ok) {
   const int row = quarter * 32 + lane;
   const uint32_t staging_address = smem_address(staging);
 #pragma unroll 1
   for (int step = 0; step < (kTileN / 2) / kStoreColumns; ++step) {
     const int column0 = half * (kTileN / 2) + step * kStoreColumns;
+    uint4 residual_words[8];
+    if (residual_tile != nullptr && vector_ok) {      // issued before the tensor-memory load so the two latencies overlap
+      const int unit = lane & 7;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = quarter * 32 + i * 4 + (lane >> 3);
+        residual_words[i] = make_uint4(0, 0, 0, 0);
+        if (r < rows_left && column0 + unit * 8 < columns_left) {
+          residual_words[i] = __ldg(reinterpret_cast<const uint4*>(residual_tile + static_cast<long long>(r) * ldr + column0 + unit * 8));
+        }
+      }
+    }
     uint32_t r0[32], r1[32];
     tmem_load_32(tmem_accumulator + column0 + (static_cast<uint32_t>(quarter * 32) << 16), r0);
     tmem_load_32(tmem_accumulator + column0 + 32 + (static_cast<uint32_t>(quarter * 32) << 16), r1);
     tmem_load_wait();
     if (vector_ok) {
+      if (residual_tile != nullptr) {
+        const int unit = lane & 7;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = i * 4 + (lane >> 3);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(staging_address + r * 128 + ((unit ^ (r & 7)) << 4)),
+                       "r"(residual_words[i].x), "r"(residual_words[i].y), "r"(residual_words[i].z), "r"(residual_words[i].w)
+                       : "memory");
+        }
+        __syncwarp();
+      }
 #pragma unroll
       for (int unit = 0; unit < 8; ++unit) {
-        Vec<T, 8> out;
+        Vec<T, 8> out, add;
+        if (residual_tile != nullptr) {
+          uint4 word;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(word.x), "=r"(word.y), "=r"(word.z), "=r"(word.w)
+                       : "r"(staging_address + lane * 128 + ((unit ^ (lane & 7)) << 4))
+                       : "memory");
+          add = *reinterpret_cast<const Vec<T, 8>*>(&word);
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int j = unit * 8 + e;
-          const float value = __uint_as_float(j < 32 ? r0[j] : r1[j - 32]) + bias_tile[column0 + j];
-          out.v[e] = from_compute<T, float>(activate(value, activation));
+          float value = activate(__uint_as_float(j < 32 ? r0[j] : r1[j - 32]) + bias_tile[column0 + j], activation);
+          if (residual_tile != nullptr) value += to_compute(add.v[e]);
+          out.v[e] = from_compute<T, float>(value);
         }
         const uint4 word = *reinterpret_cast<const uint4*>(&out);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(staging_address + lane * 128 + ((unit ^ (lane & 7)) << 4)),
@@ -155,11 +191,13 @@ __device__ __forceinline__ void epilogue_rows(uint32_t tmem_accumulator, int qua
       __syncwarp();
     } else if (row < rows_left) {
       T* c_row = c_tile + static_cast<long long>(row) * ldc + column0;
+      const T* residual_row = residual_tile == nullptr ? nullptr : residual_tile + static_cast<long long>(row) * ldr + column0;
 #pragma unroll
       for (int j = 0; j < 64; ++j) {
         if (column0 + j < columns_left) {
-          const float value = __uint_as_float(j < 32 ? r0[j] : r1[j - 32]) + bias_tile[column0 + j];
-          c_row[j] = from_compute<T, float>(activate(value, activation));
+          float value = activate(__uint_as_float(j < 32 ? r0[j] : r1[j - 32]) + bias_tile[column0 + j], activation);
+          if (residual_row != nullptr) value += to_compute(residual_row[j]);
+          c_row[j] = from_compute<T, float>(value);
         }
       }
     }
@@ -277,7 +315,8 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const int epilogue_thread = threadIdx.x - 64;
     const int quarter = warp & 3, half = (warp - 2) >> 2;
     unsigned char* staging = aligned + kStages * kStageBytes + 2 * kTileN * sizeof(float) + 256 + (warp - 2) * kStoreBytes;
-    const bool vector_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (p.stride_c % 8 == 0) && (p.n % 8 == 0);
+    const bool vector_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (p.stride_c % 8 == 0) && (p.n % 8 == 0) &&
+                           (p.residual == nullptr || ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) && (p.stride_r % 8 == 0)));
     uint32_t local_tile = 0;
     for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++local_tile) {
       int batch, tile_m, tile_n;
@@ -296,8 +335,10 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");   // bias_tile is complete
 
       T* c_tile = static_cast<T*>(p.c) + static_cast<long long>(batch) * p.stride_c + static_cast<long long>(tile_m) * kTileM * p.ldc + n0;
-      epilogue_rows<T>(tmem_base + acc * kTileN, quarter, half, lane, bias_tile, c_tile, p.ldc, p.m - tile_m * kTileM, p.n - n0,
-                       p.activation, staging, vector_ok);
+      const T* residual_tile = p.residual == nullptr ? nullptr : static_cast<const T*>(p.residual) + static_cast<long long>(batch) * p.stride_r +
+                                                                  static_cast<long long>(tile_m) * kTileM * p.ldr + n0;
+      epilogue_rows<T>(tmem_base + acc * kTileN, quarter, half, lane, bias_tile, c_tile, p.ldc, residual_tile, p.ldr, p.m - tile_m * kTileM,
+                       p.n - n0, p.activation, staging, vector_ok);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) barrier_arrive(tmem_empty_bar(acc));   // this warp has read its part of the accumulator
@@ -454,7 +495,8 @@ gemm_bias_act_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     const int epilogue_thread = threadIdx.x - 64;
     const int quarter = warp & 3, half = (warp - 2) >> 2;
     unsigned char* staging = aligned + kPairStages * kPairStageBytes + 2 * kTileN * sizeof(float) + 256 + (warp - 2) * kStoreBytes;
-    const bool vector_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (p.stride_c % 8 == 0) && (p.n % 8 == 0);
+    const bool vector_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (p.stride_c % 8 == 0) && (p.n % 8 == 0) &&
+                           (p.residual == nullptr || ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) && (p.stride_r % 8 == 0)));
     uint32_t local_tile = 0;
     for (long long tile = pair; tile < p.num_tiles; tile += pairs, ++local_tile) {
       int batch, tile_m, tile_n;
@@ -474,8 +516,10 @@ gemm_bias_act_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 
       const int row0 = tile_m * kPairTileM + static_cast<int>(rank) * kTileM;
       T* c_tile = static_cast<T*>(p.c) + static_cast<long long>(batch) * p.stride_c + static_cast<long long>(row0) * p.ldc + n0;
-      epilogue_rows<T>(tmem_base + acc * kTileN, quarter, half, lane, bias_tile, c_tile, p.ldc, p.m - row0, p.n - n0, p.activation,
-                       staging, vector_ok);
+      const T* residual_tile = p.residual == nullptr ? nullptr : static_cast<const T*>(p.residual) + static_cast<long long>(batch) * p.stride_r +
+                                                                  static_cast<long long>(row0) * p.ldr + n0;
+      epilogue_rows<T>(tmem_base + acc * kTileN, quarter, half, lane, bias_tile, c_tile, p.ldc, residual_tile, p.ldr, p.m - row0, p.n - n0,
+                       p.activation, staging, vector_ok);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) remote_arrive(peer_address(tmem_empty_bar(acc), 0));   // tell the leader: this part is drained
@@ -572,9 +616,19 @@ extern "C" tq_status tq_gemm_bias_act_launch(tq_dtype dtype, tq_activation activ
                                              const void* bias, void* c, int64_t ldc, int64_t m, int64_t n, int64_t k,
                                              int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_c,
                                              int32_t device, void* stream) {
+  return tq_gemm_bias_act_residual_launch(dtype, activation, a, lda, trans_a, b, ldb, trans_b, bias, nullptr, 0, 0, c, ldc, m, n, k,
+                                          batch, stride_a, stride_b, stride_c, device, stream);
+}
+
+extern "C" tq_status tq_gemm_bias_act_residual_launch(tq_dtype dtype, tq_activation activation, const void* a, int64_t lda,
+                                                      int32_t trans_a, const void* b, int64_t ldb, int32_t trans_b,
+                                                      const void* bias, const void* residual, int64_t ldr, int64_t stride_r,
+                                                      void* c, int64_t ldc, int64_t m, int64_t n, int64_t k, int64_t batch,
+                                                      int64_t stride_a, int64_t stride_b, int64_t stride_c, int32_t device,
+                                                      void* stream) {
   TQ_RECORD_OR_RUN([=](int32_t d, void* s) {
-    return tq_gemm_bias_act_launch(dtype, activation, a, lda, trans_a, b, ldb, trans_b, bias, c, ldc, m, n, k, batch, stride_a,
-                                   stride_b, stride_c, d, s);
+    return tq_gemm_bias_act_residual_launch(dtype, activation, a, lda, trans_a, b, ldb, trans_b, bias, residual, ldr, stride_r, c, ldc,
+                                            m, n, k, batch, stride_a, stride_b, stride_c, d, s);
   });
   TQ_REQUIRE(dtype == TQ_BF16 || dtype == TQ_F16, TQ_UNSUPPORTED,
              "the tensor-core GEMM takes bf16 or f16 operands, not %s", tq::dtype_name(dtype));
@@ -593,6 +647,8 @@ extern "C" tq_status tq_gemm_bias_act_launch(tq_dtype dtype, tq_activation activ
                  (batch == 1 || (stride_a % 8 == 0 && stride_b % 8 == 0)),
              TQ_UNSUPPORTED, "operands must be 16-byte aligned with leading dimensions and batch strides that are multiples of 8 elements");
   TQ_REQUIRE(tq::aligned_to(c, 2) && (bias == nullptr || tq::aligned_to(bias, 2)), TQ_INVALID_ARGUMENT, "misaligned result or bias");
+  TQ_REQUIRE(residual == nullptr || (tq::aligned_to(residual, 2) && ldr >= n), TQ_INVALID_ARGUMENT,
+             "misaligned residual, or its leading dimension is smaller than a row");
   if (tq_status s = tq::use_device(device)) return s;
   int* status = tq::device_status_word(device);
   TQ_REQUIRE(status != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
@@ -620,6 +676,9 @@ extern "C" tq_status tq_gemm_bias_act_launch(tq_dtype dtype, tq_activation activ
   p.tiles_n = static_cast<int>((n + tq::kTileN - 1) / tq::kTileN);
   p.num_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * batch;
   p.bias = bias;
+  p.residual = residual;
+  p.ldr = ldr;
+  p.stride_r = stride_r;
   p.c = c;
   p.ldc = ldc;
   p.stride_c = stride_c;

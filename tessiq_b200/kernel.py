@@ -458,12 +458,13 @@ class GemmKernel(Kernel):
     kind = "gemm"
     packs_inputs = False
 
-    def __init__(self, activation: str = "none", has_bias: bool = False, inputs=None, output: str = "out"):
-        names = list(inputs) if inputs is not None else (["a", "b", "bias"] if has_bias else ["a", "b"])
+    def __init__(self, activation: str = "none", has_bias: bool = False, inputs=None, output: str = "out", has_residual: bool = False):
+        names = list(inputs) if inputs is not None else (["a", "b"] + (["bias"] if has_bias else []) + (["residual"] if has_residual else []))
         super().__init__(names, output)
         self.activation = {"none": _lib.ACT_NONE, "gelu": _lib.ACT_GELU_ERF, "gelu_erf": _lib.ACT_GELU_ERF,
                            "gelu_tanh": _lib.ACT_GELU_TANH}[activation]
         self.has_bias = has_bias
+        self.has_residual = has_residual      # launch takes [a, b, (bias), (residual)]: act(a @ b + bias) + residual
 
     def output_shape(self, inputs):
         a, b = inputs[0], inputs[1]
@@ -484,7 +485,8 @@ class GemmKernel(Kernel):
         self._check_count(inputs)
         a, b = inputs[0], inputs[1]
         bias = inputs[2] if self.has_bias else None
-        device = _device_of([t for t in (a, b, bias, out) if t is not None])
+        residual = inputs[-1] if self.has_residual else None
+        device = _device_of([t for t in (a, b, bias, residual, out) if t is not None])
         if a.dim() != b.dim() or a.dim() not in (2, 3):
             raise _lib.Declined("the GEMM kernel takes two matrices or two batches of matrices")
         if a.dtype != b.dtype or out.dtype != a.dtype:
@@ -500,13 +502,15 @@ class GemmKernel(Kernel):
             raise ValueError("the GEMM result must be a packed tensor of shape [.., m, n]")
         if bias is not None and (bias.numel() != n or not bias.is_contiguous() or bias.dtype != out.dtype):
             raise _lib.Declined("the bias must be one packed value per output column")
+        if residual is not None and (residual.dtype != out.dtype or residual.numel() != out.numel() or not residual.is_contiguous()):
+            raise _lib.Declined("the residual must be a packed tensor of the result's shape and type")
         trans_a, lda = self._operand(a)
         trans_b, ldb = self._operand(b)
         stride_a = a.stride(0) if a.dim() == 3 else 0
         stride_b = b.stride(0) if b.dim() == 3 else 0
-        check(lib.tq_gemm_bias_act_launch(dtype_code(a.dtype), self.activation, _pointer(a), lda, trans_a, _pointer(b),
-                                          ldb, trans_b, _pointer(bias), _pointer(out), n, m, n, k, batch, stride_a,
-                                          stride_b, m * n, device, ctypes.c_void_p(_stream(stream, device))))
+        check(lib.tq_gemm_bias_act_residual_launch(dtype_code(a.dtype), self.activation, _pointer(a), lda, trans_a, _pointer(b),
+                                                   ldb, trans_b, _pointer(bias), _pointer(residual), n, m * n, _pointer(out), n, m, n, k,
+                                                   batch, stride_a, stride_b, m * n, device, ctypes.c_void_p(_stream(stream, device))))
 
 
 class AttentionKernel(Kernel):

@@ -297,18 +297,19 @@ def batch_norm_eval(x, weight, bias, running_mean, running_var, eps):
 # GEMM
 
 
-def _gemm(a, b, bias, activation):
+def _gemm(a, b, bias, activation, residual=None):
     out = torch.empty([*a.shape[:-1], b.shape[-1]], dtype=a.dtype, device=a.device)
     if out.numel() == 0:
         return out
-    kernel = GemmKernel(activation, has_bias=bias is not None)
-    kernel.launch([a, b] if bias is None else [a, b, bias], out, stream=None)
+    kernel = GemmKernel(activation, has_bias=bias is not None, has_residual=residual is not None)
+    kernel.launch([t for t in (a, b, bias, residual) if t is not None], out, stream=None)
     return out
 
 
-def gemm(a, b, bias=None, activation="none"):
-    """act(a @ b + bias): the GEMM kernel with any of its epilogues ("none", "gelu_erf", "gelu_tanh")."""
-    return _gemm(a, b, bias, activation)
+def gemm(a, b, bias=None, activation="none", residual=None):
+    """act(a @ b + bias) + residual: the GEMM kernel with any of its epilogues ("none", "gelu_erf",
+    "gelu_tanh"); `residual` is a packed tensor with the result's element count."""
+    return _gemm(a, b, bias, activation, residual)
 
 
 def mm(a, b):

@@ -84,6 +84,24 @@ def test_matmul_form_b_read_in_place(tq, m, n, k):
     check(got, truth(a, b, bias, "gelu_tanh"), torch.bfloat16, k)
 
 
+@pytest.mark.parametrize("m, n, k", [(128, 256, 64), (300, 520, 200), (129, 264, 72), (2048, 768, 3072), (513, 24, 136), (96, 81, 64)])
+@pytest.mark.parametrize("act", ["none", "gelu_tanh"])
+def test_residual_rides_in_the_epilogue(tq, m, n, k, act):
+    # x + linear(y): act(a @ w.T + bias) + r in one kernel, rounded once (n = 81: the scalar epilogue)
+    g = torch.Generator().manual_seed(m + 2 * n + 3 * k)
+    a = (torch.randn(m, k, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(n, k, generator=g) * (1.0 / np.sqrt(k))).bfloat16()
+    bias = (torch.randn(n, generator=g) * 0.5).bfloat16()
+    r = torch.randn(m, n, generator=g).bfloat16()
+    got = tq.gemm(a.cuda(), w.cuda().t(), bias.cuda(), act, r.cuda())
+    check(got, truth(a, w.t(), bias, act if act != "none" else None) + r.double(), torch.bfloat16, k)
+    # and against the oracle's two nodes (addmm, add), each rounded
+    if act == "none":
+        ref = (torch.addmm(bias, a, w.t()) + r).float()
+        torch.testing.assert_close(got.cpu().float(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
+    assert poll() == 0
+
+
 def test_against_the_oracle_and_golden(tq, golden):
     x, w, bias = (torch.from_numpy(golden[name]) for name in ("gemm_x", "gemm_w", "gemm_bias"))
     xb, wb, bb = x.bfloat16(), w.bfloat16(), bias.bfloat16()
