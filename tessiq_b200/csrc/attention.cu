@@ -210,11 +210,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (lane == 0 && steps[g] > 0) {
       constexpr uint32_t idesc_s = attn_instruction_descriptor<T>(kKeys, false);
       constexpr uint32_t idesc_o = attn_instruction_descriptor<T>(kHeadDim, true);
-      // Descriptors as (low, high) words: the high word is one constant (stride offset 1024, version
-      // 1, 128-byte swizzle), the low word is (address >> 4) | leading offset, stepped by adds.
-      constexpr uint32_t kHighWord = (1024u >> 4) | (1u << 14) | (2u << 29);
-      const uint32_t low_q = (base + kOffsetQ + g * kTileBytes) >> 4, low_k = (base + kOffsetK) >> 4;
-      const uint32_t low_v = ((base + kOffsetV) >> 4) | ((kTileBytes >> 4) << 16);
+      // Descriptors as (low, high) words: one constant high word, low words stepped by adds.
+      constexpr uint32_t kHighWord = kDescriptorHigh;
+      const uint32_t low_q = descriptor_low(base + kOffsetQ + g * kTileBytes, 0), low_k = descriptor_low(base + kOffsetK, 0);
+      const uint32_t low_v = descriptor_low(base + kOffsetV, kTileBytes);
       const uint32_t buffers = tmem_base + static_cast<uint32_t>(2 * g * kKeys);     // buffer b at + 128 b
       // S(i) = Q K_i^T into buffer i % 2: both operands K-major, 16 elements of K = 32 B in the swizzle row
       auto scores = [&](int i) {

@@ -283,8 +283,8 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       constexpr uint32_t step_a16 = (A_MN ? 2048 : 32) >> 4, step_b16 = (B_MN ? 2048 : 32) >> 4;
       // Descriptors as (low, high) words stepped by one add, stage and phase as counters, no
       // tcgen05 fence per k-block: what this lane does between two k-blocks is time the pipe can run dry.
-      constexpr uint32_t kHigh = (1024u >> 4) | (1u << 14) | (2u << 29);
-      const uint32_t low_a0 = (base >> 4) | ((lead_a >> 4) << 16), low_b0 = ((base + kBytesA) >> 4) | ((lead_b >> 4) << 16);
+      constexpr uint32_t kHigh = kDescriptorHigh;
+      const uint32_t low_a0 = descriptor_low(base, lead_a), low_b0 = descriptor_low(base + kBytesA, lead_b);
       uint32_t s = 0, phase = 0;
       uint32_t local_tile = 0;
       bool alive = true;
@@ -465,9 +465,9 @@ gemm_bias_act_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       // can run dry: descriptors are (low, high) words stepped by one add, the stage and its
       // phase are counters (no division), and there is no tcgen05 fence per k-block — the
       // operands come from TMA through the full barrier, not from another thread's tcgen05 work.
-      constexpr uint32_t kHigh = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kHigh = kDescriptorHigh;
       constexpr uint32_t step_a16 = step_a >> 4, step_b16 = step_b >> 4;
-      const uint32_t low_a0 = (base >> 4) | ((lead_a >> 4) << 16), low_b0 = ((base + kBytesA) >> 4) | ((lead_b >> 4) << 16);
+      const uint32_t low_a0 = descriptor_low(base, lead_a), low_b0 = descriptor_low(base + kBytesA, lead_b);
       uint32_t s = 0, phase = 0;
       for (long long tile = pair; alive && tile < p.num_tiles; tile += pairs, ++local_tile) {
         const uint32_t acc = local_tile & 1;

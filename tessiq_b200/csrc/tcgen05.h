@@ -43,19 +43,6 @@ __device__ __forceinline__ bool barrier_try_wait(uint32_t bar, uint32_t parity) 
 // Waits for the phase of `bar` with the given parity, for a bounded number of polls. When the
 // bound runs out (or another thread's already did) the status word gets `code` and the caller
 // must leave its loop.
-// One non-blocking look at the phase of `bar` with the given parity (for a thread that polls
-// several barriers in turn).
-__device__ __forceinline__ bool barrier_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done != 0;
-}
 __device__ __forceinline__ bool barrier_wait(uint32_t bar, uint32_t parity, int* status, int code) {
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
     if (barrier_try_wait(bar, parity)) return true;
@@ -84,18 +71,9 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns)
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// D[tmem] (+)= A[smem] * B[smem], 128 x N x 16, issued by one thread.
-__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// The same, with each descriptor given as its constant high word and its low word (start address
-// and leading offset), so that stepping through a tile is one 32-bit add per operand.
+// D[tmem] (+)= A[smem] * B[smem], 128 x N x 16, issued by one thread. Each descriptor is given as
+// its constant high word and its low word (start address and leading offset), so that stepping
+// through a tile is one 32-bit add per operand (see descriptor_low for the bit layout).
 __device__ __forceinline__ void mma_f16_split(uint32_t tmem_d, uint32_t a_low, uint32_t a_high, uint32_t b_low, uint32_t b_high,
                                               uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -154,20 +132,17 @@ __device__ __forceinline__ void tmem_store_32(uint32_t address, const uint32_t (
 }
 __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor, 128-byte swizzle. Bits: [0,14) start address >> 4,
-// [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4, [46,48) version = 1,
-// [61,64) layout = 2 (SWIZZLE_128B). For a K-major operand the stride offset is the distance
-// between 8-row groups (8 x 128 B) and the leading offset is unused; for an MN-major operand the
-// leading offset is the distance between 64-element chunks along M/N and the stride offset the
-// distance between groups of 8 K-rows.
-__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t leading_bytes, uint32_t stride_bytes) {
-  uint64_t desc = 0;
-  desc |= static_cast<uint64_t>((address & 0x3ffff) >> 4);
-  desc |= static_cast<uint64_t>((leading_bytes >> 4) & 0x3fff) << 16;
-  desc |= static_cast<uint64_t>((stride_bytes >> 4) & 0x3fff) << 32;
-  desc |= static_cast<uint64_t>(1) << 46;
-  desc |= static_cast<uint64_t>(2) << 61;
-  return desc;
+// Shared-memory matrix descriptor, 128-byte swizzle, as two 32-bit words.
+//   low word:  [0,14) start address >> 4, [16,30) leading byte offset >> 4
+//   high word: [0,14) stride byte offset >> 4, [14,16) version = 1, [29,32) layout = 2 (SWIZZLE_128B)
+// For a K-major operand the stride offset is the distance between 8-row groups (8 x 128 B = 1024)
+// and the leading offset is unused; for an MN-major operand the leading offset is the distance
+// between 64-element chunks along M/N and the stride offset the distance between groups of 8
+// K-rows (again 1024). Stepping 16 elements along K is +32 B (K-major) or +2048 B (MN-major) on the
+// start address, i.e. +2 or +128 on the low word.
+constexpr uint32_t kDescriptorHigh = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t descriptor_low(uint32_t address, uint32_t leading_bytes) {
+  return ((address & 0x3ffff) >> 4) | ((leading_bytes >> 4) << 16);
 }
 
 __device__ __forceinline__ float exp2_ftz(float t) {
@@ -225,17 +200,7 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t address, uint32_t col
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
 }
 
-__device__ __forceinline__ void mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// The same with each descriptor as (low, high) words and the accumulate flag as a predicate set
-// from a register: stepping through a tile is one 32-bit add per operand.
+// The CTA-pair form (cta_group::2): one MMA over both CTAs' tiles, descriptors as (low, high) words.
 __device__ __forceinline__ void mma_f16_pair_split(uint32_t tmem_d, uint32_t a_low, uint32_t a_high, uint32_t b_low, uint32_t b_high,
                                                    uint32_t idesc, uint32_t accumulate) {
   asm volatile(
