@@ -770,6 +770,10 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
     if (vec < 1) vec = 1;
     while (vec > 1 && inner % vec != 0) vec /= 2;
     if ((op == TQ_ARGMAX || op == kOpMoments) && vec > 4) vec = 4;  // their per-column state is large
+    if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_VEC")) {    // tuning override: 1, 2, 4 or 8
+      const int value = std::atoi(forced);
+      if ((value == 1 || value == 2 || value == 4 || value == 8) && value * size <= 16 && inner % value == 0) vec = value;
+    }
     p.vec = vec;
     long long groups = (inner + vec - 1) / vec;
     // A warp reads 32 vectors (512 bytes) of one row; the CTA's 8 warps read 8 consecutive rows.
