@@ -54,7 +54,13 @@ constexpr int kGroups = 2;            // query tiles per CTA
 constexpr int kKeys = 128;            // keys per step
 constexpr int kRing = 4;              // stages of the key ring and of the value ring
 constexpr int kAttnThreads = 384;     // 8 softmax warps; producer and issuer in a third group of four warps
-constexpr int kSoftmaxRegisters = 224, kOtherRegisters = 56;   // 256 x 224 + 128 x 56 = the 64 K registers of an SM
+// setmaxnreg moves registers inside the CTA's own allocation (384 threads x 168 at launch): what the
+// third group of four warps gives up is exactly what the eight softmax warps take. An increase
+// beyond what was released would wait for ever.
+constexpr int kLaunchRegisters = 168, kSoftmaxRegisters = 224, kOtherRegisters = 56;
+static_assert(256 * (kSoftmaxRegisters - kLaunchRegisters) <= 128 * (kLaunchRegisters - kOtherRegisters),
+              "the softmax warps would wait for registers nobody releases");
+static_assert(kLaunchRegisters == (65536 / kAttnThreads) / 8 * 8, "ptxas gives a CTA of this size this many registers per thread");
 constexpr uint32_t kTileBytes = kRows * kHeadDim * 2;       // 16 KiB: a Q, K or V tile
 constexpr uint32_t kOffsetQ = 0;
 constexpr uint32_t kOffsetK = kOffsetQ + kGroups * kTileBytes;
