@@ -21,6 +21,9 @@ the step before come down (the 4 GB of results per step are what bounds it).
 With more than one GPU every rank runs the same step on its own rows (the path shards by rows with
 no exchange), so scaling is weak; the times are combined as the max over ranks.
 
+Before anything is timed, rank 0 runs the 26 operations on a 512-row sample and holds them against
+the CPU device's results (`parity` in the line; a mismatch ends the run with nothing timed).
+
 `--impl reference` times the reference's CPU implementation of the same step (PyTorch's CPU
 kernels, which its CPU device `tessiq:0` forwards every operator to) on the host cores, on a
 bounded sample of the rows.
@@ -217,6 +220,9 @@ def run_ours(args) -> dict:
 
     from tessiq_b200 import ops
 
+    # Parity first (rank 0; the other ranks run the same kernels): a mismatch stops the run before anything is timed.
+    parity = parity_gate(local) if rank == 0 else None
+
     step = Step(local)
     stream = torch.cuda.Stream(device=local)
     raw = stream.cuda_stream
@@ -393,6 +399,8 @@ def run_ours(args) -> dict:
         "kernels": per_op,
         "extra": extra,
     }
+    if parity is not None:
+        line["parity"] = parity
     if rank == 0 and world == 1:
         line["cpu_baseline"] = cpu_baseline(sample_rows=2048, repeats=3)
     if world > 1:
@@ -698,6 +706,47 @@ DOMINANT_TRAFFIC_BYTES = 964180992
 
 # ---------------------------------------------------------------------------------------------
 # The step on the host CPU (the reference's CPU device)
+
+
+def parity_gate(device: int, sample_rows: int = 512) -> dict:
+    """Before any timing: the 26 operations on a sample of rows, GPU against the CPU device's
+    results (the checker; the reference gates its own benchmarks the same way,
+    bench/gemm_bias_gelu.py:91-95). Bit-exact for argmax, amax and pack; 1e-5 for f32 (sums against
+    1e-5 of the sum of magnitudes); 1e-2 of the largest value for bf16. Raises on a mismatch."""
+    import torch
+
+    from tessiq_b200 import ops
+
+    g = torch.Generator().manual_seed(4321)
+    x = torch.randn(sample_rows, WIDTH, generator=g)
+    gamma, beta = 1 + torch.randn(WIDTH, generator=g) * 0.02, torch.randn(WIDTH, generator=g) * 0.02
+    gamma_t, beta_t = 1 + torch.randn(sample_rows, generator=g) * 0.02, torch.randn(sample_rows, generator=g) * 0.02
+    expected = cpu_step(x, gamma, beta, gamma_t, beta_t)
+    dev = f"cuda:{device}"
+    got, labels = [], []
+    for dtype in (torch.float32, torch.bfloat16):
+        xd = x.to(dtype).to(dev)
+        params = [t.to(dtype).to(dev) for t in (gamma, beta, gamma_t, beta_t)]
+        for view, width, gg, bb, where in ((xd, WIDTH, params[0], params[1], "rows"), (xd.t(), sample_rows, params[2], params[3], "cols")):
+            got += [ops.sum(view, -1), ops.mean(view, -1), ops.amax(view, -1), ops.argmax(view, -1), ops.softmax(view, -1),
+                    ops.layer_norm(view, [width], gg, bb, 1e-5)]
+            labels += [f"{op}_{where}_{dtype}" for op in ("sum", "mean", "amax", "argmax", "softmax", "layer_norm")]
+        got.append(ops.contiguous(xd.t()))
+        labels.append(f"pack_{dtype}")
+    torch.cuda.synchronize()
+    magnitude = x.abs().sum(-1).max().item()
+    for label, mine, ref in zip(labels, got, expected):
+        mine = mine.cpu()
+        if label.startswith(("argmax", "amax", "pack")):
+            ok = torch.equal(mine, ref)
+        elif "float32" in label:
+            atol = 1e-5 * magnitude if label.startswith("sum") else 1e-5 * max(ref.abs().max().item(), 1e-30)
+            ok = torch.allclose(mine, ref, rtol=1e-5, atol=atol)
+        else:
+            ok = torch.allclose(mine.float(), ref.float(), rtol=1e-2, atol=1e-2 * max(ref.float().abs().max().item(), 1e-30))
+        if not ok:
+            raise SystemExit(f"parity gate failed on {label}: the GPU result differs from the CPU device's; nothing was timed")
+    return {"rows": sample_rows, "checks": len(labels), "ok": True}
 
 
 def cpu_step(x32, gamma, beta, gamma_t, beta_t):
