@@ -291,17 +291,25 @@ struct SoftmaxStatReducer {
   __device__ static Acc shuffle(Acc a, int offset) { return Acc{shfl_xor(a.m, offset), shfl_xor(a.s, offset)}; }
   template <int VEC> using Local = Acc;
   template <int VEC> __device__ static Acc local_identity() { return identity(); }
-  // Per element: one maximum, one (rarely taken, three-instruction) rescale, one exponential. The
-  // threads of a warp walk different columns, so a branch with a long body would run for almost
-  // every element; this form keeps the rare part to a predicated multiply.
+  // `m` is a reference point, not necessarily the maximum: softmax is exp(x - m) / sum exp(x - m) for
+  // any m, so a thread keeps the first value it sees and only moves the reference (rescaling its
+  // sum) when an element lies more than 2^kSlack above it — rare, and then a real branch. Per
+  // element that leaves one FMA, one ex2 and one add (the exact running maximum with its
+  // predicated rescale was 24 instructions per element and made this pass issue-bound). Terms are
+  // at most 2^kSlack, far from overflow in f32; `combine` brings two references together exactly.
+  static constexpr float kSlack = 32.f;
   template <int VEC> __device__ static void step(Acc& local, T v, long long) {
     const float x = to_compute(v);
-    const float m = ExtremeReducer<float, true>::combine(local.m, x);
-    if (m != local.m) {                       // a new maximum (or a NaN, which stays)
-      local.s *= stat_exp2((local.m - m) * kLog2e);
-      local.m = m;
+    float t = (x - local.m) * kLog2e;
+    if (!(t <= kSlack)) {                      // far above the reference, the first element (m = -inf), or a NaN
+      if (x == -std::numeric_limits<float>::infinity()) {
+        t = x;                                 // -inf before any finite value: contributes nothing, the reference stays
+      } else {
+        local.s *= stat_exp2(-t);              // exp2(-inf) = 0 for the first element; NaN for a NaN or a second +inf
+        local.m = x;
+        t = 0.f;
+      }
     }
-    const float t = x == m ? 0.f : (x - m) * kLog2e;   // equal infinities contribute exp(0), not NaN
     local.s += stat_exp2(t);
   }
   template <int VEC> __device__ static void step_vector(Acc& local, const Vec<T, VEC>& x, long long) {
@@ -769,7 +777,7 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
     if (vec > 8) vec = 8;
     if (vec < 1) vec = 1;
     while (vec > 1 && inner % vec != 0) vec /= 2;
-    if ((op == TQ_ARGMAX || op == kOpMoments) && vec > 4) vec = 4;  // their per-column state is large
+    if ((op == TQ_ARGMAX || op == kOpMoments) && vec > 4) vec = 4;  // their per-column state is large; 16-byte loads measured no better (argmax) or worse (moments)
     if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_VEC")) {    // tuning override: 1, 2, 4 or 8
       const int value = std::atoi(forced);
       if ((value == 1 || value == 2 || value == 4 || value == 8) && value * size <= 16 && inner % value == 0) vec = value;

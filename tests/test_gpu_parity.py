@@ -648,6 +648,11 @@ def test_transposed_normalisations_special_columns_and_fallback(tq):
     x[:, 5] = float("-inf")
     x[100, 9] = float("inf")
     x[:, 11] = 1e30
+    x[:, 13] = torch.linspace(-500.0, 500.0, 512)      # the reference point of the running sum has to move, many times
+    x[:, 14] = torch.linspace(500.0, -500.0, 512)      # ... or never
+    x[:10, 15] = float("-inf")                         # -inf before the first finite value
+    x[::2, 17] = float("-inf")                         # ... and in between
+    x[:, 19] = torch.where(torch.arange(512) % 97 == 0, 80.0, -3.0)   # rare large values
     got = tq.softmax(dev(x).t(), -1).cpu()
     torch.testing.assert_close(got, tessiq0.softmax(x.t(), -1), rtol=1e-5, atol=1e-7, equal_nan=True)
     odd = torch.randn(130, 37, generator=torch.Generator().manual_seed(6))   # not a multiple of the vector width: packs first
