@@ -285,16 +285,20 @@ class _NoMatch(Exception):
     """Why a rewrite does not apply; kept in `Recipe.notes`."""
 
 
+class _NotThePattern(Exception):
+    """The node is not the end of the pattern at all (a bmm of something else): nothing to report."""
+
+
 def _match_attention(last: fx.Node, constant: set[fx.Node], folded: dict) -> Attention:
     """`last` is the second bmm of softmax(scale * q @ k.T [mask]) @ v. Returns the match when the
     whole pattern hangs on this node alone (no intermediate value has another reader); raises
     `_NoMatch` with the reason otherwise."""
     if last.target is not aten.bmm.default or _shape(last) == ():
-        raise _NoMatch("not a bmm")
+        raise _NotThePattern()
     path: list[fx.Node] = []
     softmax = _peel(last.args[0], path)
     if softmax.op != "call_function" or softmax.target is not aten._softmax.default:
-        raise _NoMatch("the first operand is not a softmax")
+        raise _NotThePattern()
     width = len(_shape(softmax))
     if softmax.args[1] not in (-1, width - 1) or softmax.args[2]:
         raise _NoMatch("the softmax is not over the key axis")
@@ -526,6 +530,8 @@ def build_recipe(gm: fx.GraphModule, math_mode: str = "fast") -> Recipe:
                 # the compiler runs inside AOTAutograd's fake-tensor mode; reading the mask needs real values
                 with _disable_current_modes():
                     match = _match_attention(node, constant, folded)
+            except _NotThePattern:
+                match = None
             except _NoMatch as reason:
                 notes.append(f"{node.name}: no fused attention: {reason}")
                 match = None

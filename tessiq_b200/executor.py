@@ -55,6 +55,18 @@ class Recipe:
             out[step.kind] = out.get(step.kind, 0) + 1
         return out
 
+    def explain(self) -> str:
+        """The schedule as text, one line per step: what kind of step computes which value from
+        which, then the rewrites that did not apply and why (the reference prints the same two
+        things in the `kernels` and `schedule` sections of python/tessiq/explain.py:258-300)."""
+        lines = [f"{len(self.steps)} steps: " + ", ".join(f"{count} {kind}" for kind, count in sorted(self.counts().items()))]
+        for step in self.steps:
+            members = getattr(step.kernel, "members", None)
+            detail = f"  [{len(members)} nodes fused]" if members and len(members) > 1 else ""
+            lines.append(f"  {step.kind:<12} {step.output:<28} <- {', '.join(step.reads) or '-'}{detail}" + (f"  ({step.note})" if step.note else ""))
+        lines += [f"  note: {note}" for note in self.notes]
+        return "\n".join(lines)
+
     @property
     def interpreted(self) -> list[str]:
         """The nodes that have no kernel here and run as PyTorch operators."""

@@ -163,6 +163,9 @@ def test_decoder_block_becomes_attention_and_epilogue_kernels():
     with FakeTensorMode():   # AOTAutograd calls the compiler inside its fake-tensor mode: the mask must still be read
         assert build_recipe(gm).counts()["attention"] == 1
 
+    text = recipe.explain()
+    assert "attention    view_10" in text and recipe.notes == []
+
     narrow = DecoderBlock(128, 4).eval().bfloat16()   # heads of 32: no attention kernel, the pattern stays as it was
     with torch.no_grad():
         gm = trace(lambda p, x: functional_call(narrow, p, (x,)), dict(narrow.named_parameters()), torch.randn(2, 64, 128).bfloat16())
@@ -170,6 +173,7 @@ def test_decoder_block_becomes_attention_and_epilogue_kernels():
     assert "attention" not in recipe.counts() and recipe.counts()["gemm"] == 6 and recipe.interpreted == []
     assert recipe.counts()["fused"] == 1   # only the masked scaling of the scores is left as an elementwise kernel
     assert recipe.counts()["constant"] >= 1   # the mask is computed once, not on every call
+    assert any("heads of 32" in note for note in recipe.notes) and "heads of 32" in recipe.explain()
 
 
 def test_only_a_lower_triangular_or_empty_mask_is_taken_for_attention():
@@ -247,6 +251,23 @@ def test_decoder_block_matches_eager_cpu(graphed, d, heads, t):
         torch.testing.assert_close(got.cpu().float(), ref, rtol=2e-2, atol=2e-2 * ref.abs().max().item())
     counts = holder["fn"].recipes[0].counts()
     assert ("attention" in counts) == (d // heads == 64) and holder["fn"].recipes[0].interpreted == []
+
+
+@pytest.mark.gpu
+def test_kernel_costs_lists_every_kernel_slowest_first():
+    from tessiq_b200.backend import build_recipe
+    from tessiq_b200.costs import kernel_costs
+
+    def model(x, w, b):
+        return torch.softmax(F.layer_norm(x, (512,), w, b, 1e-5) * 2.0, -1).sum(-1)
+
+    x, w, b = torch.randn(4096, 512), torch.randn(512), torch.randn(512)
+    recipe = build_recipe(trace(model, x, w, b))
+    costs = kernel_costs(recipe, x.cuda(), w.cuda(), b.cuda(), repeats=10)
+    assert [c.kind for c in costs].count("custom") == 2 and len(costs) == recipe.counts()["custom"] + recipe.counts()["fused"] + recipe.counts()["reduction"]
+    assert all(c.microseconds > 0 for c in costs) and costs == sorted(costs, key=lambda c: -c.microseconds)
+    with pytest.raises(ValueError):
+        kernel_costs(recipe, x, w, b)          # host tensors: there is nothing to time
 
 
 @pytest.mark.gpu
