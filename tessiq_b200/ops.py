@@ -58,10 +58,72 @@ def clone(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def elementwise(op: str, *operands, math_mode: str = "fast") -> torch.Tensor:
-    """One elementwise operation with torch's broadcasting. Tensor operands must share an
-    element type (mixed types are promoted by torch on its host path in the reference, which
-    here is a decline); Python numbers become kernel scalars."""
+def _dense(t: torch.Tensor) -> bool:
+    """Non-overlapping and dense: some permutation of the axes is packed."""
+    order = sorted(range(t.dim()), key=lambda d: (-t.stride(d), d))
+    return t.permute(order).is_contiguous() if t.dim() else True
+
+
+def _result_like(op: str, tensors: list[torch.Tensor], out_shape: list[int], out_dtype: torch.dtype) -> torch.Tensor:
+    """An empty result with the layout torch gives (csrc/tessiq/torch/eager.cpp:260-306, pinned by
+    tests/python/test_eager.py:218-236): operands of one dense layout give that layout; packed
+    operands give a packed result; anything else gets the strides torch's own meta kernel picks."""
+    device = tensors[0].device
+    first = tensors[0]
+    if _dense(first) and all(t.shape == first.shape and t.stride() == first.stride() for t in tensors):
+        return torch.empty_strided(first.shape, first.stride(), dtype=out_dtype, device=device)
+    if all(t.is_contiguous() for t in tensors):
+        return torch.empty(out_shape, dtype=out_dtype, device=device)
+    metas = [torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device="meta") for t in tensors]
+    try:
+        # any binary ufunc has torch's TensorIterator layout rule; `add` stands for all of them
+        like = metas[0]
+        for m in metas[1:]:
+            like = torch.add(like, m)
+        if len(metas) == 1:
+            like = torch.neg(like)
+    except Exception as reason:  # noqa: BLE001
+        raise Declined(f"torch cannot say what layout {op} gives these operands: {reason}")
+    if tuple(like.shape) != tuple(out_shape) or not _dense(like):
+        raise Declined(f"{op} would give a result layout the kernel cannot write")
+    return torch.empty_strided(like.shape, like.stride(), dtype=out_dtype, device=device)
+
+
+def _overlaps(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """Conservative: the two views share storage and their address ranges meet."""
+    if a.numel() == 0 or b.numel() == 0 or a.untyped_storage().data_ptr() != b.untyped_storage().data_ptr():
+        return False
+
+    def span(t):
+        low = t.storage_offset() * t.element_size()
+        reach = 0                                   # (this module's `sum` is the reduction, not the builtin)
+        for n, st in zip(t.shape, t.stride()):
+            reach += (n - 1) * st
+        return low, low + (reach + 1) * t.element_size()
+
+    (a0, a1), (b0, b1) = span(a), span(b)
+    return a0 < b1 and b0 < a1
+
+
+def _written_into(target: torch.Tensor, tensors: list[torch.Tensor], out_shape: list[int], out_dtype: torch.dtype) -> torch.Tensor:
+    """`target` as the result of an out= or in-place call (csrc/tessiq/torch/eager.cpp:314-330): on
+    the operands' device, of the result's type and broadcast shape, dense, and overlapping no
+    operand other than itself read where it is written — `x.add_(x.t())` would read elements
+    another thread has already written."""
+    if target.device != tensors[0].device or target.dtype != out_dtype or list(target.shape) != list(out_shape) or not _dense(target):
+        raise Declined("the target of an in-place or out= call must be a dense tensor of the result's shape, type and device")
+    for t in tensors:
+        itself = t.data_ptr() == target.data_ptr() and t.shape == target.shape and t.stride() == target.stride()
+        if not itself and _overlaps(target, t):
+            raise Declined("the target overlaps an operand it is not identical to")
+    return target
+
+
+def elementwise(op: str, *operands, math_mode: str = "fast", out: torch.Tensor | None = None) -> torch.Tensor:
+    """One elementwise operation with torch's broadcasting and torch's result layout. Tensor
+    operands must share an element type (mixed types are promoted by torch on its host path in the
+    reference, which here is a decline); Python numbers become kernel scalars. `out` writes into an
+    existing tensor (an operand itself for the in-place form) under the reference's conditions."""
     tensors = [o for o in operands if isinstance(o, torch.Tensor)]
     if not tensors:
         raise ValueError(f"{op} needs at least one tensor operand")
@@ -74,14 +136,23 @@ def elementwise(op: str, *operands, math_mode: str = "fast") -> torch.Tensor:
         raise Declined(f"{op} over mixed element types {sorted(map(str, value_dtypes))} has no kernel")
     dtype = value_dtypes.pop()
     out_dtype = torch.bool if op in COMPARES else dtype
+    result = _written_into(out, tensors, out_shape, out_dtype) if out is not None else _result_like(op, tensors, out_shape, out_dtype)
+    if result.numel() == 0:
+        return result
+    # Walking the result in the order of its memory is walking a packed tensor: every operand is
+    # seen through the same permutation (csrc/tessiq/torch/eager.cpp, `memory_order`).
+    order = sorted(range(len(out_shape)), key=lambda d: (-result.stride(d), d))
+    packed = result.permute(order)
     lines = [f"math {math_mode}"]
     names, inputs, scalars = [], [], []
     for i, operand in enumerate(operands):
         if isinstance(operand, torch.Tensor):
-            read, _ = classify_read(operand.shape, operand.stride(), out_shape)
+            aligned = operand.reshape([1] * (len(out_shape) - operand.dim()) + list(operand.shape)) if operand.dim() < len(out_shape) else operand
+            seen = aligned.permute(order)
+            read, _ = classify_read(seen.shape, seen.stride(), packed.shape)
             name = f"t{i}"
             lines.append(f"in {name} {DTYPE_NAMES[operand.dtype]} {read}")
-            inputs.append(operand)
+            inputs.append(seen)
         else:
             name = f"s{i}"
             scalar_dtype = dtype if not isinstance(operand, bool) else torch.bool
@@ -90,8 +161,13 @@ def elementwise(op: str, *operands, math_mode: str = "fast") -> torch.Tensor:
         names.append(name)
     lines.append(f"r = {op} {' '.join(names)}")
     lines.append(f"out r {DTYPE_NAMES[out_dtype]}")
-    out = torch.empty(out_shape, dtype=out_dtype, device=tensors[0].device)
-    return fused("\n".join(lines), inputs, out, scalars)
+    fused("\n".join(lines), inputs, packed, scalars)
+    return result
+
+
+def elementwise_(op: str, target: torch.Tensor, *others, math_mode: str = "fast") -> torch.Tensor:
+    """The in-place form: `target = op(target, *others)`, e.g. `x.add_(y)`."""
+    return elementwise(op, target, *others, math_mode=math_mode, out=target)
 
 
 def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:

@@ -662,6 +662,66 @@ def test_transposed_normalisations_special_columns_and_fallback(tq):
     close32(tq.layer_norm(dev(shifted).t(), [256]), tessiq0.native_layer_norm(shifted.t(), [256], None, None, 1e-5)[0], rtol=1e-3, scale=1e-3)
 
 
+def _layouts():
+    g = torch.Generator().manual_seed(0)
+    return {
+        "transposed": torch.randn(48, 64, generator=g).t(),
+        "channels-last": torch.randn(2, 3, 4, 5, generator=g).to(memory_format=torch.channels_last),
+        "strided": torch.randn(8, 64, generator=g)[:, ::2],
+        "expanded": torch.randn(1, 64, generator=g).expand(8, 64),
+    }
+
+
+def _on_device_like(x):
+    """The same view over device memory: same sizes, strides and storage offset."""
+    base = torch.empty(x.untyped_storage().nbytes() // x.element_size(), dtype=x.dtype)
+    base.set_(x.untyped_storage(), 0, (base.numel(),), (1,))
+    return torch.as_strided(base.cuda(), x.shape, x.stride(), x.storage_offset())
+
+
+@pytest.mark.parametrize("name", ["transposed", "channels-last", "strided", "expanded"])
+def test_elementwise_results_have_the_layout_torch_gives(tq, name):
+    # tests/python/test_eager.py:218-236 of the reference: values AND strides as on the host
+    x = _layouts()[name]
+    xd = _on_device_like(x)
+    assert xd.stride() == x.stride()
+    cases = [(torch.exp(x), tq.elementwise("exp", xd, math_mode="precise")),
+             (x * x.contiguous(), tq.elementwise("mul", xd, xd.contiguous())),
+             (x - x[:1], tq.elementwise("sub", xd, xd[:1])),
+             (torch.where(x > 0, x, x * 2), tq.elementwise("where", tq.elementwise("gt", xd, 0.0), xd, tq.elementwise("mul", xd, 2.0)))]
+    for expected, got in cases:
+        assert got.shape == expected.shape and got.stride() == expected.stride(), (name, got.stride(), expected.stride())
+        torch.testing.assert_close(got.cpu(), expected, rtol=2e-6, atol=1e-6)
+
+
+def test_elementwise_out_and_in_place_forms(tq):
+    from tessiq_b200._lib import Declined
+
+    g = torch.Generator().manual_seed(1)
+    a, b = torch.randn(33, 40, generator=g), torch.randn(40, generator=g)
+    ad, bd = dev(a), dev(b)
+    out = torch.full((33, 40), 7.0, device="cuda")
+    assert tq.elementwise("add", ad, bd, out=out) is out
+    torch.testing.assert_close(out.cpu(), a + b)
+    t = dev(a).t()                                   # a dense, transposed target keeps its memory
+    before = t.data_ptr()
+    tq.elementwise_("mul", t, 2.0)
+    assert t.data_ptr() == before and t.stride() == (1, 40)
+    torch.testing.assert_close(t.cpu(), a.t() * 2)
+    x = dev(a).clone()
+    tq.elementwise_("add", x, x)                     # the target itself as an operand is fine
+    torch.testing.assert_close(x.cpu(), a + a)
+    square = dev(torch.randn(16, 16, generator=g))
+    with pytest.raises(Declined):
+        tq.elementwise_("add", square, square.t())   # reads elements another thread may already have written
+    with pytest.raises(Declined):
+        tq.elementwise("add", ad, bd, out=torch.empty(33, 40, dtype=torch.float64, device="cuda"))
+    with pytest.raises(Declined):
+        tq.elementwise("add", ad, bd, out=torch.empty(33, 80, device="cuda")[:, ::2])   # not dense
+    with pytest.raises(Declined):
+        tq.elementwise("add", ad, bd, out=torch.empty(40, device="cuda"))                # not the broadcast shape
+
+
 # ---------------------------------------------------------------------------------------------
 # pack
 
