@@ -444,14 +444,37 @@ def register_custom_ops() -> None:
     if _library is not None:
         return
     library = torch.library.Library("tessiq", "DEF")
+    functional = torch.nn.functional
+
+    def or_reference(kernel, reference):
+        """A decline (TQ_UNSUPPORTED: an f32 GEMM, a pointer TMA cannot take, a ragged width) runs the
+        operation's ATen definition on the same GPU, as the reference's `call.decline` runs its
+        `.reference()` (csrc/tessiq/torch/custom_op.h:117-246); nothing here runs on the host."""
+        def run(*args):
+            try:
+                return kernel(*args)
+            except Declined:
+                return reference(*args)
+        return run
+
     schemas = {
-        "softmax(Tensor self, int dim, bool half_to_float) -> Tensor": lambda self, dim, half_to_float: softmax(self, dim, half_to_float),
-        "layer_norm(Tensor x, Tensor weight, Tensor bias, float eps) -> Tensor": lambda x, weight, bias, eps: layer_norm(x, weight.shape, weight, bias, eps),
-        "rms_norm(Tensor x, Tensor weight, float eps) -> Tensor": rms_norm,
-        "gemm_bias_gelu_tanh(Tensor x, Tensor weight, Tensor bias) -> Tensor": gemm_bias_gelu_tanh,
-        "gemm_bias_gelu(Tensor x, Tensor weight, Tensor bias) -> Tensor": gemm_bias_gelu,
-        "fast_gelu(Tensor x) -> Tensor": lambda x: elementwise("fast_gelu", x),
-        "swiglu(Tensor gate, Tensor up) -> Tensor": lambda gate, up: elementwise("swiglu", gate, up),
+        "softmax(Tensor self, int dim, bool half_to_float) -> Tensor": or_reference(
+            lambda self, dim, half_to_float: softmax(self, dim, half_to_float),
+            lambda self, dim, half_to_float: torch.softmax(self, dim, dtype=torch.float32 if half_to_float else None)),
+        "layer_norm(Tensor x, Tensor weight, Tensor bias, float eps) -> Tensor": or_reference(
+            lambda x, weight, bias, eps: layer_norm(x, weight.shape, weight, bias, eps),
+            lambda x, weight, bias, eps: functional.layer_norm(x, weight.shape, weight, bias, eps)),
+        "rms_norm(Tensor x, Tensor weight, float eps) -> Tensor": or_reference(
+            rms_norm, lambda x, weight, eps: x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight),
+        "gemm_bias_gelu_tanh(Tensor x, Tensor weight, Tensor bias) -> Tensor": or_reference(
+            gemm_bias_gelu_tanh, lambda x, weight, bias: functional.gelu(torch.addmm(bias, x, weight.t()), approximate="tanh")),
+        "gemm_bias_gelu(Tensor x, Tensor weight, Tensor bias) -> Tensor": or_reference(
+            gemm_bias_gelu, lambda x, weight, bias: functional.gelu(torch.addmm(bias, x, weight.t()))),
+        "fast_gelu(Tensor x) -> Tensor": or_reference(lambda x: elementwise("fast_gelu", x), lambda x: x * torch.sigmoid(1.702 * x)),
+        "swiglu(Tensor gate, Tensor up) -> Tensor": or_reference(lambda gate, up: elementwise("swiglu", gate, up),
+                                                                 lambda gate, up: functional.silu(gate) * up),
+        "attention(Tensor q, Tensor k, Tensor v, float scale, bool causal) -> Tensor": or_reference(
+            attention, lambda q, k, v, scale, causal: functional.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)),
     }
     for schema, implementation in schemas.items():
         library.define(schema)
