@@ -176,7 +176,7 @@ class Step:
         # softmax / LayerNorm over the view's rows of 32768 (two launches each): read in place —
         # per-column statistics, then one transposing pass that normalises — or, where that is the
         # faster of the two (kernel.prefers_transposed), packed first and then a cluster of CTAs per row
-        if K.prefers_transposed("softmax", x.dtype):
+        if K.prefers_transposed("softmax", x.dtype, 1, ROWS, WIDTH):
             ops.append(("softmax_cols", lambda: K.launch_transposed("softmax", x, None, None, s["softmax_cols"], 1, ROWS, WIDTH, 0.0, self.device, stream)))
         else:
             ops.append(("softmax_cols", lambda: (self.pack.launch([x.t()], s["pack"], stream),

@@ -301,9 +301,16 @@ tq_status tq_layer_norm_launch(tq_dtype dtype,
  * statistics read in place, then one transposing pass that normalises. LayerNorm's weight and bias
  * (either may be null) have `rows` elements. dtype f32/f16/bf16; rows and cols must be multiples
  * of 16 / sizeof(element) and the tensors 16-byte aligned, else TQ_UNSUPPORTED (pack, then use the
- * row entry points). `workspace` must hold tq_transposed_workspace_bytes bytes. */
+ * row entry points). `workspace` must hold tq_transposed_workspace_bytes bytes.
+ * Long columns of a small tensor (8192 to 51200 rows, at most 32 MiB, rows a multiple of 8 vectors and
+ * cols of 2) take TWO passes instead: a cluster of 8 CTAs keeps a slab of columns by all the rows in
+ * its shared memory and reads HBM once. tq_transposed_passes reports which form a shape takes (2 or
+ * 3), so that a caller can choose between this entry and pack + row kernels before it launches (the
+ * reference decides only after the fact, when a kernel declines: csrc/tessiq/torch/custom.cpp:563-598). */
 tq_status tq_transposed_workspace_bytes(int32_t layer_norm, tq_dtype dtype, int64_t batch, int64_t rows,
                                         int64_t cols, int32_t device, size_t* bytes);
+tq_status tq_transposed_passes(int32_t layer_norm, tq_dtype dtype, int64_t batch, int64_t rows, int64_t cols,
+                               int32_t device, int32_t* passes);
 tq_status tq_softmax_transposed_launch(tq_dtype dtype, const void* in, void* out, int64_t batch, int64_t rows,
                                        int64_t cols, void* workspace, size_t workspace_bytes, int32_t device,
                                        void* stream);

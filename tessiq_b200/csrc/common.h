@@ -106,6 +106,14 @@ tq_status slice_stats_launch(int kind, tq_dtype dtype, const void* in, void* sta
 tq_status transpose_normalize_launch(int kind, tq_dtype dtype, const void* in, void* out, const void* stats, const void* weight,
                                      const void* bias, long long batch, long long rows, long long cols, float eps, cudaStream_t stream);
 
+// slabnorm.cu: the same result from ONE pass over HBM — a cluster of 8 CTAs keeps a slab of columns
+// by all the rows in its shared memory. Sets `*handled` and launches when slab_takes() the shape (rows
+// a multiple of 8 vectors, 8192 to 51200, cols a multiple of two vectors, at most 32 MiB in all) and
+// the pointers are 16-byte aligned; otherwise launches nothing.
+bool slab_takes(tq_dtype dtype, long long batch, long long rows, long long cols);
+tq_status slab_normalize_launch(int kind, tq_dtype dtype, const void* in, void* out, const void* weight, const void* bias,
+                                long long batch, long long rows, long long cols, float eps, cudaStream_t stream, bool* handled);
+
 }  // namespace tq
 
 // ---------------------------------------------------------------------------------------------

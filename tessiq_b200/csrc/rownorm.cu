@@ -601,6 +601,9 @@ tq_status transposed_launch(int kind, tq_dtype dtype, const void* in, const void
              "this call needs %zu bytes of 16-byte-aligned scratch and was given %zu", stats + reduce_scratch, workspace_bytes);
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
   unsigned char* scratch = static_cast<unsigned char*>(workspace);
+  bool handled = false;
+  if (tq_status s = tq::slab_normalize_launch(kind, dtype, in, out, weight, bias, batch, rows, cols, static_cast<float>(eps), cuda_stream, &handled)) return s;
+  if (handled) return TQ_OK;
   if (tq_status s = tq::slice_stats_launch(kind, dtype, in, scratch, batch, rows, cols, scratch + stats, reduce_scratch, device, cuda_stream)) return s;
   return tq::transpose_normalize_launch(kind, dtype, in, out, scratch, weight, bias, batch, rows, cols, static_cast<float>(eps), cuda_stream);
 }
@@ -615,6 +618,17 @@ tq_status tq_transposed_workspace_bytes(int32_t layer_norm, tq_dtype dtype, int6
   *bytes = 0;
   if (batch == 0 || cols == 0 || rows == 0) return TQ_OK;
   *bytes = stats_bytes(batch, cols) + tq::slice_stats_workspace_bytes(layer_norm ? 1 : 0, dtype, batch, rows, cols, device);
+  return TQ_OK;
+}
+
+tq_status tq_transposed_passes(int32_t layer_norm, tq_dtype dtype, int64_t batch, int64_t rows, int64_t cols, int32_t device,
+                               int32_t* passes) {
+  (void)layer_norm;
+  (void)device;
+  TQ_REQUIRE(passes != nullptr, TQ_INVALID_ARGUMENT, "passes out-pointer is null");
+  TQ_REQUIRE(batch >= 0 && rows >= 0 && cols >= 0, TQ_INVALID_ARGUMENT, "negative extent");
+  TQ_REQUIRE(tq::dtype_size(dtype) != 0, TQ_INVALID_ARGUMENT, "unknown element type %d", dtype);
+  *passes = tq::slab_takes(dtype, batch, rows, cols) ? 2 : 3;
   return TQ_OK;
 }
 

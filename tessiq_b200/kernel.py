@@ -333,13 +333,23 @@ def launch_reduce(op: str, x: torch.Tensor, out: torch.Tensor, outer: int, reduc
                                0 if scratch is None else scratch.numel(), device, ctypes.c_void_p(stream)))
 
 
-def prefers_transposed(kind: str, dtype: torch.dtype) -> bool:
-    """Whether op(x.transpose(-1, -2), -1) should take the in-place path (statistics + transposing
-    normalise, 3 passes over the data) rather than pack-then-rows (4 passes). Measured on B200 at
-    [32768, 4096]: the in-place path wins for 4-byte softmax (310 vs 357 us) and for LayerNorm
+def transposed_passes(kind: str, dtype: torch.dtype, batch: int, rows: int, cols: int, device: int = 0) -> int:
+    """Passes over HBM tq_*_transposed_launch makes for this shape: 2 (a cluster keeps a slab of
+    columns in shared memory) or 3 (statistics, then a transposing normalise)."""
+    passes = ctypes.c_int32()
+    check(lib.tq_transposed_passes(1 if kind == "layer_norm" else 0, dtype_code(dtype), batch, rows, cols, device, ctypes.byref(passes)))
+    return passes.value
+
+
+def prefers_transposed(kind: str, dtype: torch.dtype, batch: int = 0, rows: int = 0, cols: int = 0) -> bool:
+    """Whether op(x.transpose(-1, -2), -1) should take the in-place path rather than pack-then-rows
+    (4 passes). Always when the shape takes the two-pass slab kernel. For the three-pass form,
+    measured on B200 at [32768, 4096]: it wins for 4-byte softmax (310 vs 357 us) and for LayerNorm
     (f32 331 vs 394, bf16 214 vs 238); for 2-byte softmax its statistics pass is issue-bound and
     pack-then-rows stays ahead (198 vs 228 us)."""
-    return kind == "layer_norm" or dtype.itemsize >= 4
+    if kind == "layer_norm" or dtype.itemsize >= 4:
+        return True
+    return rows > 0 and transposed_passes(kind, dtype, batch, rows, cols) == 2
 
 
 def launch_transposed(kind: str, base: torch.Tensor, weight, bias, out: torch.Tensor, batch: int, rows: int, cols: int,

@@ -273,9 +273,11 @@ def _transposed_base(x: torch.Tensor):
 
 def softmax(x: torch.Tensor, dim: int = -1, half_to_float: bool = False) -> torch.Tensor:
     out_dtype = torch.float32 if half_to_float else x.dtype
-    transposed = _transposed_base(x) if (x.dim() and dim % x.dim() == x.dim() - 1 and not half_to_float and prefers_transposed("softmax", x.dtype)) else None
+    transposed = _transposed_base(x) if (x.dim() and dim % x.dim() == x.dim() - 1 and not half_to_float) else None
+    if transposed is not None and not prefers_transposed("softmax", x.dtype, *transposed[1:]):
+        transposed = None
     if transposed is not None:
-        # over the last axis of a transposed view: statistics in place, then one transposing pass
+        # over the last axis of a transposed view: a column slab kept on chip, or statistics in place and then one transposing pass
         base, batch, rows, cols = transposed
         out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         device = _device_of([x])

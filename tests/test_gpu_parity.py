@@ -662,6 +662,68 @@ def test_transposed_normalisations_special_columns_and_fallback(tq):
     close32(tq.layer_norm(dev(shifted).t(), [256]), tessiq0.native_layer_norm(shifted.t(), [256], None, None, 1e-5)[0], rtol=1e-3, scale=1e-3)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(8192, 48), (8192, 528), (3, 8192, 16), (2, 2, 16384, 32), (51200, 16), (32768, 64), (20000, 8), (51264, 16)])
+def test_transposed_normalisations_from_a_column_slab(tq, dtype, shape):
+    """Long columns of a small tensor (8192 to 51200 rows, a multiple of 8 vectors; at most 32 MiB) are
+    kept in a cluster's shared memory and read from HBM once; the last two shapes stand just outside
+    that rule for one element size or for both."""
+    from tessiq_b200 import kernel as K
+
+    vec = 16 // dtype.itemsize
+    fits = shape[-2] % (8 * vec) == 0 and shape[-2] <= 51200 and shape[-1] % (2 * vec) == 0
+    assert K.transposed_passes("softmax", dtype, math.prod(shape[:-2]), shape[-2], shape[-1]) == (2 if fits else 3)
+    assert K.transposed_passes("layer_norm", dtype, 1, 32768, 4096) == 3        # 512 MiB: the pieces no longer meet in L2
+    assert K.transposed_passes("layer_norm", dtype, 64, 1024, 1024) == 3        # short columns
+
+    g = torch.Generator().manual_seed(sum(shape) + 1)
+    x = (torch.randn(*shape, generator=g) * 2 - 0.7).to(dtype)
+    rows, cols = shape[-2], shape[-1]
+    batch = x.numel() // (rows * cols)
+    w = (1 + torch.randn(rows, generator=g) * 0.1).to(dtype)
+    b = (torch.randn(rows, generator=g) * 0.1).to(dtype)
+    xd, wd, bd = dev(x), dev(w), dev(b)
+    view = x.transpose(-1, -2)
+    stream = torch.cuda.current_stream().cuda_stream
+    got_softmax = torch.empty(view.shape, dtype=dtype, device="cuda")
+    got_norm = torch.empty(view.shape, dtype=dtype, device="cuda")
+    K.launch_transposed("softmax", xd, None, None, got_softmax, batch, rows, cols, 0.0, 0, stream)
+    K.launch_transposed("layer_norm", xd, wd, bd, got_norm, batch, rows, cols, 1e-5, 0, stream)
+    ref_softmax = tessiq0.softmax(view, -1)
+    ref_norm = tessiq0.native_layer_norm(view, [rows], w, b, 1e-5)[0]
+    if dtype == torch.float32:
+        close32(got_softmax, ref_softmax, scale=1e-6)
+        close32(got_norm, ref_norm, rtol=2e-5, scale=4e-6)
+        close32(tq.layer_norm(xd.transpose(-1, -2), [rows]), tessiq0.native_layer_norm(view, [rows], None, None, 1e-5)[0], rtol=2e-5, scale=4e-6)
+    else:
+        close16(got_softmax, ref_softmax)
+        close16(got_norm, ref_norm)
+
+
+def test_column_slab_special_columns(tq):
+    rows = 8192
+    x = torch.randn(rows, 64, generator=torch.Generator().manual_seed(8))
+    x[7, 3] = float("nan")
+    x[:, 5] = float("-inf")
+    x[7900, 9] = float("inf")
+    x[:, 11] = 1e30
+    x[:, 13] = torch.linspace(-500.0, 500.0, rows)
+    x[:, 14] = torch.linspace(500.0, -500.0, rows)
+    x[:1100, 15] = float("-inf")                       # a whole CTA's share of the column is -inf
+    x[::2, 17] = float("-inf")
+    x[:, 19] = torch.where(torch.arange(rows) % 97 == 0, 80.0, -3.0)
+    x[:, 21] = -1e30
+    got = tq.softmax(dev(x).t(), -1).cpu()
+    torch.testing.assert_close(got, tessiq0.softmax(x.t(), -1), rtol=1e-5, atol=1e-7, equal_nan=True)
+    shifted = torch.randn(rows, 64, generator=torch.Generator().manual_seed(9)) + 1000.0
+    close32(tq.layer_norm(dev(shifted).t(), [rows]), tessiq0.native_layer_norm(shifted.t(), [rows], None, None, 1e-5)[0], rtol=1e-3, scale=1e-3)
+    nan_norm = torch.randn(rows, 16, generator=torch.Generator().manual_seed(10))
+    nan_norm[5, 2] = float("nan")
+    nan_norm[6, 9] = float("inf")
+    got = tq.layer_norm(dev(nan_norm).t(), [rows]).cpu()
+    torch.testing.assert_close(got, tessiq0.native_layer_norm(nan_norm.t(), [rows], None, None, 1e-5)[0], rtol=2e-5, atol=4e-6, equal_nan=True)
+
+
 def _layouts():
     g = torch.Generator().manual_seed(0)
     return {
