@@ -4,14 +4,14 @@
 //
 // bf16 or f16 operands with 64-element heads, f32 scores and sums, one rounding of the result. The
 // score matrix never leaves the SM: one CTA owns 256 query rows of one head (two tiles of 128) and
-// walks the keys 128 at a time with a running row maximum and row sum (the online form of softmax).
+// walks the keys 128 at a time with a row reference point and row sum (the online form of softmax).
 //
 //   warps 0..3 / 4..7   one softmax group per query tile, one thread per query row: tcgen05.ld of
 //                       the row's 128 f32 scores (held in registers for both the maximum and the
 //                       exponentials), ex2, row sum; the probabilities go back into tensor memory
 //                       with tcgen05.st as packed bf16/f16 pairs — the A operand of the second
-//                       product — and the partial result of the previous step is read from tensor
-//                       memory and folded into the row's 64 accumulators with one FMA each.
+//                       product. The result accumulates in tensor memory across the steps and is
+//                       read once, at the end.
 //   warp 8, one lane    producer: TMA loads (128-byte swizzle) of the two query tiles once, then one
 //                       128 x 64 key tile and one value tile per step into two 4-stage rings; the
 //                       first loads leave before the CTA's set-up barrier.
@@ -21,10 +21,16 @@
 //                       thread about a hundred cycles and a step needs twelve, so one thread for
 //                       both groups was the bottleneck; with one each, no group waits for the other.
 //
-// Each group has two 128-column buffers of tensor memory: the scores of step j sit in buffer j % 2;
-// once the group holds them in registers it writes the probabilities over columns 64..127, and the
-// second product writes the step's partial result over columns 0..63. So the scores of step j + 1
-// are computed while the group is still working on step j. The softmax groups run with 224
+// softmax is exp(s - m) / sum exp(s - m) for ANY m, so a row keeps the maximum of its first key tile
+// as its reference point and moves it only when a later tile rises more than 2^8 above it — then,
+// and only then, the row's sum and its 64 accumulators in tensor memory are rescaled (a warp-wide
+// slow path, rare on real data). Without that, nothing is read back per step: the second product
+// accumulates O += P V in place. Probabilities are at most 2^8, well inside bf16 and f16.
+//
+// Each group has 256 columns of tensor memory: the scores (0..127), the probabilities as packed
+// pairs (128..191) and the result (192..255). A group takes its scores into registers at the start
+// of a step and hands the columns back at once, so the scores of step j + 1 are computed while the
+// group is still working on step j. The softmax groups run with 224
 // registers per thread, the other four warps with 56 (setmaxnreg). Q, K, V and
 // the result are addressed through (batch, head, token) strides, so the three slices of a fused QKV
 // projection are read in place and the result is written directly in [batch, token, head, 64] order:
@@ -67,8 +73,10 @@ constexpr uint32_t kOffsetK = kOffsetQ + kGroups * kTileBytes;
 constexpr uint32_t kOffsetV = kOffsetK + kRing * kTileBytes;
 constexpr uint32_t kOffsetBarriers = kOffsetV + kRing * kTileBytes;
 constexpr size_t kAttnSmemBytes = 1024 + kOffsetBarriers + 256;
-constexpr uint32_t kAttnTmemColumns = 512;   // two groups x two buffers x 128 columns
-constexpr uint32_t kColumnP = 64;            // in a buffer whose scores are spent: O in columns 0..63, P (packed pairs) in 64..127
+constexpr uint32_t kAttnTmemColumns = 512;   // two groups x 256 columns
+constexpr uint32_t kGroupColumns = 256;      // of a group: scores 0..127, probabilities (packed pairs) 128..191, result 192..255
+constexpr uint32_t kColumnP = 128, kColumnO = 192;
+constexpr float kSlack = 8.f;                // a row's reference point moves when a tile's maximum is more than 2^kSlack above it
 
 enum AttnWait { kWaitQ = 201, kWaitKeyEmpty = 202, kWaitValueEmpty = 203, kWaitKeyFull = 204, kWaitValueFull = 205,
                 kWaitScores = 206, kWaitProbabilities = 207, kWaitPartial = 208, kWaitBufferFree = 209 };
@@ -98,6 +106,12 @@ __host__ __device__ constexpr uint32_t attn_instruction_descriptor(int n, bool b
          (static_cast<uint32_t>(kRows >> 4) << 24);
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <typename T>
 __device__ __forceinline__ uint32_t pack_pair(float low, float high) {
   if constexpr (std::is_same_v<T, __nv_bfloat16>) {
@@ -123,11 +137,11 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   auto k_empty = [&](int s) { return barriers + 8u * (1 + kRing + s); };
   auto v_full = [&](int s) { return barriers + 8u * (1 + 2 * kRing + s); };
   auto v_empty = [&](int s) { return barriers + 8u * (1 + 3 * kRing + s); };
-  auto s_full = [&](int g, int b) { return barriers + 8u * (1 + 4 * kRing + 2 * g + b); };
-  auto o_full = [&](int g, int b) { return barriers + 8u * (1 + 4 * kRing + 2 * kGroups + 2 * g + b); };
-  auto p_full = [&](int g) { return barriers + 8u * (1 + 4 * kRing + 4 * kGroups + g); };
-  auto buffer_free = [&](int g) { return barriers + 8u * (1 + 4 * kRing + 5 * kGroups + g); };
-  constexpr int kBarrierCount = 1 + 4 * kRing + 6 * kGroups;
+  auto s_full = [&](int g) { return barriers + 8u * (1 + 4 * kRing + g); };                   // the scores of a step are in tensor memory
+  auto s_free = [&](int g) { return barriers + 8u * (1 + 4 * kRing + kGroups + g); };          // ... and in the group's registers
+  auto p_full = [&](int g) { return barriers + 8u * (1 + 4 * kRing + 2 * kGroups + g); };      // the probabilities of a step are in tensor memory
+  auto pv_done = [&](int g) { return barriers + 8u * (1 + 4 * kRing + 3 * kGroups + g); };     // ... and the second product has consumed them
+  constexpr int kBarrierCount = 1 + 4 * kRing + 4 * kGroups;
   const uint32_t tmem_slot = barriers + 8u * kBarrierCount;
   volatile uint32_t* tmem_slot_pointer = reinterpret_cast<volatile uint32_t*>(aligned + kOffsetBarriers + 8 * kBarrierCount);
 
@@ -165,12 +179,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       barrier_init(v_empty(s), kGroups);
     }
     for (int g = 0; g < kGroups; ++g) {
-      for (int b = 0; b < 2; ++b) {
-        barrier_init(s_full(g, b), 1);
-        barrier_init(o_full(g, b), 1);
-      }
+      barrier_init(s_full(g), 1);
+      barrier_init(pv_done(g), 1);
       barrier_init(p_full(g), kRows / 32);          // one arrival per warp of the group
-      barrier_init(buffer_free(g), kRows / 32);
+      barrier_init(s_free(g), kRows / 32);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     if (total_steps > 0) {
@@ -220,21 +232,22 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       constexpr uint32_t kHighWord = kDescriptorHigh;
       const uint32_t low_q = descriptor_low(base + kOffsetQ + g * kTileBytes, 0), low_k = descriptor_low(base + kOffsetK, 0);
       const uint32_t low_v = descriptor_low(base + kOffsetV, kTileBytes);
-      const uint32_t buffers = tmem_base + static_cast<uint32_t>(2 * g * kKeys);     // buffer b at + 128 b
-      // S(i) = Q K_i^T into buffer i % 2: both operands K-major, 16 elements of K = 32 B in the swizzle row
+      const uint32_t columns = tmem_base + static_cast<uint32_t>(g) * kGroupColumns;
+      // S(i) = Q K_i^T: both operands K-major, 16 elements of K = 32 B in the swizzle row
       auto scores = [&](int i) {
-        const uint32_t k = low_k + (i % kRing) * (kTileBytes >> 4), d = buffers + (i & 1) * kKeys;
+        const uint32_t k = low_k + (i % kRing) * (kTileBytes >> 4);
 #pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk) mma_f16_split(d, low_q + kk * 2, kHighWord, k + kk * 2, kHighWord, idesc_s, kk != 0 ? 1u : 0u);
-        mma_commit(s_full(g, i & 1));
+        for (int kk = 0; kk < kHeadDim / 16; ++kk) mma_f16_split(columns, low_q + kk * 2, kHighWord, k + kk * 2, kHighWord, idesc_s, kk != 0 ? 1u : 0u);
+        mma_commit(s_full(g));
       };
-      // O(i) = P_i V_i over columns 0..63 of buffer i % 2: P from tensor memory (columns 64..127, 16
-      // keys = 8 columns), V MN-major from shared memory (16 keys = 2048 B)
+      // O += P_i V_i (O = for the first step): P from tensor memory (16 keys = 8 columns), V MN-major
+      // from shared memory (16 keys = 2048 B)
       auto partial = [&](int i) {
-        const uint32_t v = low_v + (i % kRing) * (kTileBytes >> 4), d = buffers + (i & 1) * kKeys;
+        const uint32_t v = low_v + (i % kRing) * (kTileBytes >> 4);
 #pragma unroll
-        for (int kk = 0; kk < kKeys / 16; ++kk) mma_f16_tmem_a(d, d + kColumnP + kk * 8, v + kk * (2048 >> 4), kHighWord, idesc_o, kk != 0 ? 1u : 0u);
-        mma_commit(o_full(g, i & 1));
+        for (int kk = 0; kk < kKeys / 16; ++kk)
+          mma_f16_tmem_a(columns + kColumnO, columns + kColumnP + kk * 8, v + kk * (2048 >> 4), kHighWord, idesc_o, (i != 0 || kk != 0) ? 1u : 0u);
+        mma_commit(pv_done(g));
       };
       bool alive = barrier_wait(q_full, 0, p.status, kWaitQ) && barrier_wait(k_full(0), 0, p.status, kWaitKeyFull);
       if (alive) {
@@ -242,14 +255,14 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         scores(0);
       }
       for (int i = 0; alive && i < steps[g]; ++i) {
-        // the scores of step i + 1, once the group has taken O(i-1) out of that buffer (its i-th arrival)
+        // the scores of step i + 1, once the group holds those of step i in registers
         if (i + 1 < steps[g]) {
           if (!barrier_wait(k_full((i + 1) % kRing), ((i + 1) / kRing) & 1, p.status, kWaitKeyFull)) break;
-          if (!barrier_wait(buffer_free(g), i & 1, p.status, kWaitBufferFree)) break;
+          if (!barrier_wait(s_free(g), i & 1, p.status, kWaitBufferFree)) break;
           tcgen05_fence_after();
           scores(i + 1);
         }
-        // the partial result of step i, once the group's probabilities are in tensor memory
+        // the second product of step i, once the group's probabilities are in tensor memory
         if (!barrier_wait(v_full(i % kRing), (i / kRing) & 1, p.status, kWaitValueFull)) break;
         if (!barrier_wait(p_full(g), i & 1, p.status, kWaitProbabilities)) break;
         tcgen05_fence_after();
@@ -263,27 +276,12 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int row = quarter * 32 + lane;
     const int query = q0 + g * kRows + row;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t tmem_group = tmem_base + static_cast<uint32_t>(2 * g * kKeys) + lane_base;   // buffer b at + 128 b
+    const uint32_t tmem_group = tmem_base + static_cast<uint32_t>(g) * kGroupColumns + lane_base;
     const int my_steps = steps[g];
-    float acc[kHeadDim];
-#pragma unroll
-    for (int i = 0; i < kHeadDim; ++i) acc[i] = 0.f;
-    float row_max = -INFINITY, row_sum = 0.f;
+    float reference = -INFINITY, row_sum = 0.f;     // -inf: the row has seen no finite score yet
     bool alive = true;
     const int last_allowed = p.causal ? min(query, p.k_tokens - 1) : p.k_tokens - 1;   // the last key this row may see
 
-    // acc <- acc * scale + (the partial result in buffer b): one FMA per element
-    auto add_partial = [&](int b, float scale) {
-      uint32_t r0[32], r1[32];
-      tmem_load_32(tmem_group + b * kKeys, r0);
-      tmem_load_32(tmem_group + b * kKeys + 32, r1);
-      tmem_load_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        acc[i] = fmaf(acc[i], scale, __uint_as_float(r0[i]));
-        acc[32 + i] = fmaf(acc[32 + i], scale, __uint_as_float(r1[i]));
-      }
-    };
     // one row of scores: 128 columns, one wait
     auto load_row = [&](uint32_t address, uint32_t (&r)[kKeys], bool edge, int limit) {
 #pragma unroll
@@ -296,109 +294,142 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
       }
     };
+    // the second product of step j has finished: its probabilities and its value tile are spent
+    auto wait_product = [&](int j) {
+      if (!barrier_wait(pv_done(g), j & 1, p.status, kWaitPartial)) return false;
+      tcgen05_fence_after();
+      if (threadIdx.x == g * kRows) {
+        barrier_arrive(v_empty(j % kRing));
+        if (j >= steps[1 - g]) barrier_arrive(v_empty(j % kRing));     // for the other group too, if it has no step j
+      }
+      return true;
+    };
 
-    // With m_j the running maximum after step j and alpha_j = exp2((m_{j-1} - m_j) scale), the result
-    // obeys A_j = A_{j-1} alpha_j + O_j. O_j leaves the tensor core one step late, so the group
-    // keeps alpha_j and applies it when it takes O_j out of tensor memory (step j + 1, or the end).
-    float alpha_previous = 0.f;
     for (int j = 0; j < my_steps; ++j) {
-      const uint32_t tmem_s = tmem_group + (j & 1) * kKeys;
-      if (!barrier_wait(s_full(g, j & 1), (j >> 1) & 1, p.status, kWaitScores)) { alive = false; break; }
+      if (!barrier_wait(s_full(g), j & 1, p.status, kWaitScores)) { alive = false; break; }
       tcgen05_fence_after();
       if (threadIdx.x == g * kRows) {      // the first product has read key tile j: hand it back (for the other group too, if it has no step j)
         barrier_arrive(k_empty(j % kRing));
         if (j >= steps[1 - g]) barrier_arrive(k_empty(j % kRing));
       }
-      // the partial result of step j - 1 (A_{j-1} = A_{j-2} alpha_{j-1} + O_{j-1}); after it that
-      // buffer is free for step j + 1's scores
-      if (j > 0) {
-        if (!barrier_wait(o_full(g, (j - 1) & 1), ((j - 1) >> 1) & 1, p.status, kWaitPartial)) { alive = false; break; }
-        tcgen05_fence_after();
-        if (threadIdx.x == g * kRows) {    // the second product has read value tile j - 1
-          barrier_arrive(v_empty((j - 1) % kRing));
-          if (j - 1 >= steps[1 - g]) barrier_arrive(v_empty((j - 1) % kRing));
-        }
-        add_partial((j - 1) & 1, alpha_previous);
-      }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) barrier_arrive(buffer_free(g));
-
-      // this step's scores: one row per thread, held in registers for both the maximum and the exponentials
+      // this step's scores: one row per thread, held in registers for both the maximum and the
+      // exponentials; the columns go back to the issuer at once
       const int key0 = j * kKeys;
       const int limit = last_allowed - key0;                       // columns > limit are masked for this row
       const bool edge = key0 + kKeys - 1 > (p.causal ? min(q0 + g * kRows, p.k_tokens - 1) : p.k_tokens - 1);   // uniform in the group
       uint32_t r[kKeys];
-      load_row(tmem_s, r, edge, limit);
-      float m0 = row_max, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+      load_row(tmem_group, r, edge, limit);
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) barrier_arrive(s_free(g));
+
+      // (three-input maximum, and below two-element FMA and add: the step is bound by the number of
+      // instructions its eight softmax warps issue, so every element costs half an instruction for
+      // the maximum, half for the scaling, one ex2, half for the sum and half for the rounding)
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
       for (int i = 0; i < kKeys; i += 8) {
-        m0 = fmaxf(fmaxf(m0, __uint_as_float(r[i])), __uint_as_float(r[i + 1]));
-        m1 = fmaxf(fmaxf(m1, __uint_as_float(r[i + 2])), __uint_as_float(r[i + 3]));
-        m2 = fmaxf(fmaxf(m2, __uint_as_float(r[i + 4])), __uint_as_float(r[i + 5]));
-        m3 = fmaxf(fmaxf(m3, __uint_as_float(r[i + 6])), __uint_as_float(r[i + 7]));
+        m0 = max3(m0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+        m1 = max3(m1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        m2 = max3(m2, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+        m3 = max3(m3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
       }
-      const float new_max = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-      const float alpha = exp2_ftz((row_max - new_max) * p.scale_log2);
-      row_max = new_max;
-      alpha_previous = alpha;
-      const float shift = -new_max * p.scale_log2;
+      const float tile_max = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      // The reference point: the first tile's maximum, moved only when a tile rises more than
+      // 2^kSlack above it (from -inf, any finite maximum does). `factor` rescales what the row has
+      // gathered so far; it is 1 for a row that stays.
+      float factor = 1.f;
+      const bool moves = j == 0 || (tile_max - reference) * p.scale_log2 > kSlack;       // false for NaN
+      if (moves) {
+        if (j != 0) factor = exp2_ftz((reference - tile_max) * p.scale_log2);             // from -inf: 0, and nothing was gathered
+        reference = tile_max;
+      }
+      const bool rescale = j != 0 && __any_sync(0xffffffffu, moves);
+      const float shift = reference == -INFINITY ? 0.f : -reference * p.scale_log2;       // all scores -inf so far: every probability is 0
 
       // probabilities and their sum; the probabilities go back into tensor memory as the A operand of
-      // the second product (16-bit pairs over columns 64..127 of this step's buffer)
-      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-      {
-        uint32_t packed[kKeys / 2];
+      // the second product (16-bit pairs)
+      float2 sum0 = make_float2(0.f, 0.f), sum1 = sum0, sum2 = sum0, sum3 = sum0;
+      uint32_t packed[kKeys / 2];
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(shift, shift);
 #pragma unroll
-        for (int chunk = 0; chunk < kKeys / 8; ++chunk) {
-          const float p0 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 0]), p.scale_log2, shift));
-          const float p1 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 1]), p.scale_log2, shift));
-          const float p2 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 2]), p.scale_log2, shift));
-          const float p3 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 3]), p.scale_log2, shift));
-          const float p4 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 4]), p.scale_log2, shift));
-          const float p5 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 5]), p.scale_log2, shift));
-          const float p6 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 6]), p.scale_log2, shift));
-          const float p7 = exp2_ftz(fmaf(__uint_as_float(r[chunk * 8 + 7]), p.scale_log2, shift));
-          sum0 += p0 + p4;
-          sum1 += p1 + p5;
-          sum2 += p2 + p6;
-          sum3 += p3 + p7;
-          packed[chunk * 4 + 0] = pack_pair<T>(p0, p1);
-          packed[chunk * 4 + 1] = pack_pair<T>(p2, p3);
-          packed[chunk * 4 + 2] = pack_pair<T>(p4, p5);
-          packed[chunk * 4 + 3] = pack_pair<T>(p6, p7);
-        }
-        tmem_store_32(tmem_s + kColumnP, *reinterpret_cast<const uint32_t(*)[32]>(&packed[0]));
-        tmem_store_32(tmem_s + kColumnP + 32, *reinterpret_cast<const uint32_t(*)[32]>(&packed[32]));
-        tmem_store_wait();
+      for (int chunk = 0; chunk < kKeys / 8; ++chunk) {
+        const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(r[chunk * 8 + 0]), __uint_as_float(r[chunk * 8 + 1])), scale2, shift2);
+        const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(r[chunk * 8 + 2]), __uint_as_float(r[chunk * 8 + 3])), scale2, shift2);
+        const float2 t2 = __ffma2_rn(make_float2(__uint_as_float(r[chunk * 8 + 4]), __uint_as_float(r[chunk * 8 + 5])), scale2, shift2);
+        const float2 t3 = __ffma2_rn(make_float2(__uint_as_float(r[chunk * 8 + 6]), __uint_as_float(r[chunk * 8 + 7])), scale2, shift2);
+        const float2 e0 = make_float2(exp2_ftz(t0.x), exp2_ftz(t0.y));
+        const float2 e1 = make_float2(exp2_ftz(t1.x), exp2_ftz(t1.y));
+        const float2 e2 = make_float2(exp2_ftz(t2.x), exp2_ftz(t2.y));
+        const float2 e3 = make_float2(exp2_ftz(t3.x), exp2_ftz(t3.y));
+        sum0 = __fadd2_rn(sum0, e0);
+        sum1 = __fadd2_rn(sum1, e1);
+        sum2 = __fadd2_rn(sum2, e2);
+        sum3 = __fadd2_rn(sum3, e3);
+        packed[chunk * 4 + 0] = pack_pair<T>(e0.x, e0.y);
+        packed[chunk * 4 + 1] = pack_pair<T>(e1.x, e1.y);
+        packed[chunk * 4 + 2] = pack_pair<T>(e2.x, e2.y);
+        packed[chunk * 4 + 3] = pack_pair<T>(e3.x, e3.y);
       }
-      row_sum = row_sum * alpha + ((sum0 + sum1) + (sum2 + sum3));
+      const float2 sum01 = __fadd2_rn(sum0, sum1), sum23 = __fadd2_rn(sum2, sum3);
+      const float tile_sum = (sum01.x + sum01.y) + (sum23.x + sum23.y);
+      row_sum = row_sum * factor + tile_sum;
+
+      // The previous step's product still reads the probability columns and adds into the result:
+      // wait for it (it had this step's loads and exponentials to finish), then write.
+      if (j > 0) {
+        if (!wait_product(j - 1)) { alive = false; break; }
+        if (rescale) {       // rare: some row of this warp moved its reference point
+          uint32_t o0[32], o1[32];
+          tmem_load_32(tmem_group + kColumnO, o0);
+          tmem_load_32(tmem_group + kColumnO + 32, o1);
+          tmem_load_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            o0[i] = __float_as_uint(__uint_as_float(o0[i]) * factor);
+            o1[i] = __float_as_uint(__uint_as_float(o1[i]) * factor);
+          }
+          tmem_store_32(tmem_group + kColumnO, o0);
+          tmem_store_32(tmem_group + kColumnO + 32, o1);
+        }
+      }
+      tmem_store_32(tmem_group + kColumnP, *reinterpret_cast<const uint32_t(*)[32]>(&packed[0]));
+      tmem_store_32(tmem_group + kColumnP + 32, *reinterpret_cast<const uint32_t(*)[32]>(&packed[32]));
+      tmem_store_wait();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) barrier_arrive(p_full(g));
     }
 
-    if (alive && my_steps > 0) {
-      if (barrier_wait(o_full(g, (my_steps - 1) & 1), ((my_steps - 1) >> 1) & 1, p.status, kWaitPartial)) {
-        tcgen05_fence_after();
-        add_partial((my_steps - 1) & 1, alpha_previous);
-        if (query < p.q_tokens) {
-          const float inverse = 1.0f / row_sum;
-          T* out_row = static_cast<T*>(p.out) + batch * p.out_batch + head * p.out_head + static_cast<long long>(query) * p.out_token;
-          const bool vector_ok = (reinterpret_cast<uintptr_t>(out_row) & 15) == 0;
-          if (vector_ok) {
+    if (alive && my_steps > 0 && wait_product(my_steps - 1)) {
+      uint32_t o0[32], o1[32];
+      tmem_load_32(tmem_group + kColumnO, o0);
+      tmem_load_32(tmem_group + kColumnO + 32, o1);
+      tmem_load_wait();
+      if (query < p.q_tokens) {
+        const float inverse = 1.0f / row_sum;
+        T* out_row = static_cast<T*>(p.out) + batch * p.out_batch + head * p.out_head + static_cast<long long>(query) * p.out_token;
+        const bool vector_ok = (reinterpret_cast<uintptr_t>(out_row) & 15) == 0;
+        if (vector_ok) {
 #pragma unroll
-            for (int v = 0; v < kHeadDim / 8; ++v) {
-              uint4 word;
-              word.x = pack_pair<T>(acc[v * 8 + 0] * inverse, acc[v * 8 + 1] * inverse);
-              word.y = pack_pair<T>(acc[v * 8 + 2] * inverse, acc[v * 8 + 3] * inverse);
-              word.z = pack_pair<T>(acc[v * 8 + 4] * inverse, acc[v * 8 + 5] * inverse);
-              word.w = pack_pair<T>(acc[v * 8 + 6] * inverse, acc[v * 8 + 7] * inverse);
-              *reinterpret_cast<uint4*>(out_row + v * 8) = word;
-            }
-          } else {
+          for (int v = 0; v < 4; ++v) {
+            uint4 word;
+            word.x = pack_pair<T>(__uint_as_float(o0[v * 8 + 0]) * inverse, __uint_as_float(o0[v * 8 + 1]) * inverse);
+            word.y = pack_pair<T>(__uint_as_float(o0[v * 8 + 2]) * inverse, __uint_as_float(o0[v * 8 + 3]) * inverse);
+            word.z = pack_pair<T>(__uint_as_float(o0[v * 8 + 4]) * inverse, __uint_as_float(o0[v * 8 + 5]) * inverse);
+            word.w = pack_pair<T>(__uint_as_float(o0[v * 8 + 6]) * inverse, __uint_as_float(o0[v * 8 + 7]) * inverse);
+            *reinterpret_cast<uint4*>(out_row + v * 8) = word;
+            word.x = pack_pair<T>(__uint_as_float(o1[v * 8 + 0]) * inverse, __uint_as_float(o1[v * 8 + 1]) * inverse);
+            word.y = pack_pair<T>(__uint_as_float(o1[v * 8 + 2]) * inverse, __uint_as_float(o1[v * 8 + 3]) * inverse);
+            word.z = pack_pair<T>(__uint_as_float(o1[v * 8 + 4]) * inverse, __uint_as_float(o1[v * 8 + 5]) * inverse);
+            word.w = pack_pair<T>(__uint_as_float(o1[v * 8 + 6]) * inverse, __uint_as_float(o1[v * 8 + 7]) * inverse);
+            *reinterpret_cast<uint4*>(out_row + 32 + v * 8) = word;
+          }
+        } else {
 #pragma unroll
-            for (int i = 0; i < kHeadDim; ++i) out_row[i] = from_compute<T, float>(acc[i] * inverse);
+          for (int i = 0; i < 32; ++i) {
+            out_row[i] = from_compute<T, float>(__uint_as_float(o0[i]) * inverse);
+            out_row[32 + i] = from_compute<T, float>(__uint_as_float(o1[i]) * inverse);
           }
         }
       }

@@ -88,6 +88,8 @@ def global_reduce(op: str, local: torch.Tensor, *, offset: int = 0, total: int |
             if world > 1:
                 dist.all_reduce(value, op=dist.ReduceOp.MAX if op == "amax" else dist.ReduceOp.MIN, group=group)
             return value.reshape(())
+        if world == 1:
+            return value.reshape(())         # the kernel's maximum already propagates NaN; nothing to exchange
         wide = value.to(accumulate)
         nan_flag = torch.isnan(wide).to(accumulate)
         clean = torch.where(torch.isnan(wide), torch.full_like(wide, -math.inf if op == "amax" else math.inf), wide)

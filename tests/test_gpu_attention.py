@@ -41,7 +41,7 @@ def draw(shape, dtype, seed, spread=1.0):
     return (torch.randn(*shape, generator=g) * spread).to(dtype)
 
 
-def check(got, q, k, v, scale, causal):
+def check(got, q, k, v, scale, causal, half_oracle=True):
     dtype = q.dtype
     ulp = 2.0**-8 if dtype == torch.bfloat16 else 2.0**-11
     q64, k64, v64 = (t.double().numpy() for t in (q, k, v))
@@ -51,6 +51,8 @@ def check(got, q, k, v, scale, causal):
     error = np.abs(got.detach().cpu().double().numpy() - exact)
     worst = (error / bound).max()
     assert worst <= 1.0, f"error {error.max():.3e} exceeds the float64 bound by {worst:.2f}x"
+    if not half_oracle:
+        return
     ref = tessiq0.attention(q, k, v, scale, causal).float()
     torch.testing.assert_close(got.detach().cpu().float(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
 
@@ -89,6 +91,32 @@ def test_attention_f16_and_large_scores(tq):
     for causal in (True, False):
         got = tq.attention(q.cuda(), k.cuda(), v.cuda(), 1.0 / 8, causal)   # scores up to ~ +-100: sharp rows
         check(got, q, k, v, 1.0 / 8, causal)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_attention_when_the_scores_keep_rising(tq, dtype):
+    """The kernel keeps one reference point per row and moves it only when a key tile rises far above
+    it, rescaling what the row has gathered. Scores that grow with the key index make every tile
+    move it; scores that fall never do; a late spike moves it once; and rows of one warp differ."""
+    tokens = 640
+    g = torch.Generator().manual_seed(21)
+    direction = torch.randn(64, generator=g)
+    direction /= direction.norm()
+    ramp = torch.linspace(0.0, 60.0, tokens)
+    v = draw((1, 1, tokens, 64), dtype, 22)
+    noise = torch.randn(tokens, 64, generator=g) * 0.3
+    for name, profile in (("rising", ramp), ("falling", ramp.flip(0)), ("spike", torch.where(torch.arange(tokens) == 500, 90.0, 0.0)),
+                          ("steps", (torch.arange(tokens) // 128).float() * 11.0)):
+        k = (noise + profile[:, None] * direction).to(dtype).view(1, 1, tokens, 64)
+        # rows alternate between following the profile and opposing it, so the rows of one warp disagree
+        sign = torch.where(torch.arange(tokens) % 3 == 0, -1.0, 1.0)
+        q = ((sign[:, None] * direction) * 8.0 + torch.randn(tokens, 64, generator=g) * 0.1).to(dtype).view(1, 1, tokens, 64)
+        for causal in (True, False):
+            got = tq.attention(q.cuda(), k.cuda(), v.cuda(), 0.125, causal)
+            # scores of +-60 rounded to 16 bits between the oracle's nodes move ITS result by tens of
+            # per cent, so only the float64 bound is meaningful here
+            check(got, q, k, v, 0.125, causal, half_oracle=False)
+    assert poll() == 0
 
 
 def test_attention_reads_a_fused_qkv_projection_in_place_and_writes_token_major(tq):
