@@ -45,6 +45,7 @@ template <typename C> __device__ __forceinline__ C shfl_xor(C v, int offset) {
 
 template <typename T>
 struct SumReducer {
+  static constexpr bool kSeeded = false;   // no seed / step_seeded / set_count protocol (see MomentsReducer)
   using C = typename Compute<T>::type;
   using Acc = std::conditional_t<std::is_integral_v<C>, long long, C>;
   using Out = std::conditional_t<std::is_same_v<T, int>, long long, T>;
@@ -72,6 +73,7 @@ struct SumReducer {
 
 template <typename T, bool kMax>
 struct ExtremeReducer {
+  static constexpr bool kSeeded = false;   // no seed / step_seeded / set_count protocol (see MomentsReducer)
   using C = typename Compute<T>::type;
   using Acc = C;
   using Out = T;
@@ -122,6 +124,7 @@ struct alignas(16) Indexed {
 
 template <typename T>
 struct ArgmaxReducer {
+  static constexpr bool kSeeded = false;   // no seed / step_seeded / set_count protocol (see MomentsReducer)
   using C = typename Compute<T>::type;
   using Acc = Indexed<C>;
   using Out = long long;
@@ -277,6 +280,7 @@ __device__ __forceinline__ float stat_exp2(float t) {
 // all -inf at (-inf, count) instead of NaN; a NaN makes the maximum and the sum NaN.
 template <typename T>
 struct SoftmaxStatReducer {
+  static constexpr bool kSeeded = false;   // no seed / step_seeded / set_count protocol (see MomentsReducer)
   using C = float;
   using Acc = MaxSum;
   using Out = MaxSum;
@@ -371,6 +375,16 @@ struct MomentsReducer {
 #pragma unroll
     for (int e = 0; e < VEC; ++e) step<VEC>(local, x.v[e], 0);
   }
+  // The columns kernel seeds the pivot with the thread's first value before its loop and sets the
+  // count after it, which leaves a subtraction, an add and an FMA per element.
+  static constexpr bool kSeeded = true;
+  template <int VEC> __device__ static void seed(Local<VEC>& local, T v) { local.pivot = to_compute(v); }
+  template <int VEC> __device__ static void step_seeded(Local<VEC>& local, T v) {
+    const float d = to_compute(v) - local.pivot;
+    local.s1 += d;
+    local.s2 = fmaf(d, d, local.s2);
+  }
+  template <int VEC> __device__ static void set_count(Local<VEC>& local, int count) { local.n = static_cast<float>(count); }
   template <int VEC> __device__ static Acc to_acc(const Local<VEC>& local) {
     if (local.n == 0.f) return identity();
     const float shifted_mean = local.s1 / local.n;
@@ -574,32 +588,63 @@ reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long
       // shared memory with cp.async: the copies in flight cost no registers, so a thread keeps
       // kRingDepth - 1 rows (up to 112 bytes) on their way from HBM while it folds the oldest.
       // A slot is written and read by the same thread only, so no barrier is involved.
-      Vec<T, VEC>* ring = reinterpret_cast<Vec<T, VEC>*>(cluster_scratch + lanes_x * VEC);
+      // The loop is unrolled by the ring's depth, so slot addresses are constants, the source is a
+      // pointer that advances by one stride, and the count is 32 bits: per row a wait, a shared
+      // load, a copy, a commit and a pointer add besides the reducer's own work (the rolled form
+      // with 64-bit index arithmetic spent 18 instructions per element on 4-byte moments and made
+      // every 2-byte column reduction issue-bound).
+      Vec<T, VEC>* ring = reinterpret_cast<Vec<T, VEC>*>(cluster_scratch + lanes_x * VEC) + threadIdx.x;     // slot d at + d * kBlock
+      const uint32_t ring_address = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
+      constexpr uint32_t kSlotBytes = static_cast<uint32_t>(kBlock) * kBytes;
       const long long first = begin + ty;
-      const long long count = first < end ? (end - first + lanes_y - 1) / lanes_y : 0;
-      auto issue = [&](long long i) {
-        if (i < count) {
-          const uint32_t slot = static_cast<uint32_t>(__cvta_generic_to_shared(ring + (i % kRingDepth) * kBlock + threadIdx.x));
-          const T* source = base + (first + i * lanes_y) * inner;
-          if constexpr (kBytes == 16) {
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(slot), "l"(source) : "memory");
-          } else {
-            asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(slot), "l"(source), "n"(kBytes) : "memory");
+      const int count = first < end ? static_cast<int>((end - first + lanes_y - 1) / lanes_y) : 0;   // the host keeps this below 2^31
+      const T* source = base + first * inner;
+      const long long stride = static_cast<long long>(lanes_y) * inner;
+      long long ri = first;
+      auto copy = [&](int slot) {
+        if constexpr (kBytes == 16) {
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring_address + slot * kSlotBytes), "l"(source) : "memory");
+        } else {
+          asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(ring_address + slot * kSlotBytes), "l"(source), "n"(kBytes) : "memory");
+        }
+        source += stride;
+      };
+      if constexpr (R::kSeeded) {
+        if (count > 0) {
+          const Vec<T, VEC> x = load_stream<T, VEC>(source);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) R::template seed<1>(local[e], x.v[e]);
+        }
+      }
+#pragma unroll
+      for (int d = 0; d < kRingDepth - 1; ++d) {
+        if (d < count) copy(d);
+        asm volatile("cp.async.commit_group;" ::: "memory");   // one group per row, empty past the end
+      }
+      for (int i = 0; i < count; i += kRingDepth) {
+#pragma unroll
+        for (int d = 0; d < kRingDepth; ++d) {
+          if (i + d < count) {
+            asm volatile("cp.async.wait_group %0;" ::"n"(kRingDepth - 2) : "memory");   // row i + d has landed
+            const Vec<T, VEC> x = ring[d * kBlock];
+            if constexpr (R::kSeeded) {
+#pragma unroll
+              for (int e = 0; e < VEC; ++e) R::template step_seeded<1>(local[e], x.v[e]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < VEC; ++e) R::template step<1>(local[e], x.v[e], ri);
+              ri += lanes_y;
+            }
+            if (i + d + kRingDepth - 1 < count) copy((d + kRingDepth - 1) % kRingDepth);   // into the slot read one row ago
+            asm volatile("cp.async.commit_group;" ::: "memory");
           }
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");   // one group per row, empty past the end
-      };
-#pragma unroll
-      for (int d = 0; d < kRingDepth - 1; ++d) issue(d);
-      for (long long i = 0; i < count; ++i) {
-        asm volatile("cp.async.wait_group %0;" ::"n"(kRingDepth - 2) : "memory");   // row i has landed
-        const Vec<T, VEC> x = ring[(i % kRingDepth) * kBlock + threadIdx.x];
-        const long long ri = first + i * lanes_y;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) R::template step<1>(local[e], x.v[e], ri);
-        issue(i + kRingDepth - 1);   // into the slot read one iteration ago
       }
       asm volatile("cp.async.wait_group 0;" ::: "memory");
+      if constexpr (R::kSeeded) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) R::template set_count<1>(local[e], count);
+      }
     } else {
       for (long long r = begin + ty; r < end; r += static_cast<long long>(lanes_y) * UNROLL) {
         Vec<T, VEC> x[UNROLL];
@@ -788,7 +833,7 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
     // Measured on B200 at [32768, 4096]: 4-byte sums and extremes are fastest with plain unrolled
     // loads, 64 lanes along `inner` and one wave of CTAs; 2-byte types and argmax (whose state
     // costs registers) with the cp.async ring and 32 lanes.
-    p.ring = size <= 2 || op == TQ_ARGMAX || op >= kOpSoftmaxStat;
+    p.ring = (size <= 2 || op == TQ_ARGMAX || op >= kOpSoftmaxStat) && reduce < (1ll << 31);   // the ring counts a thread's rows in 32 bits
     int lanes = p.ring ? 32 : 64;
     if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_LANES")) {  // tuning override: 1..256, a power of two
       const int value = std::atoi(forced);
