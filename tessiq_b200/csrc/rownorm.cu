@@ -22,6 +22,8 @@
 
 #include <limits>
 
+#include <cstdlib>
+
 #include "common.h"
 
 namespace cg = cooperative_groups;
@@ -442,6 +444,11 @@ tq_status run_vector(const RowArgs& args, cudaStream_t stream, bool* handled) {
   const long long blocks = args.rows * cluster;
   // Few threads holding several vectors each beat many threads holding one: a row then costs
   // fewer shuffles and barriers per byte, and more rows are in flight per SM.
+  // Measured on B200, 32768 rows of 4096 bf16 (512 vectors): 64 threads x 8 vectors 87.5 us (softmax) /
+  // 94 (LayerNorm); 128 x 4: 99 / 101; 32 x 16: 96 / 110; 256 x 2: 121 / 156.
+  if (cluster == 1 && per_cta <= 64 * 8) {
+    return launch_rows(row_cluster_kernel<T, OutT, VEC, 8, OP, 64>, blocks, cluster, stream, args, "row_cluster_kernel", 64);
+  }
   if (per_cta <= 128 * 4) {
     return launch_rows(row_cluster_kernel<T, OutT, VEC, 4, OP, 128>, blocks, cluster, stream, args, "row_cluster_kernel", 128);
   }
