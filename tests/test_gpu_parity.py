@@ -488,7 +488,7 @@ def test_config_2_full_size_reductions(tq):
 # ---------------------------------------------------------------------------------------------
 # softmax, LayerNorm, RMSNorm, BatchNorm
 
-WIDTHS = [1, 7, 255, 256, 257, 1000, 1024, 2048, 4096, 5000, 8192, 32768, 65536, 70000, 200000]
+WIDTHS = [1, 7, 255, 256, 257, 1000, 1024, 2048, 4096, 5000, 8192, 12000, 16384, 32768, 65536, 70000, 200000]
 
 
 @pytest.mark.parametrize("width", WIDTHS)
@@ -499,6 +499,18 @@ def test_softmax_rows(tq, width):
     got = tq.softmax(dev(x), -1)
     close32(got, tessiq0.softmax(x, -1), rtol=1e-5, scale=1e-6)
     assert (got.sum(-1).cpu() - 1).abs().max() < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("width", [2048, 2056, 4096, 16384, 20000, 32768, 65536])
+def test_softmax_and_layer_norm_rows_of_half_types(tq, dtype, width):
+    # every CTA shape of the row kernels for 2-byte elements: a warp per row, 64 threads x 8 vectors, 256 x 16, clusters
+    g = torch.Generator().manual_seed(width + 3)
+    x = (torch.randn(5, width, generator=g) * 2 + 0.5).to(dtype)
+    w = (1 + torch.randn(width, generator=g) * 0.1).to(dtype)
+    b = (torch.randn(width, generator=g) * 0.1).to(dtype)
+    close16(tq.softmax(dev(x), -1), tessiq0.softmax(x, -1))
+    close16(tq.layer_norm(dev(x), [width], dev(w), dev(b), 1e-5), tessiq0.native_layer_norm(x, [width], w, b, 1e-5)[0])
 
 
 def test_softmax_matches_golden_every_dim_and_type(tq, golden):
