@@ -856,6 +856,10 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
     // The cluster's reduce-scatter gives every CTA a whole number of threads' accumulators.
     int max_cluster = kMaxCluster;
     while (max_cluster > lanes) max_cluster /= 2;
+    if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_CLUSTER")) {  // tuning override: 1, 2, 4 or 8
+      const int value = std::atoi(forced);
+      if (value >= 1 && value <= max_cluster && (value & (value - 1)) == 0) max_cluster = value;
+    }
     if (want <= max_cluster) {
       p.split = floor_pow2(want);
       p.cluster = p.split;
