@@ -90,6 +90,44 @@ __device__ __forceinline__ float activate(float v, int activation) {
   return v;
 }
 
+// The same on two elements at once with the .f32x2 forms of add, mul and fma, and with the
+// activation a compile-time constant: the epilogue of a short-K product (12 k-blocks at K = 768) is
+// what the CTA waits for, and it is bound by the instructions its eight warps issue.
+template <int ACTIVATION>
+__device__ __forceinline__ float2 activate_pair(float2 v) {
+  if constexpr (ACTIVATION == TQ_ACT_GELU_TANH) {
+    // v / (1 + exp2(v (c0 + c1 v^2))), c0 = -2 k log2(e) = -2.3022082, c1 = 0.044715 c0
+    const float2 square = __fmul2_rn(v, v);
+    const float2 inner = __ffma2_rn(square, make_float2(-0.10294324f, -0.10294324f), make_float2(-2.302208198144325f, -2.302208198144325f));
+    const float2 t = __fmul2_rn(v, inner);
+    const float2 denominator = __fadd2_rn(make_float2(exp2_ftz(t.x), exp2_ftz(t.y)), make_float2(1.0f, 1.0f));
+    return __fmul2_rn(v, make_float2(rcp_ftz(denominator.x), rcp_ftz(denominator.y)));
+  } else if constexpr (ACTIVATION == TQ_ACT_GELU_ERF) {
+    return make_float2(activate(v.x, TQ_ACT_GELU_ERF), activate(v.y, TQ_ACT_GELU_ERF));
+  } else {
+    return v;
+  }
+}
+
+// Eight consecutive columns of one row: accumulators + bias, activation, residual, one rounding.
+template <typename T, int ACTIVATION, bool RESIDUAL>
+__device__ __forceinline__ uint4 finish_unit(const uint32_t (&r0)[32], const uint32_t (&r1)[32], const float* bias, int unit, const uint4& residual) {
+  Vec<T, 8> out;
+  const Vec<T, 8> add = *reinterpret_cast<const Vec<T, 8>*>(&residual);
+  const float4 bias_low = *reinterpret_cast<const float4*>(bias + unit * 8), bias_high = *reinterpret_cast<const float4*>(bias + unit * 8 + 4);
+  const float bias_of[8] = {bias_low.x, bias_low.y, bias_low.z, bias_low.w, bias_high.x, bias_high.y, bias_high.z, bias_high.w};
+#pragma unroll
+  for (int e = 0; e < 8; e += 2) {
+    const int j = unit * 8 + e;
+    const float2 accumulator = make_float2(__uint_as_float(j < 32 ? r0[j] : r1[j - 32]), __uint_as_float(j < 32 ? r0[j + 1] : r1[j - 31]));
+    float2 value = activate_pair<ACTIVATION>(__fadd2_rn(accumulator, make_float2(bias_of[e], bias_of[e + 1])));
+    if constexpr (RESIDUAL) value = __fadd2_rn(value, make_float2(to_compute(add.v[e]), to_compute(add.v[e + 1])));
+    out.v[e] = from_compute<T, float>(value.x);
+    out.v[e + 1] = from_compute<T, float>(value.y);
+  }
+  return *reinterpret_cast<const uint4*>(&out);
+}
+
 // Tiles in groups of 16 rows of tiles, so that the CTAs running at one time share A and B slices
 // in L2.
 __device__ __forceinline__ void tile_coordinates(long long tile, const GemmParams& p, int& batch, int& tile_m, int& tile_n) {
@@ -149,28 +187,37 @@ __device__ __forceinline__ void epilogue_rows(uint32_t tmem_accumulator, int qua
         }
         __syncwarp();
       }
+      auto finish = [&](auto activation_tag, auto residual_tag) {
+        constexpr int kActivation = decltype(activation_tag)::value;
+        constexpr bool kResidual = decltype(residual_tag)::value;
 #pragma unroll
-      for (int unit = 0; unit < 8; ++unit) {
-        Vec<T, 8> out, add;
-        if (residual_tile != nullptr) {
-          uint4 word;
-          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(word.x), "=r"(word.y), "=r"(word.z), "=r"(word.w)
-                       : "r"(staging_address + lane * 128 + ((unit ^ (lane & 7)) << 4))
+        for (int unit = 0; unit < 8; ++unit) {
+          uint4 word = make_uint4(0, 0, 0, 0);
+          if constexpr (kResidual) {
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(word.x), "=r"(word.y), "=r"(word.z), "=r"(word.w)
+                         : "r"(staging_address + lane * 128 + ((unit ^ (lane & 7)) << 4))
+                         : "memory");
+          }
+          word = finish_unit<T, kActivation, kResidual>(r0, r1, bias_tile + column0, unit, word);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(staging_address + lane * 128 + ((unit ^ (lane & 7)) << 4)),
+                       "r"(word.x), "r"(word.y), "r"(word.z), "r"(word.w)
                        : "memory");
-          add = *reinterpret_cast<const Vec<T, 8>*>(&word);
         }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const int j = unit * 8 + e;
-          float value = activate(__uint_as_float(j < 32 ? r0[j] : r1[j - 32]) + bias_tile[column0 + j], activation);
-          if (residual_tile != nullptr) value += to_compute(add.v[e]);
-          out.v[e] = from_compute<T, float>(value);
+      };
+      auto finish_with = [&](auto activation_tag) {
+        if (residual_tile != nullptr) {
+          finish(activation_tag, std::true_type{});
+        } else {
+          finish(activation_tag, std::false_type{});
         }
-        const uint4 word = *reinterpret_cast<const uint4*>(&out);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(staging_address + lane * 128 + ((unit ^ (lane & 7)) << 4)),
-                     "r"(word.x), "r"(word.y), "r"(word.z), "r"(word.w)
-                     : "memory");
+      };
+      if (activation == TQ_ACT_GELU_TANH) {
+        finish_with(std::integral_constant<int, TQ_ACT_GELU_TANH>{});
+      } else if (activation == TQ_ACT_GELU_ERF) {
+        finish_with(std::integral_constant<int, TQ_ACT_GELU_ERF>{});
+      } else {
+        finish_with(std::integral_constant<int, TQ_ACT_NONE>{});
       }
       __syncwarp();
       const int unit = lane & 7;
