@@ -102,6 +102,34 @@ def test_residual_rides_in_the_epilogue(tq, m, n, k, act):
     assert poll() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("act", ["gelu", "gelu_tanh"])
+def test_gelu_epilogues_over_the_whole_range(tq, dtype, act):
+    """The activations of the epilogue, value by value: an identity product carries a sweep of
+    -12 .. 12 through the kernel. The erf form is v * Phi(v) with Phi from a fitted erfc (it keeps the
+    negative tail's digits; 1 + erff cancels there); both must land within one rounding of the
+    float64 value. Special values come in through the bias (inf in the product would meet the
+    identity's zeros): +inf -> +inf, -inf -> NaN (inf * 0, as the reference's formula gives), NaN -> NaN."""
+    n = 256
+    sweep = torch.linspace(-12.0, 12.0, 128 * n).view(128, n).to(dtype)
+    eye = torch.eye(n).to(dtype)
+    got = tq.gemm(sweep.cuda(), eye.cuda(), torch.zeros(n).to(dtype).cuda(), act).cpu().double()
+    v = sweep.double()
+    if act == "gelu":
+        exact = torch.relu(v) - 0.5 * v.abs() * torch.special.erfc(v.abs() * 0.7071067811865476)
+    else:
+        exact = v / (1 + torch.exp(-2 * 0.7978845608028654 * (v + 0.044715 * v**3)))
+    ulp = 2.0**-8 if dtype == torch.bfloat16 else 2.0**-11
+    floor = 2.0**-120 if dtype == torch.bfloat16 else 2.0**-24      # f32 arithmetic runs out near its smallest normal (2^t overflows first); f16's last subnormal
+    worst = ((got - exact).abs() / (exact.abs() * ulp + floor)).max().item()
+    assert worst <= 1.02, f"{worst:.3f} roundings"
+    bias = torch.zeros(n)
+    bias[:4] = torch.tensor([float("inf"), float("-inf"), float("nan"), -30.0])
+    special = tq.gemm(torch.zeros(128, n).to(dtype).cuda(), eye.cuda(), bias.to(dtype).cuda(), act).cpu().float()
+    assert special[0, 0].item() == float("inf") and torch.isnan(special[0, 1]) and torch.isnan(special[0, 2])
+    assert special[0, 3].item() == 0.0 and (special[:, 4:] == 0).all()
+
+
 def test_against_the_oracle_and_golden(tq, golden):
     x, w, bias = (torch.from_numpy(golden[name]) for name in ("gemm_x", "gemm_w", "gemm_bias"))
     xb, wb, bb = x.bfloat16(), w.bfloat16(), bias.bfloat16()
