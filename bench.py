@@ -1,4 +1,4 @@
-"""Benchmark of the hot path on BASELINE config 2: row reductions and normalisation.
+"""Benchmark of the hot path on benchmark config 2: row reductions and normalisation.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
@@ -50,7 +50,7 @@ UNIT = "GB/s"
 
 
 def algorithmic_bytes(rows: int, width: int, size: int) -> dict[str, int]:
-    """Bytes per operation (SURVEY/DESIGN table): operands read once, results written once."""
+    """Algorithmic bytes per operation: every operand read once, every result written once."""
     n = rows * width
     out = {}
     for view, (r, w) in (("rows", (rows, width)), ("cols", (width, rows))):
@@ -409,7 +409,7 @@ def run_ours(args) -> dict:
 
 
 def other_configs(device: int, stream) -> dict:
-    """The other BASELINE configs' headline kernels on this rank's GPU, device-timed: config 1's
+    """The other benchmark configs' headline kernels on this rank's GPU, device-timed: config 1's
     fused chain (8 rotating buffer sets, graph replay), config 3's GEMM + bias + GELU (TFLOP/s
     against the measured cuBLAS bf16 peaks), config 5's six-op chain at 2^28 elements."""
     import torch
@@ -495,7 +495,7 @@ def other_configs(device: int, stream) -> dict:
 
 
 def decoder_block(dev: str, stream) -> dict:
-    """BASELINE config 4, the batch of 64 per GPU (weak scaling like the rest of this file):
+    """benchmark config 4, the batch of 64 per GPU (weak scaling like the rest of this file):
     LayerNorm + QKV GEMM + causal softmax attention + output projection + GELU MLP + residual
     adds, d_model 768, 12 heads, MLP 3072, 1024 tokens, bf16 inference, compiled by this repo's
     torch.compile backend and replayed as a CUDA graph."""
@@ -561,7 +561,7 @@ def run_profile(args) -> None:
 
     torch.cuda.set_device(0)
     if args.profile.startswith("chain1"):
-        # BASELINE config 1 (the fused chain on x[4096,4096] with a bias row), over rotating
+        # benchmark config 1 (the fused chain on x[4096,4096] with a bias row), over rotating
         # buffers so that no launch finds its input in L2. `chain1_precise` selects math precise.
         from tessiq_b200.kernel import FusedKernel
 
@@ -609,7 +609,7 @@ def run_profile(args) -> None:
 
 
 def run_sweep(args) -> dict:
-    """BASELINE config 5 on this rank's GPU: for fp32, bf16 and fp16 tensors of 2^20 .. 2^30 elements
+    """benchmark config 5 on this rank's GPU: for fp32, bf16 and fp16 tensors of 2^20 .. 2^30 elements
     (per GPU: weak scaling), the six-op chain (add, mul, exp, tanh, where on a > 0, cast), the [R,1]
     row broadcast `x + r` with 4096-wide rows, and the global sum / amax whose per-GPU partials are
     all-reduced. Device time per launch from CUDA events around a CUDA-graph replay of 10 launches;
@@ -848,7 +848,7 @@ def main() -> None:
                         help="for ncu: run only eager launches of OP (e.g. softmax_rows_f32, or `all`), "
                              "W warm-up + K steps, and print nothing else")
     parser.add_argument("--sweep", action="store_true",
-                        help="BASELINE config 5's size sweep (2^20 .. 2^30 elements, three element types) instead of the bench line")
+                        help="benchmark config 5's size sweep (2^20 .. 2^30 elements, three element types) instead of the bench line")
     args = parser.parse_args()
     globals()["ROWS"] = args.rows
     if args.profile:

@@ -96,7 +96,7 @@ TQ_EXPORT int tq_oracle_unary_f32(int op, const float* x, float* y, int64_t n) {
   return 0;
 }
 
-/* BASELINE config 1, one element at a time, in float: gelu_tanh(x + b) * sigmoid(x) - 0.5 x with
+/* benchmark config 1, one element at a time, in float: gelu_tanh(x + b) * sigmoid(x) - 0.5 x with
  * b read as i % cols (the cycled read of csrc/tessiq/codegen/kernel.cpp:168-206). */
 TQ_EXPORT void tq_oracle_chain_gelu_sigmoid_f32(const float* x, const float* b, float* y,
                                                 int64_t n, int64_t cols) {
@@ -108,7 +108,7 @@ TQ_EXPORT void tq_oracle_chain_gelu_sigmoid_f32(const float* x, const float* b, 
   }
 }
 
-/* BASELINE config 5: t = tanh(exp(a + b) * b); y = a > 0 ? t : a, in float (the caller rounds). */
+/* benchmark config 5: t = tanh(exp(a + b) * b); y = a > 0 ? t : a, in float (the caller rounds). */
 TQ_EXPORT void tq_oracle_chain_six_ops_f32(const float* a, const float* b, float* y, int64_t n) {
   for (int64_t i = 0; i < n; ++i) {
     const float t = tanhf(expf(a[i] + b[i]) * b[i]);

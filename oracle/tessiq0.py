@@ -67,7 +67,7 @@ def elementwise(op: str, *operands):
 
 
 def chain_gelu_sigmoid(x, b):
-    """BASELINE config 1: y = gelu_tanh(x + b) * sigmoid(x) - 0.5 * x, node by node."""
+    """benchmark config 1: y = gelu_tanh(x + b) * sigmoid(x) - 0.5 * x, node by node."""
     _cpu(x, b)
     t0 = torch.add(x, b)
     t1 = F.gelu(t0, approximate="tanh")
@@ -78,7 +78,7 @@ def chain_gelu_sigmoid(x, b):
 
 
 def chain_six_ops(a, b, out_dtype):
-    """BASELINE config 5: t = tanh(exp(a + b) * b); y = where(a > 0, t, a).to(out_dtype)."""
+    """benchmark config 5: t = tanh(exp(a + b) * b); y = where(a > 0, t, a).to(out_dtype)."""
     _cpu(a, b)
     t = torch.tanh(torch.mul(torch.exp(torch.add(a, b)), b))
     return torch.where(torch.gt(a, 0), t, a).to(out_dtype)
@@ -138,7 +138,7 @@ def gemm_bias_gelu(x, weight, bias):
 
 
 def matmul_bias_gelu_tanh(a, b, bias):
-    """BASELINE config 3 as an imported graph runs it: mm, add, gelu — three nodes, so a bf16
+    """benchmark config 3 as an imported graph runs it: mm, add, gelu — three nodes, so a bf16
     result is rounded after each."""
     _cpu(a, b, bias)
     return F.gelu(torch.add(torch.mm(a, b), bias), approximate="tanh")

@@ -31,7 +31,7 @@ def test_config_1_becomes_one_kernel():
     (kernel,) = recipe.kernels
     assert kernel.reads == ["same", "cycled"] and len(kernel.members) == 6
     assert "gelu_tanh" in kernel.program and "sigmoid" in kernel.program
-    # the reference splits this chain in two groups around a host gelu (observed IR)
+    # the reference splits this chain in two groups around a host gelu (the IR the reference prints for it)
 
 
 def test_config_5_chain_fuses_predicate_and_cast():

@@ -131,7 +131,7 @@ def test_attention_reads_a_fused_qkv_projection_in_place_and_writes_token_major(
 
 
 def test_attention_properties_at_the_decoder_block_size(tq):
-    """BASELINE config 4's attention shape (batch 64 is cut to 8 to bound the test's memory):
+    """benchmark config 4's attention shape (batch 64 is cut to 8 to bound the test's memory):
     with v = 1 every output is 1 (the probabilities of a row sum to one); under the causal mask
     row 0 returns v[0]; and shifting every key by a constant vector changes nothing for rows whose
     query is orthogonal to it — here checked through q = 0, which gives the running mean of v."""
