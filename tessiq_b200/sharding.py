@@ -90,13 +90,16 @@ def global_reduce(op: str, local: torch.Tensor, *, offset: int = 0, total: int |
             return value.reshape(())
         if world == 1:
             return value.reshape(())         # the kernel's maximum already propagates NaN; nothing to exchange
+        # One all-reduce carries both the value and a NaN flag: a collective's maximum does not promise
+        # to propagate NaN, so NaN partials are replaced by the identity and flagged; the flag rides
+        # along with the sign that makes the same MAX (or MIN) pick "some rank saw a NaN".
         wide = value.to(accumulate)
-        nan_flag = torch.isnan(wide).to(accumulate)
-        clean = torch.where(torch.isnan(wide), torch.full_like(wide, -math.inf if op == "amax" else math.inf), wide)
-        if world > 1:
-            dist.all_reduce(clean, op=dist.ReduceOp.MAX if op == "amax" else dist.ReduceOp.MIN, group=group)
-            dist.all_reduce(nan_flag, op=dist.ReduceOp.MAX, group=group)
-        result = torch.where(nan_flag > 0, torch.full_like(clean, math.nan), clean)
+        is_nan = torch.isnan(wide)
+        identity = -math.inf if op == "amax" else math.inf
+        flag_sign = 1.0 if op == "amax" else -1.0
+        packed = torch.cat([torch.where(is_nan, torch.full_like(wide, identity), wide), is_nan.to(accumulate) * flag_sign])
+        dist.all_reduce(packed, op=dist.ReduceOp.MAX if op == "amax" else dist.ReduceOp.MIN, group=group)
+        result = torch.where(packed[1:] != 0, torch.full_like(packed[:1], math.nan), packed[:1])
         return result.reshape(()).to(local.dtype)
 
     # argmax
