@@ -147,6 +147,27 @@ def test_launch_argument_checks_need_no_gpu(lib):
     assert L.tq_pack_launch(3, 1, (ctypes.c_int64 * 1)(4), (ctypes.c_int64 * 1)(1), ctypes.c_void_p(16), ctypes.c_void_p(32), 0, None) == lib.TQ_UNSUPPORTED
 
 
+def test_transposed_planning_query_needs_no_gpu(lib):
+    """Which form softmax / LayerNorm over a transposed view takes is a host-side decision: long
+    columns of a small tensor are kept on chip (2 passes over HBM), everything else takes the
+    statistics pass and the transposing pass (3)."""
+    L = lib.lib
+    passes = ctypes.c_int32()
+
+    def ask(dtype, batch, rows, cols, layer_norm=0):
+        assert L.tq_transposed_passes(layer_norm, dtype, batch, rows, cols, 0, ctypes.byref(passes)) == 0
+        return passes.value
+
+    assert ask(lib.F32, 1, 8192, 512) == 2 and ask(lib.BF16, 1, 51200, 128, 1) == 2 and ask(lib.F16, 4, 16384, 32) == 2
+    assert ask(lib.F32, 1, 32768, 4096) == 3          # 512 MiB
+    assert ask(lib.F32, 64, 1024, 1024) == 3          # short columns
+    assert ask(lib.F32, 1, 8200, 512) == 3            # rows not a multiple of 8 vectors
+    assert ask(lib.BF16, 1, 8192, 24) == 3            # cols not a multiple of 2 vectors
+    assert ask(lib.F32, 1, 51264, 16) == 3            # a CTA's share would not fit its shared memory
+    assert L.tq_transposed_passes(0, lib.F32, 1, 8192, 512, 0, None) == lib.TQ_INVALID_ARGUMENT
+    assert L.tq_transposed_passes(0, lib.F32, -1, 8192, 512, 0, ctypes.byref(passes)) == lib.TQ_INVALID_ARGUMENT
+
+
 def test_status_maps_to_the_reference_exceptions(lib):
     with pytest.raises(ValueError):
         lib.check(lib.TQ_INVALID_ARGUMENT)
