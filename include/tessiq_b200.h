@@ -311,6 +311,14 @@ tq_status tq_transposed_workspace_bytes(int32_t layer_norm, tq_dtype dtype, int6
                                         int64_t cols, int32_t device, size_t* bytes);
 tq_status tq_transposed_passes(int32_t layer_norm, tq_dtype dtype, int64_t batch, int64_t rows, int64_t cols,
                                int32_t device, int32_t* passes);
+/* Which kernel tq_*_transposed_launch runs for a shape (the pointers' alignment can still send a
+ * call to the three-pass form): statistics read in place + a transposing normalise (two launches);
+ * the column slab kept in a cluster's shared memory; or the persistent kernel that walks panels of
+ * columns with TMA (one launch, statistics and normalise side by side; f32 tensors of 256 MiB and
+ * more whose rows are a multiple of 64 and whose columns a multiple of 128). */
+enum { TQ_TRANSPOSED_THREE_PASS = 0, TQ_TRANSPOSED_SLAB = 1, TQ_TRANSPOSED_PANELS = 2 };
+tq_status tq_transposed_form(int32_t layer_norm, tq_dtype dtype, int64_t batch, int64_t rows, int64_t cols,
+                             int32_t device, int32_t* form);
 tq_status tq_softmax_transposed_launch(tq_dtype dtype, const void* in, void* out, int64_t batch, int64_t rows,
                                        int64_t cols, void* workspace, size_t workspace_bytes, int32_t device,
                                        void* stream);
@@ -486,6 +494,12 @@ tq_status tq_recipe_run(const tq_recipe* recipe, int32_t device, void* stream);
  * this library's kernels completed, otherwise a code naming the wait that gave up. Synchronises
  * `stream` first. */
 tq_status tq_status_poll(int32_t device, void* stream, int32_t* device_status);
+
+/* The first `count` (<= 64) 32-bit words of the device's status block, without clearing it: word 0 is
+ * what tq_status_poll returns, the words behind it say where the wait that gave up was (CTA, thread
+ * and up to four values of the kernel's own choosing). Call it before tq_status_poll. Synchronises
+ * `stream`. No counterpart in the reference. */
+tq_status tq_status_detail(int32_t device, void* stream, int32_t* words, int32_t count);
 
 #ifdef __cplusplus
 }

@@ -73,6 +73,7 @@ SIGNATURES = {
                                         c_int32, c_int64, c_int64, c_double, c_int32, c_void_p]),
     "tq_transposed_workspace_bytes": (c_int32, [c_int32, c_int32, c_int64, c_int64, c_int64, c_int32, POINTER(c_size_t)]),
     "tq_transposed_passes": (c_int32, [c_int32, c_int32, c_int64, c_int64, c_int64, c_int32, POINTER(c_int32)]),
+    "tq_transposed_form": (c_int32, [c_int32, c_int32, c_int64, c_int64, c_int64, c_int32, POINTER(c_int32)]),
     "tq_softmax_transposed_launch": (c_int32, [c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_size_t, c_int32, c_void_p]),
     "tq_layer_norm_transposed_launch": (c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_double,
                                                   c_void_p, c_size_t, c_int32, c_void_p]),
@@ -96,6 +97,7 @@ SIGNATURES = {
     "tq_recipe_steps": (c_int64, [c_void_p]),
     "tq_recipe_run": (c_int32, [c_void_p, c_int32, c_void_p]),
     "tq_status_poll": (c_int32, [c_int32, c_void_p, POINTER(c_int32)]),
+    "tq_status_detail": (c_int32, [c_int32, c_void_p, POINTER(c_int32), c_int32]),
 }
 
 

@@ -114,6 +114,17 @@ bool slab_takes(tq_dtype dtype, long long batch, long long rows, long long cols)
 tq_status slab_normalize_launch(int kind, tq_dtype dtype, const void* in, void* out, const void* weight, const void* bias,
                                 long long batch, long long rows, long long cols, float eps, cudaStream_t stream, bool* handled);
 
+// panelnorm.cu: the same result from 1 read + 1 write of HBM for tensors far larger than L2 — one
+// persistent kernel walks panels of columns (512 bytes of every row) that stay in L2 between their
+// statistics visit and their normalising visit. Sets `*handled` and launches when panel_takes() the
+// shape and the pointers are 16-byte aligned; otherwise launches nothing. `workspace` must hold
+// panel_workspace_bytes (partials, final statistics, panel counters, flags and the work queue).
+bool panel_takes(tq_dtype dtype, long long batch, long long rows, long long cols);
+size_t panel_workspace_bytes(tq_dtype dtype, long long batch, long long rows, long long cols);
+tq_status panel_normalize_launch(int kind, tq_dtype dtype, const void* in, void* out, const void* weight, const void* bias,
+                                 long long batch, long long rows, long long cols, float eps, void* workspace, size_t workspace_bytes,
+                                 int32_t device, cudaStream_t stream, bool* handled);
+
 }  // namespace tq
 
 // ---------------------------------------------------------------------------------------------

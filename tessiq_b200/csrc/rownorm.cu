@@ -611,12 +611,16 @@ tq_status transposed_launch(int kind, tq_dtype dtype, const void* in, const void
   if (tq_status s = tq::use_device(device)) return s;
   const size_t stats = stats_bytes(batch, cols);
   const size_t reduce_scratch = tq::slice_stats_workspace_bytes(kind, dtype, batch, rows, cols, device);
-  TQ_REQUIRE(workspace != nullptr && workspace_bytes >= stats + reduce_scratch && tq::aligned_to(workspace, 16), TQ_INVALID_ARGUMENT,
-             "this call needs %zu bytes of 16-byte-aligned scratch and was given %zu", stats + reduce_scratch, workspace_bytes);
+  const size_t need = std::max(stats + reduce_scratch, tq::panel_workspace_bytes(dtype, batch, rows, cols));
+  TQ_REQUIRE(workspace != nullptr && workspace_bytes >= need && tq::aligned_to(workspace, 16), TQ_INVALID_ARGUMENT,
+             "this call needs %zu bytes of 16-byte-aligned scratch and was given %zu", need, workspace_bytes);
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
   unsigned char* scratch = static_cast<unsigned char*>(workspace);
   bool handled = false;
   if (tq_status s = tq::slab_normalize_launch(kind, dtype, in, out, weight, bias, batch, rows, cols, static_cast<float>(eps), cuda_stream, &handled)) return s;
+  if (handled) return TQ_OK;
+  if (tq_status s = tq::panel_normalize_launch(kind, dtype, in, out, weight, bias, batch, rows, cols, static_cast<float>(eps), workspace,
+                                               workspace_bytes, device, cuda_stream, &handled)) return s;
   if (handled) return TQ_OK;
   if (tq_status s = tq::slice_stats_launch(kind, dtype, in, scratch, batch, rows, cols, scratch + stats, reduce_scratch, device, cuda_stream)) return s;
   return tq::transpose_normalize_launch(kind, dtype, in, out, scratch, weight, bias, batch, rows, cols, static_cast<float>(eps), cuda_stream);
@@ -631,7 +635,8 @@ tq_status tq_transposed_workspace_bytes(int32_t layer_norm, tq_dtype dtype, int6
   TQ_REQUIRE(tq::dtype_size(dtype) != 0, TQ_INVALID_ARGUMENT, "unknown element type %d", dtype);
   *bytes = 0;
   if (batch == 0 || cols == 0 || rows == 0) return TQ_OK;
-  *bytes = stats_bytes(batch, cols) + tq::slice_stats_workspace_bytes(layer_norm ? 1 : 0, dtype, batch, rows, cols, device);
+  *bytes = std::max(stats_bytes(batch, cols) + tq::slice_stats_workspace_bytes(layer_norm ? 1 : 0, dtype, batch, rows, cols, device),
+                    tq::panel_workspace_bytes(dtype, batch, rows, cols));
   return TQ_OK;
 }
 
@@ -643,6 +648,17 @@ tq_status tq_transposed_passes(int32_t layer_norm, tq_dtype dtype, int64_t batch
   TQ_REQUIRE(batch >= 0 && rows >= 0 && cols >= 0, TQ_INVALID_ARGUMENT, "negative extent");
   TQ_REQUIRE(tq::dtype_size(dtype) != 0, TQ_INVALID_ARGUMENT, "unknown element type %d", dtype);
   *passes = tq::slab_takes(dtype, batch, rows, cols) ? 2 : 3;
+  return TQ_OK;
+}
+
+tq_status tq_transposed_form(int32_t layer_norm, tq_dtype dtype, int64_t batch, int64_t rows, int64_t cols, int32_t device,
+                             int32_t* form) {
+  (void)layer_norm;
+  (void)device;
+  TQ_REQUIRE(form != nullptr, TQ_INVALID_ARGUMENT, "form out-pointer is null");
+  TQ_REQUIRE(batch >= 0 && rows >= 0 && cols >= 0, TQ_INVALID_ARGUMENT, "negative extent");
+  TQ_REQUIRE(tq::dtype_size(dtype) != 0, TQ_INVALID_ARGUMENT, "unknown element type %d", dtype);
+  *form = tq::slab_takes(dtype, batch, rows, cols) ? TQ_TRANSPOSED_SLAB : tq::panel_takes(dtype, batch, rows, cols) ? TQ_TRANSPOSED_PANELS : TQ_TRANSPOSED_THREE_PASS;
   return TQ_OK;
 }
 

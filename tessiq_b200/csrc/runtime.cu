@@ -211,4 +211,15 @@ tq_status tq_status_poll(int32_t device, void* stream, int32_t* device_status) {
   return TQ_OK;
 }
 
+tq_status tq_status_detail(int32_t device, void* stream, int32_t* words, int32_t count) {
+  TQ_REQUIRE(words != nullptr && count >= 0 && count <= 64, TQ_INVALID_ARGUMENT, "the status block holds 64 words");
+  if (tq_status s = tq::use_device(device)) return s;
+  int32_t* word = tq::device_status_word(device);
+  TQ_REQUIRE(word != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  TQ_CUDA(cudaMemcpyAsync(words, word, sizeof(int32_t) * count, cudaMemcpyDeviceToHost, cuda_stream));
+  TQ_CUDA(cudaStreamSynchronize(cuda_stream));
+  return TQ_OK;
+}
+
 }  // extern "C"

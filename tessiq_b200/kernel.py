@@ -341,6 +341,13 @@ def transposed_passes(kind: str, dtype: torch.dtype, batch: int, rows: int, cols
     return passes.value
 
 
+def transposed_form(kind: str, dtype: torch.dtype, batch: int, rows: int, cols: int, device: int = 0) -> str:
+    """The kernel tq_*_transposed_launch runs for this shape: "three-pass", "slab" or "panels"."""
+    form = ctypes.c_int32()
+    check(lib.tq_transposed_form(1 if kind == "layer_norm" else 0, dtype_code(dtype), batch, rows, cols, device, ctypes.byref(form)))
+    return ("three-pass", "slab", "panels")[form.value]
+
+
 def prefers_transposed(kind: str, dtype: torch.dtype, batch: int = 0, rows: int = 0, cols: int = 0) -> bool:
     """Whether op(x.transpose(-1, -2), -1) should take the in-place path rather than pack-then-rows
     (4 passes). Always when the shape takes the two-pass slab kernel. For the three-pass form,

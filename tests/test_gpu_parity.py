@@ -6,6 +6,7 @@ fp32 within rtol 1e-5 (atol 1e-5 * max|ref|); bf16/f16 within rtol 1e-2 (atol 1e
 sums against float64 within 1e-5 of sum|x| (reduction order differs from the oracle's).
 """
 
+import ctypes
 import math
 
 import numpy as np
@@ -710,6 +711,49 @@ def test_transposed_normalisations_from_a_column_slab(tq, dtype, shape):
     else:
         close16(got_softmax, ref_softmax)
         close16(got_norm, ref_norm)
+
+
+@pytest.mark.parametrize("shape", [(32768, 2048), (2, 16384, 2048), (4, 8192, 2176)])
+def test_transposed_normalisations_by_column_panels(tq, shape):
+    """f32 tensors of 256 MiB and more take the persistent kernel that walks panels of columns; the last
+    shape's columns are not a multiple of a panel's 128 and stay with the three-pass form."""
+    from tessiq_b200 import kernel as K
+
+    rows, cols = shape[-2], shape[-1]
+    batch = math.prod(shape[:-2])
+    assert K.transposed_form("softmax", torch.float32, batch, rows, cols) == ("panels" if cols % 128 == 0 else "three-pass")
+    assert K.transposed_form("softmax", torch.bfloat16, batch, rows, cols) == "three-pass"
+    assert K.transposed_form("layer_norm", torch.float32, 1, 8192, 512) == "slab"
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(*shape, generator=g) * 2 + 0.3
+    flat = x.view(-1, rows, cols)
+    flat[0, 7, 3] = float("nan")
+    flat[0, :, 5] = float("-inf")
+    flat[0, 100, 9] = float("inf")
+    flat[0, :, 11] = 1e30
+    flat[0, :, 13] = torch.linspace(-500.0, 500.0, rows)       # the running sum's reference point has to move, many times
+    flat[0, :, 14] = torch.linspace(500.0, -500.0, rows)       # ... or never
+    flat[0, :700, 15] = float("-inf")                          # a whole work item of -inf before the first finite value
+    flat[0, ::2, 17] = float("-inf")
+    flat[0, :, 19] = torch.where(torch.arange(rows) % 97 == 0, 80.0, -3.0)
+    xd = dev(x)
+    view, view_gpu = x.transpose(-1, -2), xd.transpose(-1, -2)
+    got = tq.softmax(view_gpu, -1).cpu()
+    torch.testing.assert_close(got, tessiq0.softmax(view, -1), rtol=1e-5, atol=1e-7, equal_nan=True)
+    again = tq.softmax(view_gpu, -1).cpu()                     # whichever CTA folds, the result is the same
+    assert torch.equal(torch.nan_to_num(again, nan=7.0), torch.nan_to_num(got, nan=7.0))
+    del got, again
+    y = torch.randn(*shape, generator=g) * 3 - 1.5
+    w = 1 + torch.randn(rows, generator=g) * 0.1
+    b = torch.randn(rows, generator=g) * 0.1
+    yd = dev(y)
+    close32(tq.layer_norm(yd.transpose(-1, -2), [rows], dev(w), dev(b), 1e-5),
+            tessiq0.native_layer_norm(y.transpose(-1, -2), [rows], w, b, 1e-5)[0], rtol=1e-5, scale=4e-6)
+    close32(tq.layer_norm(yd.transpose(-1, -2), [rows]), tessiq0.native_layer_norm(y.transpose(-1, -2), [rows], None, None, 1e-5)[0],
+            rtol=1e-5, scale=4e-6)
+    status = ctypes.c_int32(-1)
+    K.check(K.lib.tq_status_poll(0, None, ctypes.byref(status)))
+    assert status.value == 0
 
 
 def test_column_slab_special_columns(tq):
