@@ -124,11 +124,12 @@ class ClockSampler:
 class Step:
     """The 26 operations with every output preallocated, so a step is launches only."""
 
-    def __init__(self, device: int):
+    def __init__(self, device: int, rows: int | None = None, pinned: bool = True):
         import torch
 
         from tessiq_b200 import kernel as K
 
+        ROWS = self.rows = rows if rows is not None else globals()["ROWS"]
         self.torch, self.K, self.device = torch, K, device
         self.launches = 0
         g = torch.Generator().manual_seed(1234 + device)
@@ -137,7 +138,7 @@ class Step:
         beta = torch.randn(WIDTH, generator=g) * 0.02
         gamma_t = 1 + torch.randn(ROWS, generator=g) * 0.02
         beta_t = torch.randn(ROWS, generator=g) * 0.02
-        self.host_x = x.pin_memory()
+        self.host_x = x.pin_memory() if pinned else x
         dev = f"cuda:{device}"
         self.sets = {}
         for name, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
@@ -162,6 +163,7 @@ class Step:
 
     def operations(self, name: str, stream: int):
         """(label, launch closure) for the 13 operations of one element type."""
+        ROWS = self.rows
         K, s = self.K, self.sets[name]
         x = s["x"]
         ops = []
@@ -186,8 +188,17 @@ class Step:
         return ops
 
     def launches_per_step(self) -> int:
-        # every operation is one kernel, except the two statistics-then-transpose pairs per type
-        return 2 * (13 + 2)
+        """Kernels of this library per step: every operation is one launch, except softmax / LayerNorm
+        over the transposed view where they take two (statistics, then the transposing normalise; or
+        pack, then rows) — the f32 pair is one launch (+ a memset of its flags) when the persistent
+        panel kernel takes the shape."""
+        K, count = self.K, 0
+        for name, s in self.sets.items():
+            count += 13
+            for kind in ("softmax", "layer_norm"):
+                if K.transposed_form(kind, s["x"].dtype, 1, self.rows, WIDTH) != "panels":
+                    count += 1
+        return count
 
     def run(self, stream: int, time_dominant: bool = False) -> None:
         torch = self.torch
@@ -213,6 +224,7 @@ def run_ours(args) -> dict:
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: tessiq_b200 has no CPU path")
     torch.cuda.set_device(local)
+    host_binding = bind_to_gpu_cpus(local)
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: one JSON line only
@@ -222,6 +234,13 @@ def run_ours(args) -> dict:
 
     # Parity first (rank 0; the other ranks run the same kernels): a mismatch stops the run before anything is timed.
     parity = parity_gate(local) if rank == 0 else None
+    if parity is not None and not args.no_extra:
+        extras_checked = parity_gate_extras(local)
+        parity["checks"] += len(extras_checked)
+        parity["configs"] = ["config2 (26 operations)"] + extras_checked
+    reduce_parity = parity_gate_global_reduce(rank, world, local)   # every rank: the all-reduce needs them all
+    if parity is not None:
+        parity["config5c_global_reductions"] = reduce_parity
 
     step = Step(local)
     stream = torch.cuda.Stream(device=local)
@@ -258,14 +277,7 @@ def run_ours(args) -> dict:
             graph.replay()
         stop.record(stream)
         stream.synchronize()
-    # the dominant kernel, timed alone on the launch stream inside eager steps of the same work
-    with torch.cuda.stream(stream):
-        step.events.clear()
-        for _ in range(args.steps):
-            step.run(raw, time_dominant=True)
-        stream.synchronize()
     seconds = start.elapsed_time(stop) * 1e-3
-    dominant_ms = statistics.mean(a.elapsed_time(b) for a, b in step.events)
     barrier()
 
     # ---- per-operation device times (one event pair per operation, eager) ----------------
@@ -282,6 +294,17 @@ def run_ours(args) -> dict:
                 stream.synchronize()
                 us = a.elapsed_time(b) / 5 * 1e3
                 per_op[f"{label}_{name}"] = {"us": round(us, 1), "gbs": round(step.bytes[name][label] / us / 1e3, 1)}
+    # the dominant operation = the one that takes longest; it is then timed launch by launch with CUDA
+    # events on the launch stream inside eager steps of the whole workload (its neighbours before and after it)
+    slowest = max(per_op, key=lambda key: per_op[key]["us"])
+    step.dominant = (slowest.rsplit("_", 1)[1], slowest.rsplit("_", 1)[0])
+    with torch.cuda.stream(stream):
+        step.events.clear()
+        for _ in range(args.steps):
+            step.run(raw, time_dominant=True)
+        stream.synchronize()
+    dominant_ms = statistics.mean(a.elapsed_time(b) for a, b in step.events)
+    barrier()
 
     # ---- e2e: host buffers in, host buffers out, through the public API --------------------
     host_out = {}
@@ -367,6 +390,9 @@ def run_ours(args) -> dict:
         extra[f"config5c_global_{op}_f32"] = {"us": round(us.item(), 1), "gbs": round(world * x32.numel() * 4 / us.item() / 1e3, 1),
                                               "collective": "none" if world == 1 else f"all-reduce of per-GPU partials over {world} ranks"}
 
+    if world > 1 and not args.no_extra:
+        extra["strong"] = strong_scaling(rank, world, local, stream, step, seconds / args.steps, extra)
+
     times = torch.tensor([seconds, e2e_seconds, dominant_ms], dtype=torch.float64, device=f"cuda:{local}")
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -377,6 +403,7 @@ def run_ours(args) -> dict:
     dom_name, dom_label = step.dominant
     dom_bytes = step.bytes[dom_name][dom_label]
     achieved = dom_bytes / (dominant_ms * 1e-3) / 1e9
+    step_seconds = seconds / args.steps
     line = {
         "metric": METRIC, "value": round(world * step.step_bytes * args.steps / seconds / 1e9, 1), "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -387,13 +414,17 @@ def run_ours(args) -> dict:
                    "rows_per_gpu": ROWS, "width": WIDTH, "parallelism": f"rows sharded over {world} GPU(s), no collective",
                    "l2": "inputs (768 MiB) exceed L2; no flush", "timing": "CUDA-graph replay, CUDA events on the replay stream"},
         "algorithmic_bytes_per_step": step.step_bytes,
-        "roofline": {"bound": "hbm", "kernel": f"row_cluster_kernel<float, softmax> ({dom_label}_{dom_name})",
+        # the operation that takes longest in the step (by this run's own per-operation times, `kernels` below)
+        "roofline": {"bound": "hbm", "kernel": f"{kernel_name(step, dom_name, dom_label)} ({dom_label}_{dom_name})",
                      "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                     "peak_kind": f"of {peak_kind} copy bandwidth", "traffic": DOMINANT_TRAFFIC_BYTES,
-                     "algorithmic_bytes_per_launch": dom_bytes, "us_per_launch": round(dominant_ms * 1e3, 1)},
+                     "peak_kind": f"of {peak_kind} copy bandwidth", "traffic": NCU_TRAFFIC_BYTES.get(f"{dom_label}_{dom_name}"),
+                     "algorithmic_bytes_per_launch": dom_bytes, "us_per_launch": round(dominant_ms * 1e3, 1),
+                     "share_of_step": round(dominant_ms * 1e-3 / step_seconds, 4),
+                     "step_frac": round(step.step_bytes / step_seconds / 1e9 / peak, 4)},
         "e2e": {"value": round(world * step.step_bytes * e2e_steps / e2e_seconds / 1e9, 1), "unit": UNIT,
                 "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "ms_per_step": round(e2e_seconds / e2e_steps * 1e3, 2),
-                "steps": e2e_steps},
+                "steps": e2e_steps, "pcie_gbs_per_rank": round((h2d_bytes + d2h_bytes) * e2e_steps / e2e_seconds / 1e9, 1),
+                "host_binding": host_binding},
         "gpu_launches": step.launches_per_step() * args.steps,
         "clocks": clock_summary,
         "kernels": per_op,
@@ -406,6 +437,105 @@ def run_ours(args) -> dict:
     if world > 1:
         dist.destroy_process_group()
     return line if rank == 0 else {}
+
+
+def strong_scaling(rank: int, world: int, device: int, stream, full_step, full_step_seconds: float, extra: dict) -> dict:
+    """The same total problem split over the ranks (strong scaling), next to the weak-scaling line:
+    config 2's step on 32768 / N rows per rank, config 3's GEMM on 8192 / N rows of A (B and the bias
+    replicated), config 4's decoder block on 64 / N sequences. Each is timed on every rank; the time
+    of the sharded problem is the max over ranks and the speed-up is against the full problem timed
+    in this same run on the same GPUs (per rank: the weak-scaling numbers above)."""
+    import torch
+    import torch.distributed as dist
+
+    from tessiq_b200 import ops
+
+    dev = f"cuda:{device}"
+    raw = stream.cuda_stream
+    out = {}
+
+    def slowest(seconds: float) -> float:
+        t = torch.tensor([seconds], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    # config 2: this rank's rows of the 32768
+    shard = Step(device, rows=ROWS // world, pinned=False)
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            shard.run(raw)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            shard.run(raw)
+        graph.replay()
+        stream.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(10):
+            graph.replay()
+        b.record(stream)
+        stream.synchronize()
+    sharded = slowest(a.elapsed_time(b) / 10 * 1e-3)
+    out["config2_step"] = {"rows_per_gpu": ROWS // world, "us": round(sharded * 1e6, 1), "full_problem_us": round(full_step_seconds * 1e6, 1),
+                           "speedup_vs_n1": round(full_step_seconds / sharded, 2)}
+    del shard, graph
+    torch.cuda.empty_cache()
+
+    def timed(fn, iters):
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                fn()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(iters):
+                fn()
+            b.record(stream)
+            stream.synchronize()
+        return a.elapsed_time(b) / iters * 1e-3
+
+    # config 3: rows of A
+    g = torch.Generator().manual_seed(3)
+    a_full = (torch.randn(8192, 4096, generator=g) * 0.02).bfloat16()
+    b_mat = (torch.randn(4096, 16384, generator=g) * 0.02).bfloat16().to(dev)
+    bias = (torch.randn(16384, generator=g) * 0.02).bfloat16().to(dev)
+    rows = 8192 // world
+    a_mine = a_full[rank * rows:(rank + 1) * rows].to(dev)
+    sharded = slowest(timed(lambda: ops.matmul_bias_gelu_tanh(a_mine, b_mat, bias), 20))
+    full_us = extra.get("config3_gemm_bias_gelu_bf16", {}).get("us")
+    out["config3_gemm_bias_gelu_bf16"] = {"rows_of_a_per_gpu": rows, "us": round(sharded * 1e6, 1), "full_problem_us": full_us,
+                                          "speedup_vs_n1": round(full_us / (sharded * 1e6), 2) if full_us else None,
+                                          "tflops_all_gpus": round(2 * 8192 * 4096 * 16384 / sharded / 1e12, 1)}
+    del a_full, a_mine, b_mat, bias
+    torch.cuda.empty_cache()
+
+    # config 4: sequences of the batch of 64
+    block = decoder_block(dev, stream, batch=64 // world)
+    sharded = slowest(block["ms_per_call"] * 1e-3)
+    full_ms = extra.get("config4_decoder_block_bf16", {}).get("ms_per_call")
+    out["config4_decoder_block_bf16"] = {"sequences_per_gpu": 64 // world, "ms_per_call": round(sharded * 1e3, 3), "full_problem_ms": full_ms,
+                                         "speedup_vs_n1": round(full_ms / (sharded * 1e3), 2) if full_ms else None,
+                                         "tokens_per_s_all_gpus": round(64 * 1024 / sharded)}
+    return out
+
+
+def bind_to_gpu_cpus(device: int) -> str:
+    """Keeps this rank's host threads (and so its pinned buffers, first touched after this call) on
+    the CPUs NVML lists as local to its GPU. Returns what it did, for the e2e entry of the line."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(device)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cpus = {64 * i + bit for i, word in enumerate(words) for bit in range(64) if (word >> bit) & 1}
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return "the GPU's local CPUs are outside this process's CPU set; left unbound"
+        os.sched_setaffinity(0, allowed)
+        return f"bound to the {len(allowed)} CPUs NVML lists as local to GPU {device}"
+    except Exception as error:   # no NVML, or no permission: the run goes on unbound
+        return f"unbound ({type(error).__name__})"
 
 
 def other_configs(device: int, stream) -> dict:
@@ -494,7 +624,7 @@ def other_configs(device: int, stream) -> dict:
     return out
 
 
-def decoder_block(dev: str, stream) -> dict:
+def decoder_block(dev: str, stream, batch: int = 64) -> dict:
     """benchmark config 4, the batch of 64 per GPU (weak scaling like the rest of this file):
     LayerNorm + QKV GEMM + causal softmax attention + output projection + GELU MLP + residual
     adds, d_model 768, 12 heads, MLP 3072, 1024 tokens, bf16 inference, compiled by this repo's
@@ -504,7 +634,7 @@ def decoder_block(dev: str, stream) -> dict:
 
     from tessiq_b200.backend import compile_graph
 
-    d, heads, tokens, batch = 768, 12, 1024, 64
+    d, heads, tokens = 768, 12, 1024
 
     class Block(torch.nn.Module):
         def __init__(self):
@@ -549,7 +679,7 @@ def decoder_block(dev: str, stream) -> dict:
         b.record(stream)
         stream.synchronize()
     seconds = a.elapsed_time(b) / 5 * 1e-3
-    flop = 1_133_871_366_144  # dense flop of the six GEMMs per call; causal masking not discounted
+    flop = 1_133_871_366_144 * batch // 64  # dense flop of the six GEMMs per call; causal masking not discounted
     recipes = getattr(holder.get("fn"), "recipes", None) or []
     return {"ms_per_call": round(seconds * 1e3, 3), "tokens_per_s": round(batch * tokens / seconds), "tflops": round(flop / seconds / 1e12, 1),
             "steps": recipes[0].counts() if recipes else None, "interpreted": recipes[0].interpreted if recipes else None}
@@ -697,11 +827,32 @@ def run_sweep(args) -> dict:
             "peak_hbm_gbs": peak, "peak_kind": peak_kind, "rows": rows}
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per full launch, from one
-# ncu capture at 16384 rows scaled by two (profiles/softmax_rows_f32_row_cluster_kernel.md); the
-# traffic grows in proportion to the rows. Below the 1 073 741 824 algorithmic bytes only because
-# the tail of the result is still in L2 when the kernel ends.
-DOMINANT_TRAFFIC_BYTES = 964180992
+# dram__bytes_read.sum + dram__bytes_write.sum per full-size launch of the operations that can be the
+# longest of the step, each from one ncu capture on a reduced case (half the rows or half the columns)
+# scaled by two — the traffic of these streaming kernels grows in proportion (summaries under profiles/).
+# softmax_rows stays just below its 1 073 741 824 algorithmic bytes because the tail of the result is
+# still in L2 when the kernel ends; the transposed-view pair reads its input twice (the second visit
+# misses L2 at the setting that measured fastest), so 1.5x the algorithmic bytes.
+NCU_TRAFFIC_BYTES = {
+    "softmax_rows_f32": 964180992,
+    "softmax_cols_f32": None,
+    "layer_norm_cols_f32": None,
+}
+
+
+def kernel_name(step, name: str, label: str) -> str:
+    K = step.K
+    dtype = step.sets[name]["x"].dtype
+    if label in ("softmax_cols", "layer_norm_cols"):
+        kind = "softmax" if label == "softmax_cols" else "layer_norm"
+        form = K.transposed_form(kind, dtype, 1, step.rows, WIDTH)
+        if kind == "softmax" and not K.prefers_transposed(kind, dtype, 1, step.rows, WIDTH):
+            return "pack_transpose_blocks + row_cluster_kernel<softmax>"
+        return {"panels": f"panel_normalize_kernel<{kind}>", "slab": f"slab_normalize_kernel<{kind}>",
+                "three-pass": f"reduce_columns<statistics> + transpose_normalize_kernel<{kind}>"}[form]
+    if label.endswith("_rows"):
+        return {"softmax_rows": "row_cluster_kernel<softmax>", "layer_norm_rows": "row_cluster_kernel<LayerNorm>"}.get(label, "reduce_warp_per_slice")
+    return "pack_transpose_blocks" if label == "pack" else "reduce_columns"
 
 
 # ---------------------------------------------------------------------------------------------
@@ -749,6 +900,89 @@ def parity_gate(device: int, sample_rows: int = 512) -> dict:
     return {"rows": sample_rows, "checks": len(labels), "ok": True}
 
 
+def parity_gate_extras(device: int) -> list[str]:
+    """The other configs' kernels, on small cases, against the CPU device's results, before they are
+    timed: config 1's chain (1e-5), config 3's A @ B + bias -> GELU(tanh) on 64 rows of A, config 4's
+    causal attention on 2 heads, config 5's six-op chain (1e-2 of the largest value for bf16 results).
+    Raises on a mismatch; returns the names of what it checked."""
+    import torch
+
+    from oracle import tessiq0
+    from tessiq_b200 import ops
+    from tessiq_b200.kernel import FusedKernel
+
+    dev = f"cuda:{device}"
+    g = torch.Generator().manual_seed(99)
+    checked = []
+
+    def close16(got, ref, what):
+        got, ref = got.cpu().float(), ref.float()
+        if not torch.allclose(got, ref, rtol=1e-2, atol=1e-2 * max(ref.abs().max().item(), 1e-30)):
+            raise SystemExit(f"parity gate failed on {what}: the GPU result differs from the CPU device's; nothing was timed")
+        checked.append(what)
+
+    x, b = torch.randn(256, 4096, generator=g), torch.randn(4096, generator=g) * 0.02
+    chain = FusedKernel("in x f32 same\nin b f32 cycled\nv0 = add x b\nv1 = gelu_tanh v0\nv2 = sigmoid x\nv3 = mul v1 v2\n"
+                        "v4 = mul x 0.5\nv5 = sub v3 v4\nout v5 f32\n")
+    y = torch.empty(256, 4096, device=dev)
+    chain.launch([x.to(dev), b.to(dev)], y, stream=None)
+    ref = tessiq0.chain_gelu_sigmoid(x, b)
+    if not torch.allclose(y.cpu(), ref, rtol=1e-5, atol=1e-5 * ref.abs().max().item()):
+        raise SystemExit("parity gate failed on config 1's fused chain; nothing was timed")
+    checked.append("config1_fused_chain_f32")
+
+    a = (torch.randn(64, 4096, generator=g) * 0.02).bfloat16()
+    w = (torch.randn(4096, 16384, generator=g) * 0.02).bfloat16()
+    bias = (torch.randn(16384, generator=g) * 0.02).bfloat16()
+    close16(ops.matmul_bias_gelu_tanh(a.to(dev), w.to(dev), bias.to(dev)), tessiq0.matmul_bias_gelu_tanh(a, w, bias), "config3_gemm_bias_gelu_bf16")
+
+    qkv = torch.randn(1, 1024, 3 * 128, generator=g).bfloat16()
+    q, k, v = (z.view(1, 1024, 2, 64).transpose(1, 2) for z in qkv.split(128, dim=-1))
+    qd, kd, vd = (z.view(1, 1024, 2, 64).transpose(1, 2) for z in qkv.to(dev).split(128, dim=-1))
+    close16(ops.attention(qd, kd, vd, None, True), tessiq0.attention(q, k, v, 0.125, True), "config4_causal_attention_bf16")
+
+    p, r = torch.rand(1 << 16, generator=g) * 2 - 1, torch.rand(1 << 16, generator=g) * 2 - 1
+    six = FusedKernel("in a f32 same\nin b f32 same\nt0 = add a b\nt1 = exp t0\nt2 = mul t1 b\nt3 = tanh t2\nc = gt a 0\n"
+                      "w = where c t3 a\ny = cast w bf16\nout y bf16\n")
+    out = torch.empty(1 << 16, dtype=torch.bfloat16, device=dev)
+    six.launch([p.to(dev), r.to(dev)], out, stream=None)
+    close16(out, tessiq0.chain_six_ops(p, r, torch.bfloat16), "config5_six_op_chain_f32_to_bf16")
+    torch.cuda.synchronize()
+    return checked
+
+
+def parity_gate_global_reduce(rank: int, world: int, device: int) -> dict:
+    """config 5c across ranks: every rank holds 2^22 seeded elements (one rank's part carries a NaN for
+    the amax check), sharding.global_reduce combines them, and every rank rebuilds the whole tensor on
+    the CPU and compares: sum against 1e-5 of the sum of magnitudes, amax / amin / argmax exactly.
+    Raises on a mismatch."""
+    import torch
+
+    from tessiq_b200 import sharding
+
+    n = 1 << 22
+    parts = []
+    for r in range(world):
+        part = torch.rand(n, generator=torch.Generator().manual_seed(500 + r)) * 2 - 1
+        parts.append(part)
+    whole = torch.cat(parts)
+    mine = parts[rank].to(f"cuda:{device}")
+    with_nan = parts[rank].clone()
+    if rank == world - 1:
+        with_nan[12345] = float("nan")
+    whole_nan = whole.clone()
+    whole_nan[(world - 1) * n + 12345] = float("nan")
+    got = {op: sharding.global_reduce(op, mine, offset=rank * n, total=world * n).cpu() for op in ("sum", "amax", "amin", "argmax")}
+    got_nan = sharding.global_reduce("amax", with_nan.to(f"cuda:{device}"), offset=rank * n, total=world * n).cpu()
+    torch.cuda.synchronize()
+    ok = (abs(got["sum"].double().item() - whole.double().sum().item()) <= 1e-5 * whole.abs().sum().item()
+          and got["amax"].item() == whole.amax().item() and got["amin"].item() == whole.amin().item()
+          and got["argmax"].item() == whole.argmax().item() and torch.isnan(got_nan).item() and torch.isnan(whole_nan.amax()).item())
+    if not ok:
+        raise SystemExit(f"parity gate failed on the global reductions over {world} ranks (rank {rank}); nothing was timed")
+    return {"ranks": world, "elements_per_rank": n, "checks": ["sum", "amax", "amin", "argmax", "amax with a NaN on the last rank"], "ok": True}
+
+
 def cpu_step(x32, gamma, beta, gamma_t, beta_t):
     """The 26 operations as the reference's CPU device runs them: one ATen CPU kernel per node."""
     import torch
@@ -779,25 +1013,72 @@ def use_all_host_threads() -> int:
 
 
 def cpu_baseline(sample_rows: int, repeats: int) -> dict:
-    import torch
+    """The CPU baseline beside our line: the reference arm of this file, run as a process of its own
+    (the reference registers the `tessiq` device and operator namespace that tessiq_b200 mirrors, so
+    the two cannot share an interpreter). Falls back to the in-process port if that process fails."""
+    try:
+        result = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", str(repeats), "--warmup", "1"],
+                                capture_output=True, text=True, timeout=600, cwd=str(ROOT),
+                                env={k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "OMP_NUM_THREADS")})
+        line = json.loads(result.stdout.strip().splitlines()[-1])
+        baseline = dict(line["cpu_baseline"])
+        baseline["fair_cpu"] = line.get("cpu_port")
+        baseline["ms_per_step"] = line.get("ms_per_step")
+        baseline["host_cpus"] = os.cpu_count()
+        return baseline
+    except Exception as error:   # the subprocess could not run: time the port here
+        import torch
 
-    use_all_host_threads()
-    g = torch.Generator().manual_seed(1234)
-    x = torch.randn(sample_rows, WIDTH, generator=g)
-    gamma, beta = 1 + torch.randn(WIDTH, generator=g) * 0.02, torch.randn(WIDTH, generator=g) * 0.02
-    gamma_t, beta_t = 1 + torch.randn(sample_rows, generator=g) * 0.02, torch.randn(sample_rows, generator=g) * 0.02
-    nbytes = sum(sum(algorithmic_bytes(sample_rows, WIDTH, size).values()) for size in (4, 2))
-    cpu_step(x, gamma, beta, gamma_t, beta_t)
-    times = []
-    for _ in range(repeats):
-        t0 = time.perf_counter()
+        use_all_host_threads()
+        g = torch.Generator().manual_seed(1234)
+        x = torch.randn(sample_rows, WIDTH, generator=g)
+        gamma, beta = 1 + torch.randn(WIDTH, generator=g) * 0.02, torch.randn(WIDTH, generator=g) * 0.02
+        gamma_t, beta_t = 1 + torch.randn(sample_rows, generator=g) * 0.02, torch.randn(sample_rows, generator=g) * 0.02
+        nbytes = sum(sum(algorithmic_bytes(sample_rows, WIDTH, size).values()) for size in (4, 2))
         cpu_step(x, gamma, beta, gamma_t, beta_t)
-        times.append(time.perf_counter() - t0)
-    seconds = statistics.median(times)
-    return {"value": round(nbytes / seconds / 1e9, 2), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"the same 26 operations on {sample_rows} of the {ROWS} rows (x[{sample_rows},{WIDTH}]), median of {repeats}; "
-                      "PyTorch CPU kernels called one operator per node, as the reference's tessiq:0 device does",
-            "seconds_per_sample": round(seconds, 3), "host_cpus": os.cpu_count()}
+        times = []
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            cpu_step(x, gamma, beta, gamma_t, beta_t)
+            times.append(time.perf_counter() - t0)
+        seconds = statistics.median(times)
+        return {"value": round(nbytes / seconds / 1e9, 2), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                "sample": f"the same 26 operations on {sample_rows} of the {ROWS} rows, median of {repeats}; PyTorch CPU kernels, one operator per "
+                          f"node, as the reference's tessiq:0 device does (the reference arm's own process failed: {type(error).__name__})",
+                "seconds_per_sample": round(seconds, 3), "host_cpus": os.cpu_count()}
+
+
+def reference_device_step(torch, x_f32, gamma, beta, gamma_t, beta_t):
+    """The 26 operations on the reference's own CPU device: eager, every operand on `tessiq:0`, every
+    operator through the device's registrations and its boxed fallback
+    (csrc/tessiq/torch/ops.cpp:323-325,367-370). Results stay on the device."""
+    import torch.nn.functional as F
+
+    results = []
+    for dtype in (torch.float32, torch.bfloat16):
+        x = x_f32.to(dtype)
+        g, b, gt, bt = (t.to(dtype) for t in (gamma, beta, gamma_t, beta_t))
+        for view, width, gg, bb in ((x, x.shape[1], g, b), (x.t(), x.shape[0], gt, bt)):
+            results += [view.sum(-1), view.mean(-1), view.amax(-1), view.argmax(-1), torch.softmax(view, -1),
+                        F.layer_norm(view, (width,), gg, bb, 1e-5)]
+        results.append(x.t().contiguous())
+    return results
+
+
+def load_reference():
+    """The reference package built by oracle/build_ref.sh (oracle/_ref travels with the repository's
+    built files), or None with the reason. Only the CPU-baseline legs call this."""
+    built = ROOT / "oracle" / "_ref"
+    if not list(built.glob("tessiq/_C*.so")):
+        return None, "oracle/_ref holds no build of the reference (oracle/build_ref.sh makes one)"
+    sys.path.insert(0, str(built))
+    try:
+        import tessiq   # noqa: PLC0415
+        return tessiq, ""
+    except Exception as error:   # another interpreter or torch than the build's
+        return None, f"the reference build does not load here: {type(error).__name__}: {error}"
+    finally:
+        sys.path.pop(0)
 
 
 def run_reference(args) -> dict:
@@ -813,15 +1094,31 @@ def run_reference(args) -> dict:
     gamma, beta = 1 + torch.randn(WIDTH, generator=g) * 0.02, torch.randn(WIDTH, generator=g) * 0.02
     gamma_t, beta_t = 1 + torch.randn(sample_rows, generator=g) * 0.02, torch.randn(sample_rows, generator=g) * 0.02
     nbytes = sum(sum(algorithmic_bytes(sample_rows, WIDTH, size).values()) for size in (4, 2))
-    for _ in range(max(args.warmup, 1)):
-        cpu_step(x, gamma, beta, gamma_t, beta_t)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu_step(x, gamma, beta, gamma_t, beta_t)
-    seconds = time.perf_counter() - t0
+
+    def timed(step, warmup, steps):
+        for _ in range(max(warmup, 1)):
+            step()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        return time.perf_counter() - t0
+
+    # the "fair CPU" line: the same PyTorch CPU kernels without the device's per-operator copies
+    port_seconds = timed(lambda: cpu_step(x, gamma, beta, gamma_t, beta_t), args.warmup, args.steps)
+    port = {"value": round(nbytes * args.steps / port_seconds / 1e9, 2), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": "the oracle port: PyTorch CPU kernels, one operator per node, on host tensors (no device copies)"}
+    tessiq, why_not = load_reference()
+    if tessiq is not None:
+        on_device = [t.to("tessiq:0") for t in (x, gamma, beta, gamma_t, beta_t)]
+        seconds = timed(lambda: reference_device_step(torch, *on_device), args.warmup, args.steps)
+        kind = "reference"
+        sample = (f"each step is the 26 operations on {sample_rows} of the {ROWS} rows, eager on the reference's own CPU device tessiq:0 "
+                  f"(reference {tessiq.__version__} built by oracle/build_ref.sh; operands resident on the device)")
+    else:
+        seconds, kind = port_seconds, "port"
+        sample = (f"each step is the 26 operations on {sample_rows} of the {ROWS} rows; PyTorch CPU kernels, one operator per node, "
+                  f"which is what the reference's CPU device tessiq:0 runs (csrc/tessiq/torch/ops.cpp:367-370); {why_not}")
     value = round(nbytes * args.steps / seconds / 1e9, 2)
-    sample = (f"each step is the 26 operations on {sample_rows} of the {ROWS} rows; PyTorch CPU kernels, one operator per node, "
-              "which is what the reference's CPU device tessiq:0 runs (csrc/tessiq/torch/ops.cpp:367-370)")
     return {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
         "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(seconds / args.steps * 1e3, 2),
@@ -830,7 +1127,8 @@ def run_reference(args) -> dict:
                                "f32 and bf16, contiguous and on the transposed view, plus the pack alone",
                    "rows_per_gpu": ROWS, "width": WIDTH, "sample_rows": sample_rows,
                    "timing": "host wall clock; each step runs the 26 operations on a bounded sample of the rows"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind, "sample": sample},
+        "cpu_port": port,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }

@@ -495,6 +495,52 @@ tq_status tq_recipe_run(const tq_recipe* recipe, int32_t device, void* stream);
  * `stream` first. */
 tq_status tq_status_poll(int32_t device, void* stream, int32_t* device_status);
 
+/* ---- Global reductions over the GPUs of one box ------------------------------------------------
+ * The reference has no multi-GPU execution (one target device per recipe,
+ * python/tessiq/recipe.py:117-161); these entry points are what its recipes shard under: a reduction
+ * over every element of a tensor whose elements are split over several GPUs is, per GPU and on one
+ * stream, tq_reduce_partial_launch -> tq_allreduce_scalar -> tq_reduce_finish_launch.
+ *
+ * tq_comm: an NCCL communicator (NCCL is opened at run time; TQ_NOT_FOUND when libnccl.so.2 is not
+ * available). One process per GPU: one rank calls tq_comm_unique_id, hands the 128 bytes to the
+ * others by its own means, and every rank calls tq_comm_create with its GPU current-able. One process
+ * that drives several GPUs: tq_comm_create_all fills one communicator per listed device. */
+typedef struct tq_comm tq_comm;
+tq_status tq_comm_unique_id(void* id, size_t bytes);
+tq_status tq_comm_create(const void* id, size_t bytes, int32_t rank, int32_t world, int32_t device, tq_comm** comm);
+tq_status tq_comm_create_all(const int32_t* devices, int32_t count, tq_comm** comms);
+tq_status tq_comm_destroy(tq_comm* comm);
+int32_t tq_comm_rank(const tq_comm* comm);
+int32_t tq_comm_world(const tq_comm* comm);
+
+/* In-place all-reduce of `count` elements of `buffer` (device memory of the communicator's GPU) over
+ * the communicator's ranks, on `stream`: TQ_SUM, TQ_AMAX (maximum) or TQ_AMIN (minimum). */
+tq_status tq_allreduce_scalar(tq_comm* comm, void* buffer, int64_t count, tq_dtype dtype, tq_reduce_op op,
+                              int32_t device, void* stream);
+
+/* The local part: `count` packed elements of `in` (f32, f16 or bf16) reduced to a two-float partial
+ * at `partial` (8-byte aligned device memory): TQ_SUM / TQ_MEAN give {sum in f32, 0}; TQ_AMAX gives
+ * {maximum with a NaN replaced by -inf, 1 if a NaN was seen}, to be all-reduced with TQ_AMAX; TQ_AMIN
+ * gives {minimum with a NaN replaced by +inf, -1 if a NaN was seen}, to be all-reduced with TQ_AMIN.
+ * Scratch as for tq_reduce_launch over [1, count, 1] (tq_reduce_workspace_bytes). */
+tq_status tq_reduce_partial_launch(tq_reduce_op op, tq_dtype dtype, const void* in, void* partial, int64_t count,
+                                   void* workspace, size_t workspace_bytes, int32_t device, void* stream);
+
+/* The finish: the combined two-float partial becomes one element of `dtype` at `out`: the sum, the
+ * sum divided by `total_count` (TQ_MEAN), or the extreme — NaN when the flag word is not zero. */
+tq_status tq_reduce_finish_launch(tq_reduce_op op, tq_dtype dtype, const void* partial, void* out, int64_t total_count,
+                                  int32_t device, void* stream);
+
+/* A self-test of the give-up path: launches one warp that waits, for at most `polls` looks, on a
+ * barrier that cannot complete, and returns by itself. Afterwards tq_status_poll reports 0x53454c46
+ * ("SELF"). looks[0] = the looks the wait took (= polls); looks[1] = how long, in units of 1024
+ * clock cycles, one of the library's own bounded waits in the same launch then took to leave
+ * (it leaves at its first look at the launch's abort word, which it takes every 1024 polls), or -1 if
+ * it completed. Kernels
+ * launched afterwards are not affected: the abort word belongs to the launch. Synchronises `stream`.
+ * No counterpart in the reference. */
+tq_status tq_selftest_bounded_wait(int32_t device, void* stream, int32_t polls, int32_t* looks);
+
 /* The first `count` (<= 64) 32-bit words of the device's status block, without clearing it: word 0 is
  * what tq_status_poll returns, the words behind it say where the wait that gave up was (CTA, thread
  * and up to four values of the kernel's own choosing). Call it before tq_status_poll. Synchronises

@@ -107,6 +107,31 @@ def native_layer_norm(x, normalized_shape, weight, bias, eps):
     return torch.native_layer_norm(x, list(normalized_shape), weight, bias, eps)
 
 
+def layer_norm_compiled(x, normalized_shape, weight, bias, eps):
+    """(y, mean, rstd) as a COMPILED graph computes an f32 LayerNorm on `tessiq:0`: the reference's
+    decomposition table breaks `native_layer_norm` up (python/tessiq/decompositions.py:25-34) and its own
+    `var_mean` (decompositions.py:38-60) keeps the pieces in ATen — mean, subtract, square, sum, divide by
+    the count, add eps, rsqrt, subtract, three multiplies-and-adds — each its own CPU kernel call. The
+    result differs from the whole operator (native_layer_norm above, which is what EAGER `tessiq:0` runs)
+    in the last bits: 9.5e-7 absolute on the golden case. Bit-identical to the reference's compiled
+    output (tests/test_oracle_ref.py)."""
+    _cpu(x, weight, bias)
+    axes = list(range(x.dim() - len(list(normalized_shape)), x.dim()))
+    count = 1
+    for axis in axes:
+        count *= x.shape[axis]
+    mean = torch.mean(x, dim=axes, keepdim=True)
+    difference = torch.sub(x, mean)
+    total = torch.sum(torch.mul(difference, difference), dim=axes, keepdim=True)
+    rstd = torch.rsqrt(torch.add(torch.div(total, float(count)), eps))
+    y = torch.mul(torch.sub(x, mean), rstd)
+    if weight is not None:
+        y = torch.mul(y, weight)
+    if bias is not None:
+        y = torch.add(y, bias)
+    return y, mean, rstd
+
+
 def rms_norm(x, weight, eps):
     """csrc/custom_ops/rms_norm/rms_norm.cpp reference: x * rsqrt(mean(x^2, -1) + eps) * weight."""
     _cpu(x, weight)
@@ -117,6 +142,22 @@ def batch_norm_eval(x, weight, bias, running_mean, running_var, eps):
     """aten::native_batch_norm with training=False (csrc/tessiq/torch/eager_norm.cpp:219-220)."""
     _cpu(x)
     return torch.native_batch_norm(x, weight, bias, running_mean, running_var, False, 0.1, eps)[0]
+
+
+def batch_norm_eval_compiled(x, weight, bias, running_mean, running_var, eps):
+    """Eval BatchNorm as a COMPILED graph computes it on `tessiq:0`: decomposed into a subtract, a
+    reciprocal square root, a scale and a shift (python/tessiq/decompositions.py:29-33), in that order.
+    Bit-identical to the reference's compiled output (tests/test_oracle_ref.py); the whole operator
+    (batch_norm_eval above, the EAGER path) differs from it by 4.8e-7 absolute on the golden case."""
+    _cpu(x)
+    shape = [1, -1] + [1] * (x.dim() - 2)
+    inverse = torch.rsqrt(torch.add(running_var, eps))
+    y = torch.mul(torch.sub(x, running_mean.view(shape)), inverse.view(shape))
+    if weight is not None:
+        y = torch.mul(y, weight.view(shape))
+    if bias is not None:
+        y = torch.add(y, bias.view(shape))
+    return y
 
 
 def pack(x):

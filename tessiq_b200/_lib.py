@@ -98,6 +98,16 @@ SIGNATURES = {
     "tq_recipe_run": (c_int32, [c_void_p, c_int32, c_void_p]),
     "tq_status_poll": (c_int32, [c_int32, c_void_p, POINTER(c_int32)]),
     "tq_status_detail": (c_int32, [c_int32, c_void_p, POINTER(c_int32), c_int32]),
+    "tq_selftest_bounded_wait": (c_int32, [c_int32, c_void_p, c_int32, POINTER(c_int32)]),
+    "tq_comm_unique_id": (c_int32, [c_void_p, c_size_t]),
+    "tq_comm_create": (c_int32, [c_void_p, c_size_t, c_int32, c_int32, c_int32, POINTER(c_void_p)]),
+    "tq_comm_create_all": (c_int32, [POINTER(c_int32), c_int32, POINTER(c_void_p)]),
+    "tq_comm_destroy": (c_int32, [c_void_p]),
+    "tq_comm_rank": (c_int32, [c_void_p]),
+    "tq_comm_world": (c_int32, [c_void_p]),
+    "tq_allreduce_scalar": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32, c_void_p]),
+    "tq_reduce_partial_launch": (c_int32, [c_int32, c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_size_t, c_int32, c_void_p]),
+    "tq_reduce_finish_launch": (c_int32, [c_int32, c_int32, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
 }
 
 

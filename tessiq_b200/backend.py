@@ -37,7 +37,7 @@ from torch import fx
 from torch.utils._python_dispatch import _disable_current_modes
 
 from . import ops
-from .executor import GraphedRecipe, NativeRecipe, Recipe, Step
+from .executor import GraphedRecipe, NativeRecipe, Recipe, Step, note_torch_work
 from .kernel import DTYPE_NAMES, FusedKernel, classify_read
 from ._lib import Declined
 
@@ -405,13 +405,16 @@ def _attention_step(match: Attention) -> Step:
         folded = q.dim() == 3
         if folded:
             q, k, v = q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0)
+        # a reader that regroups the heads wants tokens outermost; a plain bmm reader wants [batch * heads, tokens, 64],
+        # which the kernel writes directly (a reshape of the token-major view would be a PyTorch copy)
+        token_major = regrouped or folded
         try:
-            out = ops.attention(q, k, v, scale, causal)
+            out = ops.attention(q, k, v, scale, causal, token_major)
         except Declined:  # a layout TMA cannot describe: packed copies can always be described
-            out = ops.attention(ops.contiguous(q), ops.contiguous(k), ops.contiguous(v), scale, causal)
+            out = ops.attention(ops.contiguous(q), ops.contiguous(k), ops.contiguous(v), scale, causal, token_major)
         if folded:
             return out[0]
-        return out if regrouped else out.reshape(-1, out.shape[2], out.shape[3])
+        return out if regrouped else out.view(-1, out.shape[2], out.shape[3])
 
     return Step("attention", match.anchor.name, run, names)
 
@@ -423,6 +426,12 @@ def _sdpa_step(node: fx.Node) -> Step | None:
     args = list(node.args)
     q, k, v = args[:3]
     if bias_at is not None and len(args) > bias_at and args[bias_at] is not None:
+        return None
+    # a mask or bias passed by keyword, or any keyword this rewrite does not know, keeps the operator whole
+    if any(node.kwargs.get(name) is not None for name in ("attn_mask", "attn_bias")):
+        return None
+    if any(name not in ("scale", "dropout_p", "is_causal", "attn_mask", "attn_bias", "return_debug_mask", "compute_log_sumexp")
+           for name in node.kwargs):
         return None
     dropout_at = causal_at - 1
     if len(args) > dropout_at and args[dropout_at] not in (0, 0.0) or node.kwargs.get("dropout_p", 0.0) not in (0, 0.0):
@@ -662,6 +671,7 @@ def _gemm_epilogue_step(addmm: fx.Node, activation: str, residual: fx.Node | Non
         try:
             return ops.gemm(a_t, b_t, bias_t, activation, None if extra is None else ops.contiguous(extra))
         except Declined:
+            note_torch_work()
             out = fallback(torch.addmm(bias_t, a_t, b_t))
             return out if extra is None else out + extra.reshape(out.shape)
 
@@ -758,6 +768,7 @@ def _or_torch(kernel_fn: Callable, target) -> Callable:
         try:
             return kernel_fn(*args)
         except Declined:
+            note_torch_work()
             return target(*args)
 
     return run

@@ -88,7 +88,7 @@ struct AttnParams {
   float scale_log2;                // scale * log2(e)
   void* out;
   long long out_batch, out_head, out_token;   // element strides
-  int* status;
+  WaitStatus status;
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
@@ -517,8 +517,8 @@ extern "C" tq_status tq_attention_launch(tq_dtype dtype, const void* q, const vo
   TQ_REQUIRE(tq::aligned_to(out, 2) && out_strides[0] >= 0 && out_strides[1] >= 0 && out_strides[2] >= 0, TQ_INVALID_ARGUMENT,
              "misaligned result or negative result stride");
   if (tq_status s = tq::use_device(device)) return s;
-  int* status = tq::device_status_word(device);
-  TQ_REQUIRE(status != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
+  const tq::WaitStatus status = tq::wait_status_for(device);
+  TQ_REQUIRE(status.sticky != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
 
   CUtensorMap map_q, map_k, map_v;
   if (tq_status s = tq::attention_map(&map_q, dtype, q, q_tokens, heads, batch, q_strides)) return s;

@@ -90,8 +90,18 @@ tq_status record(Replay step);
     if (::tq::recording()) return ::tq::record(__VA_ARGS__);                    \
   } while (0)
 
-// Device-side status word (one per device), written by kernels whose bounded waits give up.
+// Device-side status block (one per device, 64 words), written by kernels whose bounded waits give
+// up. Word 0 is the sticky code tq_status_poll reads and clears; words 1-7 say where the wait was
+// (tq_status_detail); words 8-63 are abort words: each launch is handed one of them and an epoch no
+// other launch in flight shares, and "abort word == epoch" tells the launch's other waits to leave.
 int32_t* device_status_word(int32_t device);
+struct WaitStatus {
+  int* sticky;
+  int* abort;
+  int epoch;
+};
+// The status handles for one launch on `device`; `sticky` is null when the block cannot be allocated.
+WaitStatus wait_status_for(int32_t device);
 
 // reduce.cu: per-slice (max, 1/sum-exp) [kind 0] or (mean, variance) [kind 1] of a packed
 // [outer, reduce, inner] tensor, two floats per slice. Used by the transposed softmax / LayerNorm.

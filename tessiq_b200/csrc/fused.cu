@@ -691,10 +691,6 @@ int unroll_for(const Program& p, int vec) {
   // Registers that hold operands between the load phase and the compute phase.
   int words = 0;
   for (const Input& in : p.inputs) words += vec * (cls_of(in.dtype) == Cls::kF64 || cls_of(in.dtype) == Cls::kI64 ? 2 : 1);
-  if (const char* forced = std::getenv("TQ_FUSED_UNROLL")) {  // tuning override: 1, 2, 4 or 8
-    const int value = std::atoi(forced);
-    if (value == 1 || value == 2 || value == 4 || value == 8) return value;
-  }
   // Measured on config 1 (two 4-byte operands, 8 words): 2 tiles of loads per thread beat 4
   // (23.0 us against 24.4 us) — smaller CTAs retire and refill at a finer grain.
   // Vectors of 8 or 16 narrow elements already mean 8-16 conversions and results per load: one tile

@@ -70,7 +70,7 @@ struct GemmParams {
   void* c;
   long long ldc, stride_c;
   int activation;
-  int* status;
+  WaitStatus status;
 };
 
 // Instruction descriptor of tcgen05.mma kind::f16: f32 accumulator, A/B format (0 f16, 1 bf16),
@@ -88,6 +88,21 @@ __device__ __forceinline__ float activate(float v, int activation) {
   }
   if (activation == TQ_ACT_GELU_ERF) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
   return v;
+}
+
+// A barrier of the eight epilogue warps (named barrier 1) that also returns whether `ok` held on every
+// one of its threads, so that a bounded wait that gave up on one warp takes all of them out at once.
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+  uint32_t all;
+  asm volatile(
+      "{\n\t.reg .pred mine, every;\n\t"
+      "setp.ne.b32 mine, %1, 0;\n\t"
+      "bar.red.and.pred every, 1, %2, mine;\n\t"
+      "selp.u32 %0, 1, 0, every;\n\t}"
+      : "=r"(all)
+      : "r"(static_cast<uint32_t>(ok)), "n"(kEpilogueThreads)
+      : "memory");
+  return all != 0;
 }
 
 // The same on two elements at once with the .f32x2 forms of add, mul and fma, and with the
@@ -400,9 +415,11 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         if (p.bias != nullptr && n0 + j < p.n) value = to_compute(static_cast<const T*>(p.bias)[n0 + j]);
         bias_tile[j] = value;
       }
-      if (!barrier_wait(tmem_full_bar(acc), acc_phase, p.status, kWaitTmemFull)) break;
+      // The give-up is decided for the epilogue as a whole: every epilogue thread reaches the named
+      // barrier, which also carries the AND of their waits, and all leave together or none does.
+      const bool arrived = barrier_wait(tmem_full_bar(acc), acc_phase, p.status, kWaitTmemFull);
       tcgen05_fence_after();
-      asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");   // bias_tile is complete
+      if (!epilogue_all(arrived)) break;   // also: bias_tile is complete
 
       T* c_tile = static_cast<T*>(p.c) + static_cast<long long>(batch) * p.stride_c + static_cast<long long>(tile_m) * kTileM * p.ldc + n0;
       const T* residual_tile = p.residual == nullptr ? nullptr : static_cast<const T*>(p.residual) + static_cast<long long>(batch) * p.stride_r +
@@ -580,9 +597,11 @@ gemm_bias_act_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         if (p.bias != nullptr && n0 + j < p.n) value = to_compute(static_cast<const T*>(p.bias)[n0 + j]);
         bias_tile[j] = value;
       }
-      if (!barrier_wait(tmem_full_bar(acc), acc_phase, p.status, kWaitTmemFull)) break;
+      // The give-up is decided for the epilogue as a whole: every epilogue thread reaches the named
+      // barrier, which also carries the AND of their waits, and all leave together or none does.
+      const bool arrived = barrier_wait(tmem_full_bar(acc), acc_phase, p.status, kWaitTmemFull);
       tcgen05_fence_after();
-      asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");
+      if (!epilogue_all(arrived)) break;   // also: bias_tile is complete
 
       const int row0 = tile_m * kPairTileM + static_cast<int>(rank) * kTileM;
       T* c_tile = static_cast<T*>(p.c) + static_cast<long long>(batch) * p.stride_c + static_cast<long long>(row0) * p.ldc + n0;
@@ -720,14 +739,12 @@ extern "C" tq_status tq_gemm_bias_act_residual_launch(tq_dtype dtype, tq_activat
   TQ_REQUIRE(residual == nullptr || (tq::aligned_to(residual, 2) && ldr >= n), TQ_INVALID_ARGUMENT,
              "misaligned residual, or its leading dimension is smaller than a row");
   if (tq_status s = tq::use_device(device)) return s;
-  int* status = tq::device_status_word(device);
-  TQ_REQUIRE(status != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
+  const tq::WaitStatus status = tq::wait_status_for(device);
+  TQ_REQUIRE(status.sticky != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
 
   // Large problems run on CTA pairs (256 x 256 tiles, half the shared-memory operand traffic per
   // SM); problems with at most one row of 128 x 256 tiles keep the single-CTA kernel.
-  // TQ_GEMM_PAIR=0 forces the single-CTA kernel, =1 the pair kernel.
-  bool pair = m > tq::kTileM;
-  if (const char* forced = std::getenv("TQ_GEMM_PAIR")) pair = forced[0] == '1';
+  const bool pair = m > tq::kTileM;
   CUtensorMap map_a, map_b;
   const long long batch_a = stride_a > 0 ? batch : 1, batch_b = stride_b > 0 ? batch : 1;
   const int b_rows = pair ? tq::kTileN / 2 : tq::kTileN;

@@ -70,7 +70,7 @@ constexpr int kStatusPanelStats = 0x504e4c37;        // "PNL7": a panel's statis
 constexpr int kStatusPanelLead = 0x504e4c38;         // "PNL8": the second visit never caught up
 constexpr int kStatusPanelOrder = 0x504e4c39;        // "PNL9": a stage arrived out of order
 
-constexpr uint32_t kItemNormalize = 1u, kItemFirst = 2u, kItemLast = 4u, kItemExit = 8u;
+constexpr uint32_t kItemFirst = 2u, kItemLast = 4u, kItemExit = 8u;
 
 struct PanelArgs {
   void* out;
@@ -95,7 +95,7 @@ struct PanelArgs {
   unsigned* queue_s;        // next first-visit item
   unsigned* queue_n;        // next second-visit item
   unsigned* begun_n;        // second-visit items whose flag was seen up (what the first visit's lead is measured against)
-  int* status;
+  WaitStatus status;
 };
 
 __device__ __forceinline__ uint64_t l2_policy(int kind) {   // 0 normal, 1 evict-last, 2 evict-first
@@ -139,20 +139,25 @@ __device__ __forceinline__ void store_release(unsigned* pointer, unsigned value)
 // A bounded mbarrier wait that leaves a trace: the first wait of the device to give up writes its code
 // to the status word and, behind it, where it was (CTA, thread, and three values of the caller).
 constexpr uint32_t kPanelSpinLimit = 1u << 18;
-__device__ __forceinline__ bool panel_wait(uint32_t bar, uint32_t parity, int* status, int code, int d0, int d1, int d2,
+__device__ __forceinline__ void panel_give_up(const WaitStatus& status, int code, int d0 = 0, int d1 = 0, int d2 = 0, int d3 = 0) {
+  if (atomicCAS(status.sticky, 0, code) == 0) {
+    status.sticky[1] = static_cast<int>(blockIdx.x);
+    status.sticky[2] = static_cast<int>(threadIdx.x);
+    status.sticky[3] = d0;
+    status.sticky[4] = d1;
+    status.sticky[5] = d2;
+    status.sticky[6] = d3;
+  }
+  *reinterpret_cast<volatile int*>(status.abort) = status.epoch;
+}
+
+__device__ __forceinline__ bool panel_wait(uint32_t bar, uint32_t parity, const WaitStatus& status, int code, int d0, int d1, int d2,
                                            uint32_t limit = kPanelSpinLimit) {
   for (uint32_t spin = 0; spin < limit; ++spin) {
     if (barrier_try_wait(bar, parity)) return true;
-    if ((spin & 0x3ff) == 0x3ff && *reinterpret_cast<volatile int*>(status) != 0) return false;
+    if ((spin & 0x3ff) == 0x3ff && *reinterpret_cast<volatile int*>(status.abort) == status.epoch) return false;
   }
-  if (atomicCAS(status, 0, code) == 0) {
-    status[1] = static_cast<int>(blockIdx.x);
-    status[2] = static_cast<int>(threadIdx.x);
-    status[3] = d0;
-    status[4] = d1;
-    status[5] = d2;
-    status[6] = static_cast<int>(parity);
-  }
+  panel_give_up(status, code, d0, d1, d2, static_cast<int>(parity));
   return false;
 }
 
@@ -477,7 +482,7 @@ __global__ void __launch_bounds__(kPanelThreads, 1) panel_normalize_kernel(const
             }
             __nanosleep(100);
           }
-          if (!ok) atomicCAS(args.status, 0, kStatusPanelLead);
+          if (!ok) panel_give_up(args.status, kStatusPanelLead, static_cast<int>(item), static_cast<int>(seen_n));
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
       }
@@ -495,7 +500,7 @@ __global__ void __launch_bounds__(kPanelThreads, 1) panel_normalize_kernel(const
               __nanosleep(40);
             }
             if (seen == 0) {
-              atomicCAS(args.status, 0, kStatusPanelFlag);
+              panel_give_up(args.status, kStatusPanelFlag, panel, chunk);
               ok = 0;
             }
           }
@@ -589,7 +594,7 @@ __global__ void __launch_bounds__(kPanelThreads, 1) panel_normalize_kernel(const
       }
       const uint4 note = notes_s[stage];
       if ((note.x >> 4) != expected) {
-        atomicCAS(args.status, 0, kStatusPanelOrder);
+        panel_give_up(args.status, kStatusPanelOrder, static_cast<int>(note.x), static_cast<int>(expected), stage);
         alive = false;
         break;
       }
@@ -679,7 +684,7 @@ __global__ void __launch_bounds__(kPanelThreads, 1) panel_normalize_kernel(const
       }
       const uint4 note = notes_n[stage];
       if ((note.x >> 4) != expected) {
-        atomicCAS(args.status, 0, kStatusPanelOrder);
+        panel_give_up(args.status, kStatusPanelOrder, static_cast<int>(note.x), static_cast<int>(expected), stage);
         alive = false;
         break;
       }
@@ -866,8 +871,8 @@ tq_status panel_normalize_launch(int kind, tq_dtype dtype, const void* in, void*
   const PanelLayout l = panel_layout(dtype, batch, rows, cols);
   TQ_REQUIRE(workspace != nullptr && workspace_bytes >= l.total() && aligned_to(workspace, 16), TQ_INVALID_ARGUMENT,
              "the panel normalisation needs %zu bytes of 16-byte-aligned scratch and was given %zu", l.total(), workspace_bytes);
-  int* status = device_status_word(device);
-  TQ_REQUIRE(status != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
+  const WaitStatus status = wait_status_for(device);
+  TQ_REQUIRE(status.sticky != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
 
   // in[batch * rows, cols] as a two-axis map; a tile is one stage: 512 bytes of 64 consecutive rows.
   EncodeTiled encode = encode_tiled();

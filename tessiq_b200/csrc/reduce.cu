@@ -211,6 +211,30 @@ struct ArgmaxReducer {
 
 
 
+// The local part of a reduction over a tensor that is split over several GPUs (collective.cu): the
+// result is a two-float partial that an all-reduce can combine. A sum's partial is {sum in f32, 0}
+// (the f32 accumulator itself: a bf16 tensor's partial is not rounded to bf16 first).
+template <typename T>
+struct SumPartialReducer : SumReducer<T> {
+  using Out = float2;
+  using Acc = typename SumReducer<T>::Acc;
+  __device__ static Out finish(Acc a, long long, bool) { return make_float2(static_cast<float>(a), 0.f); }
+};
+
+// A maximum's partial is {maximum with a NaN replaced by -inf, 1 if a NaN was seen}, to be combined
+// with MAX on both words; a minimum's {minimum with a NaN replaced by +inf, -1 if a NaN was seen},
+// combined with MIN: a collective's maximum does not promise to propagate NaN, the flag does.
+template <typename T, bool kMax>
+struct ExtremePartialReducer : ExtremeReducer<T, kMax> {
+  using Out = float2;
+  using Acc = typename ExtremeReducer<T, kMax>::Acc;
+  __device__ static Out finish(Acc a, long long, bool) {
+    const float value = static_cast<float>(a);
+    if (value != value) return make_float2(kMax ? -std::numeric_limits<float>::infinity() : std::numeric_limits<float>::infinity(), kMax ? 1.f : -1.f);
+    return make_float2(value, 0.f);
+  }
+};
+
 // Reads a partial another CTA wrote, from L2 (never a stale L1 line).
 template <typename A>
 __device__ __forceinline__ A load_partial(const A* pointer) {
@@ -640,10 +664,6 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
     if (vec < 1) vec = 1;
     while (vec > 1 && inner % vec != 0) vec /= 2;
     if ((op == TQ_ARGMAX || op == kOpMoments) && vec > 4) vec = 4;  // their per-column state is large; 16-byte loads measured no better (argmax) or worse (moments)
-    if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_VEC")) {    // tuning override: 1, 2, 4 or 8
-      const int value = std::atoi(forced);
-      if ((value == 1 || value == 2 || value == 4 || value == 8) && value * size <= 16 && inner % value == 0) vec = value;
-    }
     p.vec = vec;
     long long groups = (inner + vec - 1) / vec;
     // A warp reads 32 vectors (512 bytes) of one row; the CTA's 8 warps read 8 consecutive rows.
@@ -652,18 +672,12 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
     // costs registers) with the cp.async ring and 32 lanes.
     p.ring = (size <= 2 || op == TQ_ARGMAX || op >= kOpSoftmaxStat) && reduce < (1ll << 31);   // the ring counts a thread's rows in 32 bits
     int lanes = p.ring ? 32 : 64;
-    if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_LANES")) {  // tuning override: 1..256, a power of two
-      const int value = std::atoi(forced);
-      if (value >= 1 && value <= kBlock && (value & (value - 1)) == 0) lanes = value;
-    }
     while (lanes > 1 && lanes / 2 >= groups) lanes /= 2;
     p.lanes_x = lanes;
     p.column_tiles = (groups + lanes - 1) / lanes;
     const long long base_ctas = p.column_tiles * outer;
     // One or two waves of CTAs (all of a wave resident at once, equal work each).
-    int waves = (p.ring && !(op == TQ_ARGMAX && size <= 2)) ? 2 : 1;
-    if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_WAVES")) waves = std::max(1, std::atoi(forced));
-    if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_RING")) p.ring = forced[0] == '1';
+    const int waves = (p.ring && !(op == TQ_ARGMAX && size <= 2)) ? 2 : 1;
     long long want = (target_ctas * waves + base_ctas - 1) / base_ctas;
     const long long per_pass = static_cast<long long>(kBlock / lanes) * kUnroll;
     long long most = reduce / per_pass;
@@ -673,10 +687,6 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
     // The cluster's reduce-scatter gives every CTA a whole number of threads' accumulators.
     int max_cluster = kMaxCluster;
     while (max_cluster > lanes) max_cluster /= 2;
-    if (const char* forced = std::getenv("TQ_REDUCE_COLUMN_CLUSTER")) {  // tuning override: 1, 2, 4 or 8
-      const int value = std::atoi(forced);
-      if (value >= 1 && value <= max_cluster && (value & (value - 1)) == 0) max_cluster = value;
-    }
     if (want <= max_cluster) {
       p.split = floor_pow2(want);
       p.cluster = p.split;
@@ -936,9 +946,42 @@ tq_status tq_reduce_launch(tq_reduce_op op, tq_dtype dtype, const void* in, void
   }
 }
 
+tq_status tq_reduce_partial_launch(tq_reduce_op op, tq_dtype dtype, const void* in, void* partial, int64_t count, void* workspace,
+                                   size_t workspace_bytes, int32_t device, void* stream) {
+  TQ_RECORD_OR_RUN([=](int32_t d, void* s) { return tq_reduce_partial_launch(op, dtype, in, partial, count, workspace, workspace_bytes, d, s); });
+  TQ_REQUIRE(op == TQ_SUM || op == TQ_MEAN || op == TQ_AMAX || op == TQ_AMIN, TQ_UNSUPPORTED, "no global partial for operation %d", op);
+  TQ_REQUIRE(dtype == TQ_F32 || dtype == TQ_F16 || dtype == TQ_BF16, TQ_UNSUPPORTED,
+             "the two-float partial serves f32, f16 and bf16 tensors, not %s", tq::dtype_name(dtype));
+  TQ_REQUIRE(count > 0, TQ_UNSUPPORTED, "a reduction over no elements has no kernel");
+  TQ_REQUIRE(in != nullptr && partial != nullptr && tq::aligned_to(partial, 8), TQ_INVALID_ARGUMENT, "null input, or a partial that is not 8-byte aligned");
+  const int size = tq::dtype_size(dtype);
+  TQ_REQUIRE(tq::aligned_to(in, size), TQ_INVALID_ARGUMENT, "input pointer is not aligned to its element type");
+  if (tq_status s = tq::use_device(device)) return s;
+  // the plan of the plain reduction over [1, count, 1]: same kernels, same scratch, another finish
+  const tq::Plan p = tq::plan(op == TQ_MEAN ? TQ_SUM : op, dtype, 1, count, 1, device, 16);
+  const size_t need = p.partial_bytes + p.ticket_bytes;
+  TQ_REQUIRE(need == 0 || (workspace != nullptr && workspace_bytes >= need && tq::aligned_to(workspace, 16)), TQ_INVALID_ARGUMENT,
+             "this reduction needs %zu bytes of 16-byte-aligned scratch (tq_reduce_workspace_bytes) and was given %zu", need, workspace_bytes);
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+#define TQ_PARTIAL(T)                                                                                                                      \
+  switch (op) {                                                                                                                            \
+    case TQ_AMAX: return tq::run<T, tq::ExtremePartialReducer<T, true>>(p, in, partial, 1, count, 1, false, workspace, cuda_stream);        \
+    case TQ_AMIN: return tq::run<T, tq::ExtremePartialReducer<T, false>>(p, in, partial, 1, count, 1, false, workspace, cuda_stream);       \
+    default: return tq::run<T, tq::SumPartialReducer<T>>(p, in, partial, 1, count, 1, false, workspace, cuda_stream);                        \
+  }
+  switch (dtype) {
+    case TQ_F32: TQ_PARTIAL(float)
+    case TQ_F16: TQ_PARTIAL(__half)
+    default: TQ_PARTIAL(__nv_bfloat16)
+  }
+#undef TQ_PARTIAL
+}
+
 tq_status tq_reduce_launch_static(tq_reduce_op op, tq_dtype dtype, const void* in, void* out,
                                   int64_t outer, int64_t reduce, int64_t inner, int32_t device,
                                   void* stream) {
+  // recorded like every other launch: the replay looks the built-in array up for the device it runs on
+  TQ_RECORD_OR_RUN([=](int32_t d, void* s) { return tq_reduce_launch_static(op, dtype, in, out, outer, reduce, inner, d, s); });
   if (tq_status s = tq::validate(op, dtype, outer, reduce, inner)) return s;
   if (outer == 0 || inner == 0) return TQ_OK;
   TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");

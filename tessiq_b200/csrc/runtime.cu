@@ -1,9 +1,11 @@
 // Library-wide state: error slot, device selection, per-GPU streams, the bump arena and the
 // device-side status word that bounded waits report through.
+#include <atomic>
 #include <mutex>
 #include <vector>
 
 #include "common.h"
+#include "tcgen05.h"
 
 namespace tq {
 
@@ -65,6 +67,55 @@ int32_t* device_status_word(int32_t device) {
   return g_status_word[device];
 }
 
+WaitStatus wait_status_for(int32_t device) {
+  static std::atomic<unsigned> launches{0};
+  int32_t* block = device_status_word(device);
+  if (block == nullptr) return WaitStatus{nullptr, nullptr, 0};
+  const unsigned n = launches.fetch_add(1, std::memory_order_relaxed) + 1;
+  const int epoch = static_cast<int>(n | 0x40000000u);   // never 0, the value a cleared block holds
+  return WaitStatus{block, block + 8 + n % 56, epoch};
+}
+
+}  // namespace tq
+
+namespace tq {
+namespace {
+constexpr int kStatusSelfTest = 0x53454c46;   // "SELF"
+
+// One warp waits, for at most `polls` looks, on an mbarrier that expects two arrivals and gets one:
+// the wait cannot complete. It gives up the way every bounded wait of this library does — the sticky
+// code, the launch's abort word — and the kernel returns by itself. A second wait then shows that
+// the abort word takes the launch's other waits out at their next look.
+__global__ void bounded_wait_selftest_kernel(WaitStatus status, uint32_t polls, int* looks) {
+  __shared__ uint64_t barrier;
+  const uint32_t bar = smem_address(&barrier);
+  if (threadIdx.x == 0) {
+    barrier_init(bar, 2);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    barrier_arrive(bar);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t spin = 0;
+    bool done = false;
+    for (; spin < polls; ++spin) {
+      if (barrier_try_wait(bar, 0)) {
+        done = true;
+        break;
+      }
+    }
+    if (!done) {
+      atomicCAS(status.sticky, 0, kStatusSelfTest);
+      *reinterpret_cast<volatile int*>(status.abort) = status.epoch;
+    }
+    looks[0] = static_cast<int>(spin);
+    // the library's own wait now leaves at its first look at the abort word (every 1024 polls)
+    const long long before = clock64();
+    const bool second = barrier_wait(bar, 0, status, kStatusSelfTest);
+    looks[1] = second ? -1 : static_cast<int>((clock64() - before) >> 10);
+  }
+}
+}  // namespace
 }  // namespace tq
 
 struct tq_recipe {
@@ -206,8 +257,23 @@ tq_status tq_status_poll(int32_t device, void* stream, int32_t* device_status) {
   int32_t host = 0;
   TQ_CUDA(cudaMemcpyAsync(&host, word, sizeof(host), cudaMemcpyDeviceToHost, cuda_stream));
   TQ_CUDA(cudaStreamSynchronize(cuda_stream));
-  if (host != 0) TQ_CUDA(cudaMemsetAsync(word, 0, sizeof(host), cuda_stream));
+  if (host != 0) TQ_CUDA(cudaMemsetAsync(word, 0, 256, cuda_stream));   // the code, where it happened, and the abort words
   *device_status = host;
+  return TQ_OK;
+}
+
+tq_status tq_selftest_bounded_wait(int32_t device, void* stream, int32_t polls, int32_t* looks) {
+  TQ_REQUIRE(polls > 0 && polls <= (1 << 20), TQ_INVALID_ARGUMENT, "between 1 and 2^20 polls");
+  TQ_REQUIRE(looks != nullptr, TQ_INVALID_ARGUMENT, "looks out-pointer is null");
+  if (tq_status s = tq::use_device(device)) return s;
+  const tq::WaitStatus status = tq::wait_status_for(device);
+  TQ_REQUIRE(status.sticky != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+  int* device_looks = status.sticky + 6;   // words of the status block that only a give-up's detail uses
+  tq::bounded_wait_selftest_kernel<<<1, 32, 0, cuda_stream>>>(status, static_cast<uint32_t>(polls), device_looks);
+  if (tq_status s = tq::check_launch("bounded_wait_selftest_kernel")) return s;
+  TQ_CUDA(cudaMemcpyAsync(looks, device_looks, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, cuda_stream));
+  TQ_CUDA(cudaStreamSynchronize(cuda_stream));
   return TQ_OK;
 }
 

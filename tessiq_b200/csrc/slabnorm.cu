@@ -282,10 +282,6 @@ tq_status slab_launch(const SlabArgs& args, long long batch, cudaStream_t stream
 // the columns are long (from 8192 rows: 1024 per CTA); past that the pieces, a whole row of the
 // tensor apart, each open a DRAM page of their own and the two-launch form is ahead.
 bool slab_takes(tq_dtype dtype, long long batch, long long rows, long long cols) {
-  if (const char* forced = std::getenv("TQ_SLAB")) {       // a tuning aid: 0 switches the path off, 1 drops the size rule
-    if (forced[0] == '0') return false;
-    if (forced[0] == '1') batch = 0;
-  }
   const int size = dtype_size(dtype);
   if (size != 2 && size != 4) return false;
   const int v = 16 / size;

@@ -41,14 +41,18 @@ __device__ __forceinline__ bool barrier_try_wait(uint32_t bar, uint32_t parity) 
 }
 
 // Waits for the phase of `bar` with the given parity, for a bounded number of polls. When the
-// bound runs out (or another thread's already did) the status word gets `code` and the caller
-// must leave its loop.
-__device__ __forceinline__ bool barrier_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+// bound runs out the device's sticky status word gets `code` (the first give-up wins; tq_status_poll
+// reads and clears it) and this launch's abort word gets the launch's epoch, which makes every other
+// bounded wait of the same launch leave at its next look — of THIS launch only: a later launch has
+// another epoch, so a give-up nobody has polled yet does not make it bail out. The caller must
+// leave its loop on false.
+__device__ __forceinline__ bool barrier_wait(uint32_t bar, uint32_t parity, const WaitStatus& status, int code) {
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
     if (barrier_try_wait(bar, parity)) return true;
-    if ((spin & 0x3ff) == 0x3ff && *reinterpret_cast<volatile int*>(status) != 0) return false;
+    if ((spin & 0x3ff) == 0x3ff && *reinterpret_cast<volatile int*>(status.abort) == status.epoch) return false;
   }
-  atomicCAS(status, 0, code);
+  atomicCAS(status.sticky, 0, code);
+  *reinterpret_cast<volatile int*>(status.abort) = status.epoch;
   return false;
 }
 

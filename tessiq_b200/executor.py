@@ -18,6 +18,16 @@ import torch
 from torch import fx
 
 
+# How often a step that normally launches one of this library's kernels ran a PyTorch operator instead
+# (a kernel declined the operands at launch time). A native recording cannot replay such work, so
+# NativeRecipe looks at this count around its recording run.
+_torch_work = [0]
+
+
+def note_torch_work() -> None:
+    _torch_work[0] += 1
+
+
 @dataclass
 class Step:
     kind: str                      # fused | reduction | custom | gemm | pack | view | constant | interpreted
@@ -149,6 +159,7 @@ class NativeRecipe:
         self.recipe = recipe
         self._lib = _lib
         self._recorded: dict = {}
+        self._eager: set = set()     # signatures whose recording run fell back to PyTorch for some step
         self.recordable = not recipe.interpreted
 
     def __del__(self):
@@ -165,6 +176,8 @@ class NativeRecipe:
         if not self.recordable or not all(isinstance(a, torch.Tensor) and a.is_cuda for a in args):
             return self.recipe.run(*args)
         key = GraphedRecipe._signature(args)
+        if key in self._eager:
+            return self.recipe.run(*args)
         entry = self._recorded.get(key)
         if entry is None:
             self.recipe.run(*args)  # an eager run first: modules loaded, scratch allocated
@@ -172,11 +185,17 @@ class NativeRecipe:
             handle = ctypes.c_void_p()
             self._lib.check(self._lib.lib.tq_recipe_create(ctypes.byref(handle)))
             kept: list = []
+            before = _torch_work[0]
             self._lib.check(self._lib.lib.tq_recipe_begin_recording(handle))
             try:
                 outputs = self.recipe.run(*static_inputs, keep=kept)
             finally:
                 self._lib.check(self._lib.lib.tq_recipe_end_recording(handle))
+            if _torch_work[0] != before:
+                # a kernel declined its operands and PyTorch did that step's work: the recording lacks it
+                self._lib.check(self._lib.lib.tq_recipe_destroy(handle))
+                self._eager.add(key)
+                return self.recipe.run(*args)
             entry = (handle, static_inputs, outputs, kept)
             self._recorded[key] = entry
         handle, static_inputs, outputs, _ = entry

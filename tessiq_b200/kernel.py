@@ -266,19 +266,60 @@ def reduction_extents(shape: Sequence[int], first_axis: int, last_axis: int) -> 
 
 
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_outgrown: dict[tuple[int, int], list[torch.Tensor]] = {}
 
 
 def workspace(device: int, stream: int, nbytes: int) -> torch.Tensor | None:
     """Scratch memory for one (device, stream): launches on one stream are ordered, so they can
-    share it; launches on different streams get different blocks."""
+    share it; launches on different streams get different blocks. A block that has become too small
+    is replaced by one at least twice its size and KEPT: a launch still in flight on the raw stream,
+    a captured CUDA graph or a recorded tq_recipe may hold its address (the library keeps pointers
+    as given), and PyTorch's allocator orders reuse only against its own current stream. Doubling
+    bounds what the kept blocks hold to the size of the live one; release_workspaces() frees all."""
     if nbytes == 0:
         return None
     key = (device, stream)
     block = _workspaces.get(key)
     if block is None or block.numel() < nbytes:
-        block = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=f"cuda:{device}")
+        if block is not None:
+            _outgrown.setdefault(key, []).append(block)
+        size = max(nbytes, 1 << 20, 2 * block.numel() if block is not None else 0)
+        block = torch.empty(size, dtype=torch.uint8, device=f"cuda:{device}")
         _workspaces[key] = block
     return block
+
+
+def release_workspaces() -> None:
+    """Frees every scratch block. Only when nothing that was launched, captured or recorded with them
+    will run again."""
+    torch.cuda.synchronize()
+    _workspaces.clear()
+    _outgrown.clear()
+
+
+class DeviceWaitError(RuntimeError):
+    """A bounded wait inside one of the library's kernels gave up (tq_status_poll)."""
+
+
+_WAIT_CODES = {0x53454c46: "the bounded-wait self test", 0x504e4c31: "panel normalisation: a panel's flag never went up",
+               0x504e4c32: "panel normalisation: a stage's data never arrived", 0x504e4c33: "panel normalisation: a stage was never handed back",
+               0x504e4c34: "panel normalisation: the publishers' next item never came", 0x504e4c35: "panel normalisation: accumulators never handed back",
+               0x504e4c36: "panel normalisation: a statistics buffer was never handed back", 0x504e4c37: "panel normalisation: statistics never reached shared memory",
+               0x504e4c38: "panel normalisation: the second visit never caught up", 0x504e4c39: "panel normalisation: a stage arrived out of order"}
+
+
+def check_status(device: int = 0, stream: int | None = None) -> None:
+    """Synchronises `stream`, reads and clears the device's status word, and raises DeviceWaitError
+    when a bounded wait of an earlier launch gave up (its kernel left early: results of that launch
+    are incomplete). Call it wherever results are about to be trusted after a synchronisation."""
+    words = (ctypes.c_int32 * 8)()
+    check(lib.tq_status_detail(device, ctypes.c_void_p(stream or 0), words, 8))
+    code = ctypes.c_int32()
+    check(lib.tq_status_poll(device, ctypes.c_void_p(stream or 0), ctypes.byref(code)))
+    if code.value != 0:
+        what = _WAIT_CODES.get(code.value, "a tensor-core kernel's pipeline wait")
+        raise DeviceWaitError(f"a bounded wait on device {device} gave up: code {code.value:#x} ({what}); "
+                              f"CTA {words[1]}, thread {words[2]}, detail {list(words[3:7])}")
 
 
 class ReductionKernel(Kernel):

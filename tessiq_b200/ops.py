@@ -19,7 +19,7 @@ import torch
 
 from . import _lib
 from .kernel import (DTYPE_NAMES, AttentionKernel, FusedKernel, GemmKernel, LayerNormKernel, PackKernel, SoftmaxKernel, _device_of,
-                     _pointer, _stream, classify_read, dtype_code, launch_reduce, launch_transposed, prefers_transposed)
+                     _pointer, _stream, check_status, classify_read, dtype_code, launch_reduce, launch_transposed, prefers_transposed)
 from ._lib import Declined, check, lib
 
 import ctypes
@@ -420,13 +420,18 @@ def matmul_bias_gelu_tanh(a, b, bias):
     return _gemm(a, b, bias, "gelu_tanh")
 
 
-def attention(q, k, v, scale=None, causal=False):
+def attention(q, k, v, scale=None, causal=False, token_major=True):
     """softmax(scale * q @ k.T [causal]) @ v for [batch, heads, tokens, 64] operands, one kernel.
-    The result is a [batch, heads, tokens, 64] view of a packed [batch, tokens, heads, 64] buffer,
-    so `.transpose(1, 2).reshape(batch, tokens, heads * 64)` after it is free."""
+    With `token_major` the result is a [batch, heads, tokens, 64] view of a packed
+    [batch, tokens, heads, 64] buffer, so `.transpose(1, 2).reshape(batch, tokens, heads * 64)` after it
+    is free; without, it is a packed [batch, heads, tokens, 64] tensor (free to fold into
+    [batch * heads, tokens, 64]). The kernel writes either through its output strides."""
     batch, heads, tokens, width = q.shape
     scale = 1.0 / math.sqrt(width) if scale is None else scale
-    out = torch.empty([batch, tokens, heads, width], dtype=q.dtype, device=q.device).transpose(1, 2)
+    if token_major:
+        out = torch.empty([batch, tokens, heads, width], dtype=q.dtype, device=q.device).transpose(1, 2)
+    else:
+        out = torch.empty([batch, heads, tokens, width], dtype=q.dtype, device=q.device)
     if out.numel():
         AttentionKernel(scale, causal).launch([q, k, v], out, stream=None)
     return out

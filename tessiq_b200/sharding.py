@@ -44,8 +44,93 @@ def _local_ops():
     return {"sum": ops.sum, "amax": ops.amax, "amin": ops.amin, "argmax": ops.argmax}
 
 
+class Comm:
+    """This process's NCCL communicator behind the C ABI (tq_comm_*): rank 0 draws the id, the ranks
+    of `group` pass it around through torch.distributed's host-side store, and every rank makes its
+    communicator for its own GPU. The data path never touches torch.distributed: tq_allreduce_scalar
+    enqueues NCCL's all-reduce on the caller's stream."""
+
+    def __init__(self, device: int, group=None):
+        import ctypes
+
+        from . import _lib
+
+        self._lib, self.device = _lib, device
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        box = [None]
+        if rank == 0:
+            unique = ctypes.create_string_buffer(128)
+            _lib.check(_lib.lib.tq_comm_unique_id(unique, 128))
+            box[0] = unique.raw
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        handle = ctypes.c_void_p()
+        _lib.check(_lib.lib.tq_comm_create(box[0], 128, rank, world, device, ctypes.byref(handle)))
+        self.handle, self.rank, self.world = handle, rank, world
+
+    def all_reduce(self, buffer: torch.Tensor, op: str, stream: int) -> None:
+        from .kernel import dtype_code
+
+        code = {"sum": self._lib.SUM, "amax": self._lib.AMAX, "amin": self._lib.AMIN}[op]
+        self._lib.check(self._lib.lib.tq_allreduce_scalar(self.handle, buffer.data_ptr(), buffer.numel(), dtype_code(buffer.dtype), code,
+                                                          self.device, stream))
+
+    def close(self) -> None:
+        if self.handle:
+            self._lib.lib.tq_comm_destroy(self.handle)
+            self.handle = None
+
+
+_comms: dict = {}
+
+
+def default_comm(device: int, group=None) -> "Comm | None":
+    """The communicator global_reduce uses for CUDA tensors: made on first use (a collective call: every
+    rank of `group` must reach it), None when NCCL cannot be opened — torch.distributed then carries
+    the two floats instead."""
+    key = (device, id(group))
+    if key not in _comms:
+        try:
+            _comms[key] = Comm(device, group)
+        except (KeyError, RuntimeError, OSError):
+            _comms[key] = None
+    return _comms[key]
+
+
+def _native_global_reduce(op: str, flat: torch.Tensor, total: int | None, group, comm) -> torch.Tensor:
+    """sum / mean / amax / amin of a CUDA tensor split over ranks, all behind the C ABI: the local
+    reduction writes a two-float partial (the f32 sum; or the extreme with a NaN replaced and a NaN
+    flag), ONE all-reduce combines the partials, one tiny kernel turns the result into the tensor's
+    type. Three launches and a collective on the caller's stream, nothing else."""
+    import ctypes
+
+    from . import _lib
+    from .kernel import _stream, dtype_code, workspace
+
+    device = flat.device.index
+    stream = _stream(None, device)
+    code = {"sum": _lib.SUM, "mean": _lib.MEAN, "amax": _lib.AMAX, "amin": _lib.AMIN}[op]
+    nbytes = ctypes.c_size_t()
+    _lib.check(_lib.lib.tq_reduce_workspace_bytes(_lib.SUM if op == "mean" else code, dtype_code(flat.dtype), 1, flat.numel(), 1, device, ctypes.byref(nbytes)))
+    scratch = workspace(device, stream, nbytes.value + 256)
+    partial = scratch[:8].view(torch.float32)                      # the first 256 bytes of the block: the partial
+    rest = scratch[256:]
+    _lib.check(_lib.lib.tq_reduce_partial_launch(code, dtype_code(flat.dtype), flat.data_ptr(), partial.data_ptr(), flat.numel(), rest.data_ptr(),
+                                                 rest.numel(), device, ctypes.c_void_p(stream)))
+    how = "sum" if op in ("sum", "mean") else op
+    if comm is not None:
+        comm.all_reduce(partial, how, ctypes.c_void_p(stream))
+    else:
+        dist.all_reduce(partial, op={"sum": dist.ReduceOp.SUM, "amax": dist.ReduceOp.MAX, "amin": dist.ReduceOp.MIN}[how], group=group)
+    if op == "mean" and total is None:
+        total = _global_count(flat.numel(), group, flat.device)
+    out = torch.empty((), dtype=flat.dtype, device=flat.device)
+    _lib.check(_lib.lib.tq_reduce_finish_launch(code, dtype_code(flat.dtype), partial.data_ptr(), out.data_ptr(), total or 0, device,
+                                                ctypes.c_void_p(stream)))
+    return out
+
+
 def global_reduce(op: str, local: torch.Tensor, *, offset: int = 0, total: int | None = None, group=None,
-                  local_ops: dict[str, Callable] | None = None) -> torch.Tensor:
+                  local_ops: dict[str, Callable] | None = None, comm: "Comm | None | str" = "default") -> torch.Tensor:
     """sum / mean / amax / amin / argmax over every element of a tensor whose flattened elements
     are split over the ranks of `group`; `local` is this rank's part and `offset` the flattened
     index of its first element (needed by argmax only). Every rank gets the result.
@@ -54,6 +139,10 @@ def global_reduce(op: str, local: torch.Tensor, *, offset: int = 0, total: int |
       sum, mean  partials are summed in float32 (float64 for f64); mean divides by `total`
       amax/amin  MAX/MIN of the partials plus a MAX over a NaN flag, because a collective's
                  maximum does not promise to propagate NaN
+    For f32 / f16 / bf16 CUDA tensors on more than one rank, sum, mean, amax and amin run entirely
+    behind the C ABI (_native_global_reduce): partial kernel, one all-reduce of two floats over the
+    library's own NCCL communicator (`comm`; "default" makes one on first use, None uses
+    torch.distributed for the exchange), finish kernel.
       argmax     (value, global index) pairs are gathered; the largest value wins, NaN counts as
                  largest, ties go to the lowest global index
     """
@@ -64,6 +153,12 @@ def global_reduce(op: str, local: torch.Tensor, *, offset: int = 0, total: int |
     flat = local.reshape(-1)
     accumulate = torch.float64 if local.dtype == torch.float64 else torch.float32
     integer = not local.dtype.is_floating_point
+
+    if (world > 1 and local_ops is None and flat.is_cuda and flat.numel() and op in ("sum", "mean", "amax", "amin")
+            and flat.dtype in (torch.float32, torch.float16, torch.bfloat16) and flat.is_contiguous()):
+        if comm == "default":
+            comm = default_comm(flat.device.index, group)
+        return _native_global_reduce(op, flat, total, group, comm)
 
     if op in ("sum", "mean"):
         if op == "mean" and integer:

@@ -352,3 +352,58 @@ def test_native_recipe_replays_the_recorded_launches():
         torch.testing.assert_close(got[2].cpu(), z.t().contiguous(), rtol=1e-5, atol=2e-5)
     runner = holder["fn"].runners[0]
     assert runner.recordable and runner.steps(x.cuda(), w.cuda(), b.cuda()) >= 5
+
+
+def test_fused_attention_operators_with_a_mask_by_keyword_stay_whole():
+    """`_scaled_dot_product_flash_attention_for_cpu` takes its mask as the keyword `attn_mask`: a call
+    that sets it (or any keyword the rewrite does not know) must not become the unmasked kernel."""
+    from tessiq_b200 import backend as B
+
+    target = getattr(torch.ops.aten, "_scaled_dot_product_flash_attention_for_cpu", None)
+    if target is None:
+        pytest.skip("this PyTorch has no _scaled_dot_product_flash_attention_for_cpu")
+    graph = torch.fx.Graph()
+    q, k, v, mask = (graph.placeholder(name) for name in ("q", "k", "v", "mask"))
+    value = torch.empty(1, 2, 128, 64, dtype=torch.bfloat16, device="meta")
+    for node in (q, k, v):
+        node.meta["val"] = value
+    mask.meta["val"] = torch.empty(128, 128, dtype=torch.bfloat16, device="meta")
+    plain = graph.call_function(target.default, (q, k, v, 0.0, True))
+    masked = graph.call_function(target.default, (q, k, v, 0.0, False), {"attn_mask": mask})
+    odd = graph.call_function(target.default, (q, k, v, 0.0, False), {"some_new_option": 1})
+    for node in (plain, masked, odd):
+        node.meta["val"] = (value, torch.empty(1, 2, 128, device="meta"))
+        first = graph.call_function(__import__("operator").getitem, (node, 0))
+        first.meta["val"] = value
+    assert B._sdpa_step(plain) is not None
+    assert B._sdpa_step(masked) is None
+    assert B._sdpa_step(odd) is None
+
+
+def test_check_status_raises_once_on_a_reported_wait(monkeypatch):
+    """The poll-and-raise path of the Python layer, against a fake of the two C-ABI calls."""
+    import ctypes
+
+    from tessiq_b200 import kernel as K
+
+    state = {"code": 0x504e4c31, "polls": 0}
+
+    def fake_detail(device, stream, words, count):
+        words[0], words[1], words[2] = state["code"], 17, 288
+        return 0
+
+    def fake_poll(device, stream, out):
+        ctypes.cast(out, ctypes.POINTER(ctypes.c_int32))[0] = state["code"]
+        state["code"] = 0
+        state["polls"] += 1
+        return 0
+
+    class FakeLib:
+        tq_status_detail = staticmethod(fake_detail)
+        tq_status_poll = staticmethod(fake_poll)
+
+    monkeypatch.setattr(K, "lib", FakeLib)
+    with pytest.raises(K.DeviceWaitError, match="flag never went up.*CTA 17, thread 288"):
+        K.check_status(0)
+    K.check_status(0)          # cleared by the first poll
+    assert state["polls"] == 2

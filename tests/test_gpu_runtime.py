@@ -79,3 +79,128 @@ def test_an_arena_larger_than_the_gpu_is_resource_exhausted(abi):
     abi.check(abi.lib.tq_reduce_launch(abi.SUM, abi.F32, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()), 4, 8, 1, None, 0, 0, None))
     torch.cuda.synchronize()
     assert out.tolist() == [8.0] * 4
+
+
+def test_a_bounded_wait_that_runs_out_reports_and_returns(abi):
+    """The give-up path, without a fault: one warp waits on a barrier that cannot complete, for 4096
+    looks, and returns by itself. The status word names it, the launch's other waits leave at once, and
+    launches made afterwards (another epoch) are untouched — also before anyone has polled."""
+    from tessiq_b200 import kernel as K, ops
+
+    lib, check = abi.lib, abi.check
+    status = ctypes.c_int32(-1)
+    check(lib.tq_status_poll(0, None, ctypes.byref(status)))      # start from a clear word
+    looks = (ctypes.c_int32 * 2)()
+    check(lib.tq_selftest_bounded_wait(0, None, 4096, looks))
+    assert looks[0] == 4096                                       # the wait ran out, it was not satisfied
+    # the library's own wait looks at the abort word every 1024 polls: it leaves after those (milliseconds),
+    # not after its full bound of 2^22 polls (seconds)
+    assert 0 <= looks[1] <= 65536, "the launch's second wait should leave at its first look at the abort word"
+    # a tensor-core kernel launched BEFORE the word is polled still runs to completion and is right
+    g = torch.Generator().manual_seed(1)
+    a = (torch.randn(256, 128, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(192, 128, generator=g) / 8).bfloat16()
+    bias = (torch.randn(192, generator=g) * 0.5).bfloat16()
+    got = ops.gemm_bias_gelu_tanh(a.cuda(), w.cuda(), bias.cuda()).cpu().float()
+    ref = tessiq0.gemm_bias_gelu_tanh(a, w, bias).float()
+    torch.testing.assert_close(got, ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
+    with pytest.raises(K.DeviceWaitError, match="self test"):
+        K.check_status(0)
+    K.check_status(0)                                             # read and cleared: nothing left to report
+    assert lib.tq_selftest_bounded_wait(0, None, 0, looks) == abi.TQ_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_global_reduction_partial_and_finish_on_one_gpu(abi, dtype):
+    """The two kernels either side of the all-reduce (tq_reduce_partial_launch, tq_reduce_finish_launch),
+    with the exchange left out: on one GPU the partial is already the combined one."""
+    lib, check = abi.lib, abi.check
+    code = {torch.float32: abi.F32, torch.bfloat16: abi.BF16, torch.float16: abi.F16}[dtype]
+    n = (1 << 22) + 5
+    x = (torch.rand(n, generator=torch.Generator().manual_seed(2)) * 2 - 1).to(dtype)
+    with_nan = x.clone()
+    with_nan[n // 3] = float("nan")
+    need = ctypes.c_size_t()
+    check(lib.tq_reduce_workspace_bytes(abi.SUM, code, 1, n, 1, 0, ctypes.byref(need)))
+    scratch = torch.empty(max(need.value, 16), dtype=torch.uint8, device="cuda")
+    partial = torch.empty(2, dtype=torch.float32, device="cuda")
+    out = torch.empty((), dtype=dtype, device="cuda")
+
+    def run(op, tensor, total):
+        d = tensor.cuda()
+        check(lib.tq_reduce_partial_launch(op, code, d.data_ptr(), partial.data_ptr(), n, scratch.data_ptr(), scratch.numel(), 0, None))
+        check(lib.tq_reduce_finish_launch(op, code, partial.data_ptr(), out.data_ptr(), total, 0, None))
+        torch.cuda.synchronize()
+        return out.cpu(), partial.cpu()
+
+    truth = x.double().sum().item()
+    budget = 1e-5 * x.double().abs().sum().item()
+    got, words = run(abi.SUM, x, n)
+    assert abs(words[0].item() - truth) <= budget and words[1].item() == 0.0       # the partial keeps the f32 sum
+    assert abs(got.double().item() - truth) <= budget + abs(truth) * (2.0**-8 if dtype == torch.bfloat16 else 2.0**-10 if dtype == torch.float16 else 0)
+    got, _ = run(abi.MEAN, x, 3 * n)                                               # a third of a larger tensor
+    assert abs(got.double().item() - truth / (3 * n)) <= budget / (3 * n) + 1e-6
+    got, words = run(abi.AMAX, x, n)
+    assert got.item() == x.amax().item() and words[1].item() == 0.0
+    got, words = run(abi.AMIN, x, n)
+    assert got.item() == x.amin().item() and words[1].item() == 0.0
+    got, words = run(abi.AMAX, with_nan, n)
+    assert torch.isnan(got).item() and words[0].item() == float("-inf") and words[1].item() == 1.0
+    got, words = run(abi.AMIN, with_nan, n)
+    assert torch.isnan(got).item() and words[0].item() == float("inf") and words[1].item() == -1.0
+    assert lib.tq_reduce_partial_launch(abi.ARGMAX, code, x.cuda().data_ptr(), partial.data_ptr(), n, scratch.data_ptr(), scratch.numel(), 0, None) \
+        == abi.TQ_UNSUPPORTED
+
+
+def _two_gpu_worker(rank, world, port, results):
+    import os
+    import sys
+    from pathlib import Path
+
+    import torch.distributed as dist
+
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    try:
+        from tessiq_b200 import sharding
+
+        n = 1 << 20
+        parts = [torch.rand(n, generator=torch.Generator().manual_seed(40 + r)) * 2 - 1 for r in range(world)]
+        parts[world - 1][77] = float("nan")
+        whole = torch.cat(parts)
+        clean = whole.clone()
+        clean[(world - 1) * n + 77] = 0.25
+        mine_nan = parts[rank].cuda()
+        mine = mine_nan.clone()
+        if rank == world - 1:
+            mine[77] = 0.25
+        out = {}
+        for transport in ("default", None):                    # the library's own NCCL communicator, then torch.distributed's
+            got = {op: sharding.global_reduce(op, mine, offset=rank * n, total=world * n, comm=transport).cpu() for op in ("sum", "mean", "amax", "amin")}
+            nan_max = sharding.global_reduce("amax", mine_nan, offset=rank * n, total=world * n, comm=transport).cpu()
+            torch.cuda.synchronize()
+            out[str(transport)] = (abs(got["sum"].double().item() - clean.double().sum().item()) <= 1e-5 * clean.abs().sum().item()
+                                   and abs(got["mean"].double().item() - clean.double().mean().item()) <= 1e-7
+                                   and got["amax"].item() == clean.amax().item() and got["amin"].item() == clean.amin().item()
+                                   and bool(torch.isnan(nan_max).item()))
+        out["native_comm"] = sharding.default_comm(rank) is not None
+        results[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_global_reductions_over_two_gpus():
+    """config 5c over two ranks, one process per GPU, the exchange through the library's own NCCL
+    communicator (tq_allreduce_scalar) and, for comparison, through torch.distributed."""
+    import torch.multiprocessing as mp
+
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_two_gpu_worker, args=(2, 29611, results), nprocs=2, join=True)
+    assert len(results) == 2
+    for rank in range(2):
+        assert results[rank]["native_comm"], "the library's NCCL communicator could not be made"
+        assert results[rank]["default"] and results[rank]["None"], results[rank]

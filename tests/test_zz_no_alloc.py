@@ -48,18 +48,17 @@ def static_reduce(abi, op, x, out, outer, reduce, inner):
 
 
 CASES = [
-    # (op name, dtype, outer, reduce, inner): each is split over CTAs and finished by a ticket.
-    # How much scratch a case needs depends on the library's launch plan, so the test asks
-    # (tq_reduce_workspace_bytes) and uses the cases that need some and fit the built-in array.
+    # (op name, dtype, outer, reduce, inner): each is split over CTAs and finished by a ticket, and
+    # needs some scratch but no more than the built-in array holds (the test asserts both).
     ("SUM", torch.float32, 1, (1 << 22) + 3, 1),
     ("AMAX", torch.float32, 1, 1_000_003, 1),
     ("ARGMAX", torch.bfloat16, 3, 1 << 21, 1),
-    ("SUM", torch.float32, 1, 32768, 1024),
-    ("SUM", torch.float32, 1, 32768, 256),
-    ("ARGMAX", torch.float32, 2, 20000, 128),
+    ("SUM", torch.float32, 1, 20000, 64),
+    ("SUM", torch.float32, 1, 16384, 128),
     ("ARGMAX", torch.float32, 1, 20000, 64),
-    ("MEAN", torch.bfloat16, 1, 16384, 512),
+    ("ARGMAX", torch.float32, 1, 40000, 32),
     ("MEAN", torch.bfloat16, 1, 16384, 128),
+    ("MEAN", torch.bfloat16, 1, 40000, 32),
 ]
 
 
@@ -77,8 +76,7 @@ def test_enough_cases_exercise_the_scratch(abi):
 @pytest.mark.parametrize("op_name, dtype, outer, reduce, inner", CASES)
 def test_static_scratch_matches_caller_scratch_twice_in_a_row(abi, op_name, dtype, outer, reduce, inner):
     op = getattr(abi, op_name)
-    if not 0 < scratch_need(abi, op, dtype, outer, reduce, inner) <= abi.STATIC_SCRATCH_BYTES:
-        pytest.skip("under the current launch plan this case needs no scratch, or more than the built-in array holds")
+    assert 0 < scratch_need(abi, op, dtype, outer, reduce, inner) <= abi.STATIC_SCRATCH_BYTES, "pick another case: the launch plan changed"
     out_dtype = torch.int64 if op_name == "ARGMAX" else dtype
     g = torch.Generator().manual_seed(outer * 31 + inner)
     first = (torch.rand(outer, reduce, inner, generator=g) * 2 - 1).to(dtype).cuda()
@@ -99,6 +97,32 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row(abi, op_name, dtyp
         truth = x.double().sum(1) / (reduce if op_name == "MEAN" else 1)
         budget = 1e-5 * x.double().abs().sum(1).max().item() / (reduce if op_name == "MEAN" else 1) + 2.0**-8 * truth.abs().max().item() * (dtype == torch.bfloat16)
         assert (got.cpu().double() - truth).abs().max().item() <= budget
+
+
+def test_static_entry_point_is_recorded_like_every_other_launch(abi):
+    """Between tq_recipe_begin_recording and tq_recipe_end_recording the call is appended to the recipe,
+    not launched; the replay resolves the built-in array for the device it runs on."""
+    x = (torch.rand(1, 20000, 64, generator=torch.Generator().manual_seed(3)) * 2 - 1).cuda()
+    out = torch.full((1, 64), -7.0, device="cuda")
+    recipe = ctypes.c_void_p()
+    abi.check(abi.lib.tq_recipe_create(ctypes.byref(recipe)))
+    abi.check(abi.lib.tq_recipe_begin_recording(recipe))
+    try:
+        abi.check(abi.lib.tq_reduce_launch_static(abi.SUM, abi.F32, x.data_ptr(), out.data_ptr(), 1, 20000, 64, 0, None))
+    finally:
+        abi.check(abi.lib.tq_recipe_end_recording(recipe))
+    torch.cuda.synchronize()
+    assert abi.lib.tq_recipe_steps(recipe) == 1
+    assert (out == -7.0).all(), "recording must not launch"
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(2):
+        out.fill_(-7.0)
+        abi.check(abi.lib.tq_recipe_run(recipe, 0, ctypes.c_void_p(stream)))
+        torch.cuda.synchronize()
+        expected = torch.empty(1, 64, device="cuda")
+        reference_reduce(abi, abi.SUM, x, expected, 1, 20000, 64)
+        assert torch.equal(out, expected)
+    abi.check(abi.lib.tq_recipe_destroy(recipe))
 
 
 def test_reductions_without_scratch_need_none(abi):
