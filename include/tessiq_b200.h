@@ -495,6 +495,29 @@ tq_status tq_recipe_run(const tq_recipe* recipe, int32_t device, void* stream);
  * `stream` first. */
 tq_status tq_status_poll(int32_t device, void* stream, int32_t* device_status);
 
+/* ---- One runtime over several GPUs of one process ------------------------------------------------
+ * Replaces the reference's device layer for this path (csrc/tessiq/runtime/cuda_device.cpp:34-147: one
+ * blocking copy stream per device, everything else on the legacy stream; allocator.cpp:56-108;
+ * registry.cpp:50-54: tessiq:k is CUDA ordinal k-1). tq_runtime_create checks the list the way the
+ * reference checks its `device` option (python/tessiq/backend.py:95-104: unknown entries are an
+ * invalid-argument error, not a fallback) and gives every listed GPU a non-blocking stream, a slice
+ * of arena memory (a bump pointer: tq_runtime_alloc hands out 256-byte-aligned ranges until
+ * tq_runtime_release rewinds the slice) and an event. A sharded executor enqueues the same kernels on
+ * every GPU's stream; tq_runtime_fork orders the other streams after one GPU's (inputs scattered),
+ * tq_runtime_join orders one GPU's stream after all the others (results gathered). */
+typedef struct tq_runtime tq_runtime;
+tq_status tq_runtime_create(const int32_t* devices, int32_t count, size_t arena_bytes_per_device, tq_runtime** runtime);
+tq_status tq_runtime_destroy(tq_runtime* runtime);
+int32_t tq_runtime_device_count(const tq_runtime* runtime);
+tq_status tq_runtime_device(const tq_runtime* runtime, int32_t index, int32_t* device);
+tq_status tq_runtime_stream(const tq_runtime* runtime, int32_t index, void** stream);
+tq_status tq_runtime_alloc(tq_runtime* runtime, int32_t index, size_t bytes, void** pointer);
+tq_status tq_runtime_release(tq_runtime* runtime, int32_t index);
+size_t tq_runtime_arena_used(const tq_runtime* runtime, int32_t index);
+tq_status tq_runtime_fork(tq_runtime* runtime, int32_t from);
+tq_status tq_runtime_join(tq_runtime* runtime, int32_t onto);
+tq_status tq_runtime_synchronize(tq_runtime* runtime);
+
 /* ---- Global reductions over the GPUs of one box ------------------------------------------------
  * The reference has no multi-GPU execution (one target device per recipe,
  * python/tessiq/recipe.py:117-161); these entry points are what its recipes shard under: a reduction

@@ -99,6 +99,17 @@ SIGNATURES = {
     "tq_status_poll": (c_int32, [c_int32, c_void_p, POINTER(c_int32)]),
     "tq_status_detail": (c_int32, [c_int32, c_void_p, POINTER(c_int32), c_int32]),
     "tq_selftest_bounded_wait": (c_int32, [c_int32, c_void_p, c_int32, POINTER(c_int32)]),
+    "tq_runtime_create": (c_int32, [POINTER(c_int32), c_int32, c_size_t, POINTER(c_void_p)]),
+    "tq_runtime_destroy": (c_int32, [c_void_p]),
+    "tq_runtime_device_count": (c_int32, [c_void_p]),
+    "tq_runtime_device": (c_int32, [c_void_p, c_int32, POINTER(c_int32)]),
+    "tq_runtime_stream": (c_int32, [c_void_p, c_int32, POINTER(c_void_p)]),
+    "tq_runtime_alloc": (c_int32, [c_void_p, c_int32, c_size_t, POINTER(c_void_p)]),
+    "tq_runtime_release": (c_int32, [c_void_p, c_int32]),
+    "tq_runtime_arena_used": (c_size_t, [c_void_p, c_int32]),
+    "tq_runtime_fork": (c_int32, [c_void_p, c_int32]),
+    "tq_runtime_join": (c_int32, [c_void_p, c_int32]),
+    "tq_runtime_synchronize": (c_int32, [c_void_p]),
     "tq_comm_unique_id": (c_int32, [c_void_p, c_size_t]),
     "tq_comm_create": (c_int32, [c_void_p, c_size_t, c_int32, c_int32, c_int32, POINTER(c_void_p)]),
     "tq_comm_create_all": (c_int32, [POINTER(c_int32), c_int32, POINTER(c_void_p)]),

@@ -139,6 +139,19 @@ struct tq_arena {
   char* base;
 };
 
+// One handle over several GPUs of one process: per GPU a non-blocking stream, an arena slice with a
+// bump pointer, and an event for joins.
+struct tq_runtime {
+  struct Slot {
+    int32_t device;
+    cudaStream_t stream;
+    cudaEvent_t event;
+    tq_arena arena;
+    size_t used;
+  };
+  std::vector<Slot> slots;
+};
+
 extern "C" {
 
 int32_t tq_abi_version(void) { return 1000; }
@@ -211,6 +224,139 @@ tq_status tq_arena_at(const tq_arena* arena, size_t offset, size_t bytes, void**
 }
 
 size_t tq_arena_bytes(const tq_arena* arena) { return arena ? arena->bytes : 0; }
+
+tq_status tq_runtime_create(const int32_t* devices, int32_t count, size_t arena_bytes_per_device, tq_runtime** runtime) {
+  TQ_REQUIRE(runtime != nullptr, TQ_INVALID_ARGUMENT, "runtime out-pointer is null");
+  TQ_REQUIRE(devices != nullptr && count >= 1 && count <= 64, TQ_INVALID_ARGUMENT, "between 1 and 64 devices");
+  const int32_t visible = tq_device_count();
+  for (int i = 0; i < count; ++i) {
+    TQ_REQUIRE(devices[i] >= 0 && devices[i] < visible, TQ_INVALID_ARGUMENT, "device %d is not one of the %d visible GPUs", devices[i], visible);
+    for (int j = 0; j < i; ++j) TQ_REQUIRE(devices[j] != devices[i], TQ_INVALID_ARGUMENT, "device %d is listed twice", devices[i]);
+  }
+  tq_runtime* made = new tq_runtime();
+  for (int i = 0; i < count; ++i) {
+    tq_runtime::Slot slot = {devices[i], nullptr, nullptr, {devices[i], 0, nullptr}, 0};
+    tq_status status = tq::use_device(devices[i]);
+    if (status == TQ_OK && cudaStreamCreateWithFlags(&slot.stream, cudaStreamNonBlocking) != cudaSuccess) status = tq::fail(TQ_EXTERNAL, "no stream on device %d", devices[i]);
+    if (status == TQ_OK && cudaEventCreateWithFlags(&slot.event, cudaEventDisableTiming) != cudaSuccess) status = tq::fail(TQ_EXTERNAL, "no event on device %d", devices[i]);
+    if (status == TQ_OK && arena_bytes_per_device > 0) {
+      void* base = nullptr;
+      if (cudaMalloc(&base, arena_bytes_per_device) != cudaSuccess) {
+        cudaGetLastError();
+        status = tq::fail(TQ_RESOURCE_EXHAUSTED, "device %d has no %zu bytes for its arena slice", devices[i], arena_bytes_per_device);
+      } else {
+        slot.arena.bytes = arena_bytes_per_device;
+        slot.arena.base = static_cast<char*>(base);
+      }
+    }
+    made->slots.push_back(slot);
+    if (status != TQ_OK) {
+      const std::string kept = tq_last_error();
+      tq_runtime_destroy(made);
+      tq::set_error(kept.c_str());
+      return status;
+    }
+  }
+  *runtime = made;
+  return TQ_OK;
+}
+
+tq_status tq_runtime_destroy(tq_runtime* runtime) {
+  if (runtime == nullptr) return TQ_OK;
+  for (tq_runtime::Slot& slot : runtime->slots) {
+    if (tq::use_device(slot.device) != TQ_OK) continue;
+    if (slot.stream != nullptr) {
+      cudaStreamSynchronize(slot.stream);
+      cudaStreamDestroy(slot.stream);
+    }
+    if (slot.event != nullptr) cudaEventDestroy(slot.event);
+    if (slot.arena.base != nullptr) cudaFree(slot.arena.base);
+  }
+  delete runtime;
+  return TQ_OK;
+}
+
+int32_t tq_runtime_device_count(const tq_runtime* runtime) { return runtime ? static_cast<int32_t>(runtime->slots.size()) : 0; }
+
+#define TQ_SLOT(runtime, index)                                                                                       \
+  TQ_REQUIRE((runtime) != nullptr && (index) >= 0 && (index) < static_cast<int32_t>((runtime)->slots.size()), TQ_INVALID_ARGUMENT, \
+             "slot %d is not one of the runtime's devices", static_cast<int>(index))
+
+tq_status tq_runtime_device(const tq_runtime* runtime, int32_t index, int32_t* device) {
+  TQ_SLOT(runtime, index);
+  TQ_REQUIRE(device != nullptr, TQ_INVALID_ARGUMENT, "device out-pointer is null");
+  *device = runtime->slots[index].device;
+  return TQ_OK;
+}
+
+tq_status tq_runtime_stream(const tq_runtime* runtime, int32_t index, void** stream) {
+  TQ_SLOT(runtime, index);
+  TQ_REQUIRE(stream != nullptr, TQ_INVALID_ARGUMENT, "stream out-pointer is null");
+  *stream = runtime->slots[index].stream;
+  return TQ_OK;
+}
+
+tq_status tq_runtime_alloc(tq_runtime* runtime, int32_t index, size_t bytes, void** pointer) {
+  TQ_SLOT(runtime, index);
+  TQ_REQUIRE(pointer != nullptr, TQ_INVALID_ARGUMENT, "pointer out-pointer is null");
+  tq_runtime::Slot& slot = runtime->slots[index];
+  const size_t start = (slot.used + 255) / 256 * 256;
+  TQ_REQUIRE(start <= slot.arena.bytes && bytes <= slot.arena.bytes - start, TQ_RESOURCE_EXHAUSTED,
+             "device %d's arena slice holds %zu bytes, %zu are taken and %zu more were asked for", slot.device, slot.arena.bytes, start, bytes);
+  *pointer = slot.arena.base + start;
+  slot.used = start + bytes;
+  return TQ_OK;
+}
+
+tq_status tq_runtime_release(tq_runtime* runtime, int32_t index) {
+  TQ_SLOT(runtime, index);
+  runtime->slots[index].used = 0;
+  return TQ_OK;
+}
+
+size_t tq_runtime_arena_used(const tq_runtime* runtime, int32_t index) {
+  return (runtime != nullptr && index >= 0 && index < static_cast<int32_t>(runtime->slots.size())) ? runtime->slots[index].used : 0;
+}
+
+tq_status tq_runtime_join(tq_runtime* runtime, int32_t onto) {
+  TQ_SLOT(runtime, onto);
+  // what every other GPU's stream has queued so far happens before whatever `onto`'s stream gets next
+  for (size_t i = 0; i < runtime->slots.size(); ++i) {
+    if (static_cast<int32_t>(i) == onto) continue;
+    tq_runtime::Slot& slot = runtime->slots[i];
+    if (tq_status s = tq::use_device(slot.device)) return s;
+    TQ_CUDA(cudaEventRecord(slot.event, slot.stream));
+  }
+  tq_runtime::Slot& target = runtime->slots[onto];
+  if (tq_status s = tq::use_device(target.device)) return s;
+  for (size_t i = 0; i < runtime->slots.size(); ++i) {
+    if (static_cast<int32_t>(i) != onto) TQ_CUDA(cudaStreamWaitEvent(target.stream, runtime->slots[i].event, 0));
+  }
+  return TQ_OK;
+}
+
+tq_status tq_runtime_fork(tq_runtime* runtime, int32_t from) {
+  TQ_SLOT(runtime, from);
+  // what `from`'s stream has queued so far happens before whatever the other GPUs' streams get next
+  tq_runtime::Slot& source = runtime->slots[from];
+  if (tq_status s = tq::use_device(source.device)) return s;
+  TQ_CUDA(cudaEventRecord(source.event, source.stream));
+  for (size_t i = 0; i < runtime->slots.size(); ++i) {
+    if (static_cast<int32_t>(i) == from) continue;
+    if (tq_status s = tq::use_device(runtime->slots[i].device)) return s;
+    TQ_CUDA(cudaStreamWaitEvent(runtime->slots[i].stream, source.event, 0));
+  }
+  return TQ_OK;
+}
+
+tq_status tq_runtime_synchronize(tq_runtime* runtime) {
+  TQ_REQUIRE(runtime != nullptr, TQ_INVALID_ARGUMENT, "null runtime");
+  for (tq_runtime::Slot& slot : runtime->slots) {
+    if (tq_status s = tq::use_device(slot.device)) return s;
+    TQ_CUDA(cudaStreamSynchronize(slot.stream));
+  }
+  return TQ_OK;
+}
 
 tq_status tq_recipe_create(tq_recipe** recipe) {
   TQ_REQUIRE(recipe != nullptr, TQ_INVALID_ARGUMENT, "recipe out-pointer is null");

@@ -229,3 +229,38 @@ def test_cubin_cache_survives_the_process(tmp_path):
     assert third.stdout.split() == ["0", "1", "1"]
     off = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env={**env, "TESSIQ_CACHE_DIR": ""})
     assert off.stdout.split() == ["0", "1", "0"]              # disabled: compiled, nothing stored
+
+
+def test_registration_table_is_in_the_references_format():
+    """tessiq_b200/ops_b200.toml: rows for the operations this library adds, in the format of the
+    reference's ops.toml and under its generator's rules (tools/gen_ops.py:66-88, restated here), so
+    that the file can be appended to ops.toml as it is; and every row names something the library
+    exposes."""
+    import tomllib
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    with (root / "tessiq_b200" / "ops_b200.toml").open("rb") as handle:
+        rows = tomllib.load(handle)["op"]
+    categories = {"elementwise", "reduction", "movement", "matmul", "copy", "convolution"}
+    dtypes = {"f16", "bf16", "f32", "f64", "i1", "i32", "i64"}
+    for op in rows:
+        assert {"name", "aten", "category", "arity", "kernel"} <= set(op), op
+        assert op["category"] in categories, op["name"]
+        assert bool(op.get("expression")) == (op["category"] == "elementwise"), op["name"]
+        assert set(op.get("dtypes", [])) <= dtypes and op.get("dtypes", ["f32"]), op["name"]
+    spelled = [name for op in rows for name in (op["name"], *op["aten"])]
+    assert len(set(spelled)) == len(spelled), "the same spelling appears twice"
+    from tessiq_b200 import ops
+
+    known = ops.UNARY | ops.BINARY | {"where", "cast"}
+    for op in rows:
+        if op["category"] == "elementwise":
+            assert op["name"] in known, op["name"]
+        else:
+            assert hasattr(ops, {"layer_norm": "native_layer_norm"}.get(op["name"], op["name"])), op["name"]
+    reference = Path("/root/reference/ops.toml")
+    if reference.exists():   # appended to the reference's table, no spelling collides
+        with reference.open("rb") as handle:
+            theirs = [name for op in tomllib.load(handle)["op"] for name in (op["name"], *op["aten"])]
+        assert not set(theirs) & set(spelled)
