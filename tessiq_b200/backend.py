@@ -43,7 +43,7 @@ from ._lib import Declined
 
 aten = torch.ops.aten
 
-OPTIONS = {"device", "rewrites", "math", "cuda_graph", "native"}
+OPTIONS = {"device", "devices", "shard", "rewrites", "math", "cuda_graph", "native"}
 
 UNARY = {
     aten.abs.default: "abs", aten.neg.default: "neg", aten.relu.default: "relu", aten.sigmoid.default: "sigmoid",
@@ -796,7 +796,10 @@ def _decompositions():
 def compile_graph(gm: fx.GraphModule, example_inputs, *, mode: str | None = None, options: dict | None = None):
     """The dynamo backend. `options`: "device" (a CUDA device, default: the inputs'), "math"
     ("fast" | "precise"), "cuda_graph" (bool: replay the recipe as a CUDA graph once shapes
-    repeat), "native" (bool: record the launches once and replay them with tq_recipe_run), "rewrites" (accepted for compatibility; the fusions here need no rewrite names)."""
+    repeat), "native" (bool: record the launches once and replay them with tq_recipe_run), "rewrites" (accepted for compatibility; the
+    fusions here need no rewrite names), "devices" (a list of CUDA ordinals: the batch is split along dim 0 over one runtime's GPUs,
+    checked like the reference checks its `device` option, python/tessiq/backend.py:95-104), "shard" (with "devices": the positions of
+    the arguments that carry the batch; default every tensor argument that is not a module parameter)."""
     if mode not in (None, "default"):
         raise ValueError(f"tessiq has no compile mode {mode!r}")
     options = dict(options or {})
@@ -806,6 +809,16 @@ def compile_graph(gm: fx.GraphModule, example_inputs, *, mode: str | None = None
     math_mode = options.get("math", "fast")
     if math_mode not in ("fast", "precise"):
         raise ValueError(f"option math={math_mode!r}: expected 'fast' or 'precise'")
+    devices = None
+    if "devices" in options:
+        from .runtime import check_devices
+
+        if "device" in options:
+            raise ValueError("options 'device' and 'devices' exclude one another")
+        devices = check_devices(options["devices"])   # a bad list fails the torch.compile call, not the first run
+    shard = options.get("shard")
+    if shard is not None and (devices is None or not isinstance(shard, (list, tuple)) or not all(isinstance(p, int) and not isinstance(p, bool) and p >= 0 for p in shard)):
+        raise ValueError(f"option shard={shard!r}: a list of argument positions, together with 'devices'")
     from torch._dynamo.backends.common import aot_autograd
     from functorch.compile import make_boxed_func
 
@@ -819,6 +832,16 @@ def compile_graph(gm: fx.GraphModule, example_inputs, *, mode: str | None = None
         return make_boxed_func(lambda *args: runner.run(*args))
 
     fn = aot_autograd(fw_compiler=compile_forward, decompositions=_decompositions())(gm, example_inputs)
+    if devices is not None and len(devices) > 1:
+        # the batch is split over the GPUs of one runtime: the arguments named by `shard` (default: every
+        # tensor argument that is not a parameter of the module) along dim 0, the others replicated
+        from .runtime import Runtime, ShardedRunner
+
+        positions = list(shard) if shard is not None else [i for i, a in enumerate(example_inputs)
+                                                           if isinstance(a, torch.Tensor) and not isinstance(a, torch.nn.Parameter) and a.dim() > 0]
+        single = fn
+        fn = ShardedRunner(Runtime(devices), single, positions)
+        fn.devices = devices
     fn.recipes = compiled  # for tests and reports: which kernels a graph became
     fn.runners = runners
     return fn

@@ -516,7 +516,8 @@ extern "C" tq_status tq_attention_launch(tq_dtype dtype, const void* q, const vo
              TQ_UNSUPPORTED, "Q, K and V must be 16-byte aligned with positive strides that are multiples of 8 elements (TMA's rules)");
   TQ_REQUIRE(tq::aligned_to(out, 2) && out_strides[0] >= 0 && out_strides[1] >= 0 && out_strides[2] >= 0, TQ_INVALID_ARGUMENT,
              "misaligned result or negative result stride");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   const tq::WaitStatus status = tq::wait_status_for(device);
   TQ_REQUIRE(status.sticky != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
 

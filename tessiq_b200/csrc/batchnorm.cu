@@ -107,7 +107,8 @@ extern "C" tq_status tq_batch_norm_eval_launch(tq_dtype dtype, tq_dtype param_dt
   TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");
   TQ_REQUIRE(running_mean != nullptr && running_var != nullptr, TQ_UNSUPPORTED,
              "eval BatchNorm without running statistics has no kernel");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
 #define TQ_BN(T, P) return tq::run<T, P>(in, weight, bias, running_mean, running_var, out, n, c, inner, eps, cuda_stream)
   if (dtype == TQ_F32 && param_dtype == TQ_F32) TQ_BN(float, float);

@@ -97,7 +97,8 @@ tq_status tq_comm_create(const void* id, size_t bytes, int32_t rank, int32_t wor
   TQ_REQUIRE(id != nullptr && bytes >= sizeof(ncclUniqueId), TQ_INVALID_ARGUMENT, "the id buffer must hold %zu bytes", sizeof(ncclUniqueId));
   TQ_REQUIRE(world >= 1 && rank >= 0 && rank < world, TQ_INVALID_ARGUMENT, "rank %d is not in a world of %d", rank, world);
   TQ_REQUIRE(tq::nccl().ok, TQ_NOT_FOUND, "NCCL (libnccl.so.2) is not available in this process");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   ncclUniqueId unique;
   memcpy(&unique, id, sizeof(unique));
   ncclComm_t made = nullptr;
@@ -149,7 +150,8 @@ tq_status tq_allreduce_scalar(tq_comm* comm, void* buffer, int64_t count, tq_dty
     case TQ_AMIN: how = ncclMin; break;
     default: return tq::fail(TQ_UNSUPPORTED, "an all-reduce sums, takes the maximum or the minimum; not operation %d", op);
   }
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   TQ_NCCL(tq::nccl().AllReduce(buffer, buffer, static_cast<size_t>(count), type, how, comm->comm, static_cast<cudaStream_t>(stream)));
   return TQ_OK;
 }
@@ -160,7 +162,8 @@ tq_status tq_reduce_finish_launch(tq_reduce_op op, tq_dtype dtype, const void* p
   TQ_REQUIRE(op == TQ_SUM || op == TQ_MEAN || op == TQ_AMAX || op == TQ_AMIN, TQ_UNSUPPORTED, "no global finish for operation %d", op);
   TQ_REQUIRE(partial != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null partial or output");
   TQ_REQUIRE(op != TQ_MEAN || total_count > 0, TQ_INVALID_ARGUMENT, "a mean over no elements");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
   const float* words = static_cast<const float*>(partial);
   const double count = static_cast<double>(total_count);

@@ -36,6 +36,29 @@ tq_status fail(tq_status code, const char* format, ...) __attribute__((format(pr
 // Makes `device` current for the calling thread. Cheap when it already is.
 tq_status use_device(int32_t device);
 
+// Makes `device` current for the rest of the enclosing block and puts the caller's device back at
+// its end: an entry point must not leave the thread on another GPU than it found it on (PyTorch
+// and every other user of the runtime API take the thread's current device as theirs).
+class DeviceScope {
+ public:
+  explicit DeviceScope(int32_t device) {
+    if (cudaGetDevice(&previous_) != cudaSuccess) previous_ = -1;
+    status_ = use_device(device);
+    changed_ = status_ == TQ_OK && previous_ >= 0 && previous_ != device;
+  }
+  ~DeviceScope() {
+    if (changed_) cudaSetDevice(previous_);
+  }
+  DeviceScope(const DeviceScope&) = delete;
+  DeviceScope& operator=(const DeviceScope&) = delete;
+  tq_status status() const { return status_; }
+
+ private:
+  int previous_ = -1;
+  tq_status status_ = TQ_OK;
+  bool changed_ = false;
+};
+
 // Number of SMs of `device` (cached).
 int sm_count(int32_t device);
 

@@ -1097,7 +1097,8 @@ tq_status tq_fused_launch(const tq_fused* kernel, const void* const* inputs, voi
     }
   }
 
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   if (tq_status s = tq::load(kernel->module.get())) return s;
 
   const int width = vector_path ? vec : 1;

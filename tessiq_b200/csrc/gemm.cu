@@ -738,7 +738,8 @@ extern "C" tq_status tq_gemm_bias_act_residual_launch(tq_dtype dtype, tq_activat
   TQ_REQUIRE(tq::aligned_to(c, 2) && (bias == nullptr || tq::aligned_to(bias, 2)), TQ_INVALID_ARGUMENT, "misaligned result or bias");
   TQ_REQUIRE(residual == nullptr || (tq::aligned_to(residual, 2) && ldr >= n), TQ_INVALID_ARGUMENT,
              "misaligned residual, or its leading dimension is smaller than a row");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   const tq::WaitStatus status = tq::wait_status_for(device);
   TQ_REQUIRE(status.sticky != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
 

@@ -382,7 +382,8 @@ extern "C" tq_status tq_pack_launch(int32_t element_bytes, int32_t rank, const i
              TQ_UNSUPPORTED, "elements of %d bytes have no pack kernel", element_bytes);
   TQ_REQUIRE(tq::aligned_to(src, element_bytes) && tq::aligned_to(dst, element_bytes), TQ_INVALID_ARGUMENT,
              "pointers must be aligned to the element width");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   const tq::View view = tq::collapse(rank, sizes, strides);
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
   switch (element_bytes) {

@@ -926,7 +926,8 @@ tq_status tq_reduce_launch(tq_reduce_op op, tq_dtype dtype, const void* in, void
   TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");
   const int size = tq::dtype_size(dtype);
   TQ_REQUIRE(tq::aligned_to(in, size), TQ_INVALID_ARGUMENT, "input pointer is not aligned to its element type");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   tq::Plan p = tq::plan(op, dtype, outer, reduce, inner, device,
                         inner == 1 ? 16 : tq::column_vec_bytes(in, inner, size));
   const size_t need = p.partial_bytes + p.ticket_bytes;
@@ -956,7 +957,8 @@ tq_status tq_reduce_partial_launch(tq_reduce_op op, tq_dtype dtype, const void* 
   TQ_REQUIRE(in != nullptr && partial != nullptr && tq::aligned_to(partial, 8), TQ_INVALID_ARGUMENT, "null input, or a partial that is not 8-byte aligned");
   const int size = tq::dtype_size(dtype);
   TQ_REQUIRE(tq::aligned_to(in, size), TQ_INVALID_ARGUMENT, "input pointer is not aligned to its element type");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   // the plan of the plain reduction over [1, count, 1]: same kernels, same scratch, another finish
   const tq::Plan p = tq::plan(op == TQ_MEAN ? TQ_SUM : op, dtype, 1, count, 1, device, 16);
   const size_t need = p.partial_bytes + p.ticket_bytes;
@@ -987,7 +989,8 @@ tq_status tq_reduce_launch_static(tq_reduce_op op, tq_dtype dtype, const void* i
   TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");
   const int size = tq::dtype_size(dtype);
   TQ_REQUIRE(tq::aligned_to(in, size), TQ_INVALID_ARGUMENT, "input pointer is not aligned to its element type");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   const tq::Plan p = tq::plan(op, dtype, outer, reduce, inner, device,
                               inner == 1 ? 16 : tq::column_vec_bytes(in, inner, size));
   const size_t need = p.partial_bytes + p.ticket_bytes;

@@ -515,7 +515,8 @@ tq_status tq_softmax_launch(tq_dtype dtype, tq_dtype out_dtype, const void* in, 
              "negative extent in [%lld, %lld, %lld]", (long long)outer, (long long)extent, (long long)inner);
   if (outer == 0 || extent == 0 || inner == 0) return TQ_OK;
   TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
   if (dtype == TQ_F32 && out_dtype == TQ_F32) return tq::run_softmax<float, float>(in, out, outer, extent, inner, cuda_stream);
   if (dtype == TQ_BF16 && out_dtype == TQ_BF16) return tq::run_softmax<__nv_bfloat16, __nv_bfloat16>(in, out, outer, extent, inner, cuda_stream);
@@ -538,7 +539,8 @@ tq_status tq_layer_norm_launch(tq_dtype dtype, const void* in, const void* weigh
   TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");
   TQ_REQUIRE(stat_dtype == dtype || (stat_dtype == TQ_F32 && dtype != TQ_F64), TQ_UNSUPPORTED,
              "LayerNorm statistics of type %s for %s rows have no kernel", tq::dtype_name(stat_dtype), tq::dtype_name(dtype));
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   tq::RowArgs args = {};
   args.in = in;
   args.out = out;
@@ -567,7 +569,8 @@ tq_status tq_rms_norm_launch(tq_dtype dtype, const void* in, const void* weight,
   if (rows == 0) return TQ_OK;
   TQ_REQUIRE(width > 0, TQ_UNSUPPORTED, "RMSNorm over no elements has no kernel");
   TQ_REQUIRE(in != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null input or output");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   tq::RowArgs args = {};
   args.in = in;
   args.out = out;
@@ -608,7 +611,8 @@ tq_status transposed_launch(int kind, tq_dtype dtype, const void* in, const void
   const int vec = 16 / tq::dtype_size(dtype);
   TQ_REQUIRE(rows % vec == 0 && cols % vec == 0 && tq::aligned_to(in, 16) && tq::aligned_to(out, 16), TQ_UNSUPPORTED,
              "the transposed normalisations need extents that are multiples of %d and 16-byte-aligned tensors", vec);
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   const size_t stats = stats_bytes(batch, cols);
   const size_t reduce_scratch = tq::slice_stats_workspace_bytes(kind, dtype, batch, rows, cols, device);
   const size_t need = std::max(stats + reduce_scratch, tq::panel_workspace_bytes(dtype, batch, rows, cols));

@@ -171,7 +171,8 @@ int32_t tq_device_count(void) {
 
 tq_status tq_stream_create(int32_t device, void** stream) {
   TQ_REQUIRE(stream != nullptr, TQ_INVALID_ARGUMENT, "stream out-pointer is null");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   cudaStream_t created = nullptr;
   TQ_CUDA(cudaStreamCreateWithFlags(&created, cudaStreamNonBlocking));
   *stream = created;
@@ -179,13 +180,15 @@ tq_status tq_stream_create(int32_t device, void** stream) {
 }
 
 tq_status tq_stream_destroy(int32_t device, void* stream) {
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   TQ_CUDA(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
   return TQ_OK;
 }
 
 tq_status tq_stream_synchronize(int32_t device, void* stream) {
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   TQ_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   return TQ_OK;
 }
@@ -193,7 +196,8 @@ tq_status tq_stream_synchronize(int32_t device, void* stream) {
 tq_status tq_arena_create(int32_t device, size_t bytes, tq_arena** arena) {
   TQ_REQUIRE(arena != nullptr, TQ_INVALID_ARGUMENT, "arena out-pointer is null");
   TQ_REQUIRE(bytes > 0, TQ_INVALID_ARGUMENT, "an arena of 0 bytes");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   void* base = nullptr;
   cudaError_t status = cudaMalloc(&base, bytes);
   if (status == cudaErrorMemoryAllocation) {
@@ -207,7 +211,8 @@ tq_status tq_arena_create(int32_t device, size_t bytes, tq_arena** arena) {
 
 tq_status tq_arena_destroy(tq_arena* arena) {
   if (arena == nullptr) return TQ_OK;
-  if (tq_status s = tq::use_device(arena->device)) return s;
+  tq::DeviceScope device_scope(arena->device);
+  if (tq_status s = device_scope.status()) return s;
   cudaError_t status = cudaFree(arena->base);
   delete arena;
   TQ_CUDA(status);
@@ -233,6 +238,7 @@ tq_status tq_runtime_create(const int32_t* devices, int32_t count, size_t arena_
     TQ_REQUIRE(devices[i] >= 0 && devices[i] < visible, TQ_INVALID_ARGUMENT, "device %d is not one of the %d visible GPUs", devices[i], visible);
     for (int j = 0; j < i; ++j) TQ_REQUIRE(devices[j] != devices[i], TQ_INVALID_ARGUMENT, "device %d is listed twice", devices[i]);
   }
+  tq::DeviceScope restore(devices[0]);   // the loop below moves from GPU to GPU: the caller's device comes back at the end
   tq_runtime* made = new tq_runtime();
   for (int i = 0; i < count; ++i) {
     tq_runtime::Slot slot = {devices[i], nullptr, nullptr, {devices[i], 0, nullptr}, 0};
@@ -263,6 +269,7 @@ tq_status tq_runtime_create(const int32_t* devices, int32_t count, size_t arena_
 
 tq_status tq_runtime_destroy(tq_runtime* runtime) {
   if (runtime == nullptr) return TQ_OK;
+  tq::DeviceScope restore(runtime->slots.empty() ? 0 : runtime->slots[0].device);
   for (tq_runtime::Slot& slot : runtime->slots) {
     if (tq::use_device(slot.device) != TQ_OK) continue;
     if (slot.stream != nullptr) {
@@ -320,6 +327,7 @@ size_t tq_runtime_arena_used(const tq_runtime* runtime, int32_t index) {
 
 tq_status tq_runtime_join(tq_runtime* runtime, int32_t onto) {
   TQ_SLOT(runtime, onto);
+  tq::DeviceScope restore(runtime->slots[onto].device);
   // what every other GPU's stream has queued so far happens before whatever `onto`'s stream gets next
   for (size_t i = 0; i < runtime->slots.size(); ++i) {
     if (static_cast<int32_t>(i) == onto) continue;
@@ -337,6 +345,7 @@ tq_status tq_runtime_join(tq_runtime* runtime, int32_t onto) {
 
 tq_status tq_runtime_fork(tq_runtime* runtime, int32_t from) {
   TQ_SLOT(runtime, from);
+  tq::DeviceScope restore(runtime->slots[from].device);
   // what `from`'s stream has queued so far happens before whatever the other GPUs' streams get next
   tq_runtime::Slot& source = runtime->slots[from];
   if (tq_status s = tq::use_device(source.device)) return s;
@@ -351,6 +360,7 @@ tq_status tq_runtime_fork(tq_runtime* runtime, int32_t from) {
 
 tq_status tq_runtime_synchronize(tq_runtime* runtime) {
   TQ_REQUIRE(runtime != nullptr, TQ_INVALID_ARGUMENT, "null runtime");
+  tq::DeviceScope restore(runtime->slots.empty() ? 0 : runtime->slots[0].device);
   for (tq_runtime::Slot& slot : runtime->slots) {
     if (tq_status s = tq::use_device(slot.device)) return s;
     TQ_CUDA(cudaStreamSynchronize(slot.stream));
@@ -396,7 +406,8 @@ tq_status tq_recipe_run(const tq_recipe* recipe, int32_t device, void* stream) {
 
 tq_status tq_status_poll(int32_t device, void* stream, int32_t* device_status) {
   TQ_REQUIRE(device_status != nullptr, TQ_INVALID_ARGUMENT, "status out-pointer is null");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   int32_t* word = tq::device_status_word(device);
   TQ_REQUIRE(word != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
@@ -411,7 +422,8 @@ tq_status tq_status_poll(int32_t device, void* stream, int32_t* device_status) {
 tq_status tq_selftest_bounded_wait(int32_t device, void* stream, int32_t polls, int32_t* looks) {
   TQ_REQUIRE(polls > 0 && polls <= (1 << 20), TQ_INVALID_ARGUMENT, "between 1 and 2^20 polls");
   TQ_REQUIRE(looks != nullptr, TQ_INVALID_ARGUMENT, "looks out-pointer is null");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   const tq::WaitStatus status = tq::wait_status_for(device);
   TQ_REQUIRE(status.sticky != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
@@ -425,7 +437,8 @@ tq_status tq_selftest_bounded_wait(int32_t device, void* stream, int32_t polls, 
 
 tq_status tq_status_detail(int32_t device, void* stream, int32_t* words, int32_t count) {
   TQ_REQUIRE(words != nullptr && count >= 0 && count <= 64, TQ_INVALID_ARGUMENT, "the status block holds 64 words");
-  if (tq_status s = tq::use_device(device)) return s;
+  tq::DeviceScope device_scope(device);
+  if (tq_status s = device_scope.status()) return s;
   int32_t* word = tq::device_status_word(device);
   TQ_REQUIRE(word != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);

@@ -407,3 +407,25 @@ def test_check_status_raises_once_on_a_reported_wait(monkeypatch):
         K.check_status(0)
     K.check_status(0)          # cleared by the first poll
     assert state["polls"] == 2
+
+
+def test_devices_option_is_checked_when_the_graph_is_compiled():
+    """`devices` must be a list of distinct visible CUDA ordinals; anything else is a ValueError at
+    compile time, as the reference's unknown `device` option is (python/tessiq/backend.py:95-104)."""
+    from tessiq_b200 import backend as B
+    from tessiq_b200.runtime import check_devices
+
+    assert check_devices([0, 2, 1], visible=4) == [0, 2, 1]
+    assert check_devices((torch.device("cuda", 1),), visible=2) == [1]
+    for bad in ("cuda:0", 0, [], [0, 0], [0, 7], [-1], [0.5], [True], [torch.device("cpu")], [torch.device("cuda")]):
+        with pytest.raises(ValueError):
+            check_devices(bad, visible=4)
+    gm = torch.fx.symbolic_trace(lambda x: x + 1)
+    with pytest.raises(ValueError, match="devices"):
+        B.compile_graph(gm, [torch.zeros(2)], options={"devices": "all"})
+    with pytest.raises(ValueError, match="exclude"):
+        B.compile_graph(gm, [torch.zeros(2)], options={"devices": [0], "device": 0})
+    with pytest.raises(ValueError, match="shard"):
+        B.compile_graph(gm, [torch.zeros(2)], options={"shard": [0]})
+    with pytest.raises(ValueError, match="unknown"):
+        B.compile_graph(gm, [torch.zeros(2)], options={"device_list": [0]})

@@ -204,3 +204,106 @@ def test_global_reductions_over_two_gpus():
     for rank in range(2):
         assert results[rank]["native_comm"], "the library's NCCL communicator could not be made"
         assert results[rank]["default"] and results[rank]["None"], results[rank]
+
+
+def test_runtime_handle_streams_and_arena_slices(abi):
+    """tq_runtime_*: one handle, per GPU a stream and an arena slice (here over one GPU, or two when
+    the box has them); buffers carved from the slice, kernels on the runtime's stream, fork / join."""
+    from tessiq_b200 import ops
+    from tessiq_b200.runtime import Runtime
+
+    devices = list(range(min(torch.cuda.device_count(), 2)))
+    runtime = Runtime(devices, arena_bytes=8 << 20)
+    assert len(runtime) == len(devices)
+    with pytest.raises(ValueError):
+        Runtime([0, 0])
+    with pytest.raises(ValueError):
+        Runtime([torch.cuda.device_count()])
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(256, 1000, generator=g)
+    results = []
+    runtime.fork(0)
+    for i, device in enumerate(devices):
+        with torch.cuda.device(device), torch.cuda.stream(runtime.torch_stream(i)):
+            mine = runtime.empty(i, x.shape, torch.float32)
+            assert mine.device.index == device and mine.data_ptr() % 256 == 0
+            mine.copy_(x, non_blocking=True)
+            results.append(ops.softmax(mine, -1))
+    assert runtime.used(0) >= x.numel() * 4
+    with pytest.raises(MemoryError):
+        runtime.alloc(0, 16 << 20)
+    runtime.join(0)
+    runtime.synchronize()
+    for r in results:
+        torch.testing.assert_close(r.cpu(), tessiq0.softmax(x, -1), rtol=1e-5, atol=1e-7)
+    runtime.release()
+    assert runtime.used(0) == 0
+    runtime.close()
+
+
+def test_scratch_that_grows_between_a_capture_and_its_replay_stays_valid():
+    """A captured CUDA graph holds the address of the scratch block it was captured with. When a later
+    launch on the same stream needs a larger block, the old one is kept (not handed back to PyTorch's
+    allocator), so the graph's replay still reduces into memory nobody else owns."""
+    from tessiq_b200 import kernel as K, ops
+
+    stream = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    K._workspaces.pop((0, stream.cuda_stream), None)    # PyTorch hands out pooled streams: start from no block for this one
+    x = torch.rand(1, 20000, 64, generator=torch.Generator().manual_seed(5)).cuda() * 2 - 1
+    out = torch.empty(1, 64, device="cuda")
+    with torch.cuda.stream(stream):
+        K.launch_reduce("sum", x, out, 1, 20000, 64, 0, stream.cuda_stream)     # warm: modules loaded, a small scratch block made
+        stream.synchronize()
+        first_block = K._workspaces[(0, stream.cuda_stream)]
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            K.launch_reduce("sum", x, out, 1, 20000, 64, 0, stream.cuda_stream)
+        # a launch that needs more scratch than the block holds (here: the transposed softmax of a 256 MiB
+        # tensor, whose persistent kernel keeps per-chunk partials): the block is replaced ...
+        wide = torch.randn(32768, 2048, device="cuda")
+        ops.softmax(wide.t(), -1)
+        assert K._workspaces[(0, stream.cuda_stream)].numel() > first_block.numel()
+        assert K._workspaces[(0, stream.cuda_stream)] is not first_block
+        assert any(block is first_block for block in K._outgrown[(0, stream.cuda_stream)])   # ... and kept
+        junk = [torch.full((1 << 20,), 7, dtype=torch.uint8, device="cuda") for _ in range(8)]   # what would have reused a freed block
+        out.zero_()
+        graph.replay()
+        stream.synchronize()
+    expected = x.double().sum(1)
+    assert (out.double() - expected).abs().max().item() <= 1e-5 * x.double().abs().sum(1).max().item()
+    del junk
+
+
+def _sharded_compile_worker():
+    import torch.nn.functional as F
+
+    from tessiq_b200 import backend
+
+    torch.manual_seed(0)
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.norm, self.fc, self.out = torch.nn.LayerNorm(256), torch.nn.Linear(256, 1024), torch.nn.Linear(1024, 256)
+
+        def forward(self, x):
+            return x + self.out(F.gelu(self.fc(self.norm(x)), approximate="tanh"))
+
+    block = Block().eval().bfloat16().cuda()
+    x = torch.randn(64, 128, 256).bfloat16().cuda()
+    with torch.no_grad():
+        expected = torch.compile(block, backend=backend.compile_graph)(x)
+        torch._dynamo.reset()
+        sharded = torch.compile(block, backend=lambda gm, inputs: backend.compile_graph(gm, inputs, options={"devices": [0, 1]}))
+        got = sharded(x)
+        again = sharded(x * 0.5)
+        torch.cuda.synchronize()
+    assert got.device.index == 0 and got.shape == expected.shape
+    torch.testing.assert_close(got.float(), expected.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(again.float(), torch.compile(block, backend=backend.compile_graph)(x * 0.5).float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_compiled_block_runs_sharded_over_two_gpus_of_one_process():
+    _sharded_compile_worker()
