@@ -171,6 +171,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) p.status.begin();   // this launch's abort word starts clear
     barrier_init(q_full, 1);
     for (int s = 0; s < kRing; ++s) {
       barrier_init(k_full(s), 1);
@@ -519,7 +520,7 @@ extern "C" tq_status tq_attention_launch(tq_dtype dtype, const void* q, const vo
   tq::DeviceScope device_scope(device);
   if (tq_status s = device_scope.status()) return s;
   const tq::WaitStatus status = tq::wait_status_for(device);
-  TQ_REQUIRE(status.sticky != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
+  TQ_REQUIRE(status.abort != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
 
   CUtensorMap map_q, map_k, map_v;
   if (tq_status s = tq::attention_map(&map_q, dtype, q, q_tokens, heads, batch, q_strides)) return s;

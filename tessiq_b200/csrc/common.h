@@ -113,17 +113,25 @@ tq_status record(Replay step);
     if (::tq::recording()) return ::tq::record(__VA_ARGS__);                    \
   } while (0)
 
-// Device-side status block (one per device, 64 words), written by kernels whose bounded waits give
-// up. Word 0 is the sticky code tq_status_poll reads and clears; words 1-7 say where the wait was
-// (tq_status_detail); words 8-63 are abort words: each launch is handed one of them and an epoch no
-// other launch in flight shares, and "abort word == epoch" tells the launch's other waits to leave.
+// Device-side status block (one per device, 64 words, 256-byte aligned), written by kernels whose
+// bounded waits give up. Word 0 is the sticky code tq_status_poll reads and clears; words 1-7 say
+// where the wait was (tq_status_detail); words 8-63 are abort words. Each launch is handed one abort
+// word (launches take them in turn); its first CTA clears the word when the kernel starts, a wait
+// that gives up sets it, and the launch's other waits leave when they see it set. A later launch has
+// another word, so a give-up nobody has polled yet does not make it bail out. The handle is one
+// pointer: the sticky word is found by rounding the abort word's address down to the block.
 int32_t* device_status_word(int32_t device);
 struct WaitStatus {
-  int* sticky;
   int* abort;
-  int epoch;
+#ifdef __CUDACC__
+  __device__ int* sticky() const { return reinterpret_cast<int*>(reinterpret_cast<uintptr_t>(abort) & ~static_cast<uintptr_t>(255)); }
+  __device__ bool aborted() const { return *reinterpret_cast<volatile int*>(abort) != 0; }
+  __device__ void set_abort() const { *reinterpret_cast<volatile int*>(abort) = 1; }
+  // by one thread of the launch's first CTA, before the CTA's first wait
+  __device__ void begin() const { *reinterpret_cast<volatile int*>(abort) = 0; }
+#endif
 };
-// The status handles for one launch on `device`; `sticky` is null when the block cannot be allocated.
+// The status handle for one launch on `device`; `abort` is null when the block cannot be allocated.
 WaitStatus wait_status_for(int32_t device);
 
 // reduce.cu: per-slice (max, 1/sum-exp) [kind 0] or (mean, variance) [kind 1] of a packed

@@ -309,6 +309,7 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    if (blockIdx.x == 0) p.status.begin();   // this launch's abort word starts clear
     for (int s = 0; s < kStages; ++s) {
       barrier_init(full_bar(s), 1);
       barrier_init(empty_bar(s), 1);
@@ -486,6 +487,7 @@ gemm_bias_act_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   const long long pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
+    if (blockIdx.x == 0) p.status.begin();   // this launch's abort word starts clear
     for (int s = 0; s < kPairStages; ++s) {
       barrier_init(full_bar(s), 2);                // one arrive.expect_tx from each CTA's producer
       barrier_init(empty_bar(s), 1);               // one commit
@@ -741,7 +743,7 @@ extern "C" tq_status tq_gemm_bias_act_residual_launch(tq_dtype dtype, tq_activat
   tq::DeviceScope device_scope(device);
   if (tq_status s = device_scope.status()) return s;
   const tq::WaitStatus status = tq::wait_status_for(device);
-  TQ_REQUIRE(status.sticky != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
+  TQ_REQUIRE(status.abort != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
 
   // Large problems run on CTA pairs (256 x 256 tiles, half the shared-memory operand traffic per
   // SM); problems with at most one row of 128 x 256 tiles keep the single-CTA kernel.

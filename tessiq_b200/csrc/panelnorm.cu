@@ -140,22 +140,23 @@ __device__ __forceinline__ void store_release(unsigned* pointer, unsigned value)
 // to the status word and, behind it, where it was (CTA, thread, and three values of the caller).
 constexpr uint32_t kPanelSpinLimit = 1u << 18;
 __device__ __forceinline__ void panel_give_up(const WaitStatus& status, int code, int d0 = 0, int d1 = 0, int d2 = 0, int d3 = 0) {
-  if (atomicCAS(status.sticky, 0, code) == 0) {
-    status.sticky[1] = static_cast<int>(blockIdx.x);
-    status.sticky[2] = static_cast<int>(threadIdx.x);
-    status.sticky[3] = d0;
-    status.sticky[4] = d1;
-    status.sticky[5] = d2;
-    status.sticky[6] = d3;
+  int* sticky = status.sticky();
+  if (atomicCAS(sticky, 0, code) == 0) {
+    sticky[1] = static_cast<int>(blockIdx.x);
+    sticky[2] = static_cast<int>(threadIdx.x);
+    sticky[3] = d0;
+    sticky[4] = d1;
+    sticky[5] = d2;
+    sticky[6] = d3;
   }
-  *reinterpret_cast<volatile int*>(status.abort) = status.epoch;
+  status.set_abort();
 }
 
 __device__ __forceinline__ bool panel_wait(uint32_t bar, uint32_t parity, const WaitStatus& status, int code, int d0, int d1, int d2,
                                            uint32_t limit = kPanelSpinLimit) {
   for (uint32_t spin = 0; spin < limit; ++spin) {
     if (barrier_try_wait(bar, parity)) return true;
-    if ((spin & 0x3ff) == 0x3ff && *reinterpret_cast<volatile int*>(status.abort) == status.epoch) return false;
+    if ((spin & 0x3ff) == 0x3ff && status.aborted()) return false;
   }
   panel_give_up(status, code, d0, d1, d2, static_cast<int>(parity));
   return false;
@@ -424,6 +425,7 @@ __global__ void __launch_bounds__(kPanelThreads, 1) panel_normalize_kernel(const
       barrier_init(stats_empty0 + 8 * b, kGroupWarps);
     }
     give_up = 0;
+    if (blockIdx.x == 0) args.status.begin();
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -872,7 +874,7 @@ tq_status panel_normalize_launch(int kind, tq_dtype dtype, const void* in, void*
   TQ_REQUIRE(workspace != nullptr && workspace_bytes >= l.total() && aligned_to(workspace, 16), TQ_INVALID_ARGUMENT,
              "the panel normalisation needs %zu bytes of 16-byte-aligned scratch and was given %zu", l.total(), workspace_bytes);
   const WaitStatus status = wait_status_for(device);
-  TQ_REQUIRE(status.sticky != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
+  TQ_REQUIRE(status.abort != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
 
   // in[batch * rows, cols] as a two-axis map; a tile is one stage: 512 bytes of 64 consecutive rows.
   EncodeTiled encode = encode_tiled();

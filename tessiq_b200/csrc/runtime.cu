@@ -70,10 +70,8 @@ int32_t* device_status_word(int32_t device) {
 WaitStatus wait_status_for(int32_t device) {
   static std::atomic<unsigned> launches{0};
   int32_t* block = device_status_word(device);
-  if (block == nullptr) return WaitStatus{nullptr, nullptr, 0};
-  const unsigned n = launches.fetch_add(1, std::memory_order_relaxed) + 1;
-  const int epoch = static_cast<int>(n | 0x40000000u);   // never 0, the value a cleared block holds
-  return WaitStatus{block, block + 8 + n % 56, epoch};
+  if (block == nullptr) return WaitStatus{nullptr};
+  return WaitStatus{block + 8 + launches.fetch_add(1, std::memory_order_relaxed) % 56};
 }
 
 }  // namespace tq
@@ -90,6 +88,7 @@ __global__ void bounded_wait_selftest_kernel(WaitStatus status, uint32_t polls, 
   __shared__ uint64_t barrier;
   const uint32_t bar = smem_address(&barrier);
   if (threadIdx.x == 0) {
+    status.begin();
     barrier_init(bar, 2);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     barrier_arrive(bar);
@@ -105,8 +104,8 @@ __global__ void bounded_wait_selftest_kernel(WaitStatus status, uint32_t polls, 
       }
     }
     if (!done) {
-      atomicCAS(status.sticky, 0, kStatusSelfTest);
-      *reinterpret_cast<volatile int*>(status.abort) = status.epoch;
+      atomicCAS(status.sticky(), 0, kStatusSelfTest);
+      status.set_abort();
     }
     looks[0] = static_cast<int>(spin);
     // the library's own wait now leaves at its first look at the abort word (every 1024 polls)
@@ -425,9 +424,9 @@ tq_status tq_selftest_bounded_wait(int32_t device, void* stream, int32_t polls, 
   tq::DeviceScope device_scope(device);
   if (tq_status s = device_scope.status()) return s;
   const tq::WaitStatus status = tq::wait_status_for(device);
-  TQ_REQUIRE(status.sticky != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
+  TQ_REQUIRE(status.abort != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
-  int* device_looks = status.sticky + 6;   // words of the status block that only a give-up's detail uses
+  int* device_looks = tq::device_status_word(device) + 6;   // words of the status block that only a give-up's detail uses
   tq::bounded_wait_selftest_kernel<<<1, 32, 0, cuda_stream>>>(status, static_cast<uint32_t>(polls), device_looks);
   if (tq_status s = tq::check_launch("bounded_wait_selftest_kernel")) return s;
   TQ_CUDA(cudaMemcpyAsync(looks, device_looks, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, cuda_stream));

@@ -42,17 +42,17 @@ __device__ __forceinline__ bool barrier_try_wait(uint32_t bar, uint32_t parity) 
 
 // Waits for the phase of `bar` with the given parity, for a bounded number of polls. When the
 // bound runs out the device's sticky status word gets `code` (the first give-up wins; tq_status_poll
-// reads and clears it) and this launch's abort word gets the launch's epoch, which makes every other
-// bounded wait of the same launch leave at its next look — of THIS launch only: a later launch has
-// another epoch, so a give-up nobody has polled yet does not make it bail out. The caller must
-// leave its loop on false.
+// reads and clears it) and the launch's abort word is set, which makes every other bounded wait of
+// the same launch leave at its next look (every 1024 polls). The launch's first CTA clears the abort
+// word when the kernel starts (WaitStatus::begin), so what an earlier launch left there does not
+// make this one bail out. The caller must leave its loop on false.
 __device__ __forceinline__ bool barrier_wait(uint32_t bar, uint32_t parity, const WaitStatus& status, int code) {
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
     if (barrier_try_wait(bar, parity)) return true;
-    if ((spin & 0x3ff) == 0x3ff && *reinterpret_cast<volatile int*>(status.abort) == status.epoch) return false;
+    if ((spin & 0x3ff) == 0x3ff && status.aborted()) return false;
   }
-  atomicCAS(status.sticky, 0, code);
-  *reinterpret_cast<volatile int*>(status.abort) = status.epoch;
+  atomicCAS(status.sticky(), 0, code);
+  status.set_abort();
   return false;
 }
 
