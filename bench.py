@@ -599,7 +599,50 @@ def other_configs(device: int, stream) -> dict:
                                           "frac_of_measured_burst": round(tflops / measured.get("bf16_tflops", 1590.0), 4),
                                           "frac_of_measured_sustained": round(tflops / measured.get("bf16_tflops_sustained", 1400.0), 4),
                                           "frac_of_nominal_2250": round(tflops / 2250.0, 4)}
+    # the same product back to back for two seconds and more (the GPU settles at its power cap), with the SM clock sampled
+    # meanwhile, and torch.matmul (cuBLAS, no bias, no GELU) under the same loop right after it
+    def sustained(fn, per_call_seconds):
+        calls = max(int(2.2 / per_call_seconds), 50)
+        with ClockSampler(device) as sampler, torch.cuda.stream(stream):
+            for _ in range(20):
+                fn()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record(stream)
+            for _ in range(calls):
+                fn()
+            end.record(stream)
+            stream.synchronize()
+        summary = sampler.summary()
+        return begin.elapsed_time(end) / calls * 1e-3, summary.get("sm_mhz"), summary.get("reasons")
+    ours_s, ours_mhz, ours_reasons = sustained(lambda: ops.matmul_bias_gelu_tanh(a, b, gbias), seconds)
+    blas_s, blas_mhz, _ = sustained(lambda: torch.matmul(a, b), seconds)
+    out["config3_gemm_bias_gelu_bf16"]["sustained"] = {
+        "us": round(ours_s * 1e6, 1), "tflops": round(flop / ours_s / 1e12, 1), "sm_mhz_median": ours_mhz, "reasons": ours_reasons,
+        "frac_of_measured_sustained": round(flop / ours_s / 1e12 / measured.get("bf16_tflops_sustained", 1400.0), 4),
+        "torch_matmul_same_loop": {"us": round(blas_s * 1e6, 1), "tflops": round(flop / blas_s / 1e12, 1), "sm_mhz_median": blas_mhz},
+        "ratio_to_torch_matmul": round(blas_s / ours_s, 4),
+        "note": "2 s and more of back-to-back launches each; torch.matmul is the product alone, ours adds the bias and the GELU"}
     del a, b
+
+    # config 1's chain with a STRIDED operand: x is every other column of a [4096, 8192] tensor (an unravelled read per element,
+    # no shared-memory staging) — algorithmic bytes as for the packed chain
+    wide = [torch.randn(4096, 8192, device=dev) for _ in range(4)]
+    ys2 = [torch.empty(4096, 4096, device=dev) for _ in range(4)]
+    strided_chain = FusedKernel("in x f32 strided\nin b f32 cycled\nv0 = add x b\nv1 = gelu_tanh v0\nv2 = sigmoid x\nv3 = mul v1 v2\n"
+                                "v4 = mul x 0.5\nv5 = sub v3 v4\nout v5 f32\n")
+    def strided_pass():
+        for j in range(4):
+            strided_chain.launch([wide[j][:, ::2], bias], ys2[j], stream=raw)
+    try:
+        seconds = timed(strided_pass, 10) / 4
+        touched = 4096 * 8192 * 4 + 4096 * 4096 * 4 + 4096 * 4     # every 32-byte sector of the wide tensor is fetched
+        out["config1_chain_strided_operand_f32"] = {"us": round(seconds * 1e6, 1), "gbs_algorithmic": round(nbytes / seconds / 1e9, 1),
+                                                    "gbs_of_sectors_touched": round(touched / seconds / 1e9, 1),
+                                                    "frac_of_measured_hbm_sectors": round(touched / seconds / 1e9 / peak_hbm, 4),
+                                                    "note": "stride-2 columns: half of every fetched sector is used; the sectors-touched figure is the HBM traffic"}
+    except Exception as error:   # a selector that declines this read form: say so instead of failing the bench
+        out["config1_chain_strided_operand_f32"] = {"declined": f"{type(error).__name__}: {error}"}
+    del wide, ys2
 
     # config 5a: six-op chain with predicate and cast, f32 -> bf16, 2^28 elements
     n = 1 << 28
@@ -828,15 +871,15 @@ def run_sweep(args) -> dict:
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per full-size launch of the operations that can be the
-# longest of the step, each from one ncu capture on a reduced case (half the rows or half the columns)
-# scaled by two — the traffic of these streaming kernels grows in proportion (summaries under profiles/).
-# softmax_rows stays just below its 1 073 741 824 algorithmic bytes because the tail of the result is
-# still in L2 when the kernel ends; the transposed-view pair reads its input twice (the second visit
-# misses L2 at the setting that measured fastest), so 1.5x the algorithmic bytes.
+# longest of the step, from ncu captures of the full-size launch (three metrics, one pass; summaries
+# under profiles/). softmax_rows: from a half-size capture scaled by two; it stays just below its
+# 1 073 741 824 algorithmic bytes because the tail of the result is still in L2 when the kernel ends.
+# The transposed-view pair reads its input 1.93 times (the second visit of a panel misses L2 at the
+# setting that measured fastest), so 1.42x the algorithmic bytes.
 NCU_TRAFFIC_BYTES = {
     "softmax_rows_f32": 964180992,
-    "softmax_cols_f32": None,
-    "layer_norm_cols_f32": None,
+    "softmax_cols_f32": 1520951808,      # 1 034 631 168 read + 486 320 640 written
+    "layer_norm_cols_f32": 1527664896,   # 1 040 389 120 read + 487 275 776 written
 }
 
 
