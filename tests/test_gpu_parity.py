@@ -556,7 +556,7 @@ def test_layer_norm_rows(tq, width, affine):
     assert mean.shape == rmean.shape and rstd.shape == rrstd.shape  # [..., 1]
     if width > 1:
         close32(mean, rmean, rtol=1e-5, scale=1e-5)
-        close32(rstd, rrstd, rtol=2e-5, scale=1e-5)
+        close32(rstd, rrstd, rtol=1e-5, scale=1e-5)
 
 
 def test_layer_norm_matches_golden_and_other_types(tq, golden):
@@ -647,8 +647,8 @@ def test_softmax_and_layer_norm_over_a_transposed_view(tq, dtype, shape):
     ref_plain = tessiq0.native_layer_norm(view, [rows], None, None, 1e-5)[0]
     if dtype == torch.float32:
         close32(got_softmax, ref_softmax, scale=1e-6)
-        close32(got_norm, ref_norm, rtol=2e-5, scale=4e-6)
-        close32(got_plain, ref_plain, rtol=2e-5, scale=4e-6)
+        close32(got_norm, ref_norm, rtol=1e-5, scale=4e-6)
+        close32(got_plain, ref_plain, rtol=1e-5, scale=4e-6)
     else:
         close16(got_softmax, ref_softmax)
         close16(got_norm, ref_norm)
@@ -670,7 +670,7 @@ def test_transposed_normalisations_special_columns_and_fallback(tq):
     torch.testing.assert_close(got, tessiq0.softmax(x.t(), -1), rtol=1e-5, atol=1e-7, equal_nan=True)
     odd = torch.randn(130, 37, generator=torch.Generator().manual_seed(6))   # not a multiple of the vector width: packs first
     close32(tq.softmax(dev(odd).t(), -1), tessiq0.softmax(odd.t(), -1), scale=1e-6)
-    close32(tq.layer_norm(dev(odd).t(), [130]), tessiq0.native_layer_norm(odd.t(), [130], None, None, 1e-5)[0], rtol=2e-5, scale=4e-6)
+    close32(tq.layer_norm(dev(odd).t(), [130]), tessiq0.native_layer_norm(odd.t(), [130], None, None, 1e-5)[0], rtol=1e-5, scale=4e-6)
     shifted = torch.randn(256, 64, generator=torch.Generator().manual_seed(7)) + 1000.0      # a large mean: the variance must survive it
     close32(tq.layer_norm(dev(shifted).t(), [256]), tessiq0.native_layer_norm(shifted.t(), [256], None, None, 1e-5)[0], rtol=1e-3, scale=1e-3)
 
@@ -706,8 +706,8 @@ def test_transposed_normalisations_from_a_column_slab(tq, dtype, shape):
     ref_norm = tessiq0.native_layer_norm(view, [rows], w, b, 1e-5)[0]
     if dtype == torch.float32:
         close32(got_softmax, ref_softmax, scale=1e-6)
-        close32(got_norm, ref_norm, rtol=2e-5, scale=4e-6)
-        close32(tq.layer_norm(xd.transpose(-1, -2), [rows]), tessiq0.native_layer_norm(view, [rows], None, None, 1e-5)[0], rtol=2e-5, scale=4e-6)
+        close32(got_norm, ref_norm, rtol=1e-5, scale=4e-6)
+        close32(tq.layer_norm(xd.transpose(-1, -2), [rows]), tessiq0.native_layer_norm(view, [rows], None, None, 1e-5)[0], rtol=1e-5, scale=4e-6)
     else:
         close16(got_softmax, ref_softmax)
         close16(got_norm, ref_norm)
@@ -777,7 +777,7 @@ def test_column_slab_special_columns(tq):
     nan_norm[5, 2] = float("nan")
     nan_norm[6, 9] = float("inf")
     got = tq.layer_norm(dev(nan_norm).t(), [rows]).cpu()
-    torch.testing.assert_close(got, tessiq0.native_layer_norm(nan_norm.t(), [rows], None, None, 1e-5)[0], rtol=2e-5, atol=4e-6, equal_nan=True)
+    torch.testing.assert_close(got, tessiq0.native_layer_norm(nan_norm.t(), [rows], None, None, 1e-5)[0], rtol=1e-5, atol=4e-6, equal_nan=True)
 
 
 def _layouts():
