@@ -25,6 +25,7 @@
 
 #include "common.h"
 #include "reducers.h"
+#include "tcgen05.h"
 
 namespace cg = cooperative_groups;
 
@@ -603,9 +604,217 @@ reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long
 }
 
 // ---------------------------------------------------------------------------------------------
+// inner > 1, large tensors: the persistent streaming form. The tensor is cut into panels of columns
+// (512 bytes of every row) and a panel into units of 64 rows; a unit is one TMA tile (32 KiB). The
+// units, panel after panel, are dealt out as one contiguous range per CTA (one CTA per SM), so every
+// SM streams the same number of bytes (to within one unit) and a panel is shared by the few CTAs
+// whose ranges meet it. One lane issues the tile loads into a ring of shared-memory stages; eight
+// consumer warps fold the rows (warp w rows w, w + 8, ... of a unit, a lane 16 bytes of a row). Where
+// a CTA's range leaves a panel it folds its eight warps' accumulators through shared memory and, if
+// it is not the panel's only CTA, leaves one partial per column in scratch; the last CTA of the panel
+// to take a ticket folds the partials in row order and writes the results. Replaces the thread-level
+// loads of reduce_columns for the shapes where those leave the memory system short of requests:
+// per 16 bytes a consumer spends a shared-memory load and the reducer's own work, nothing else.
+constexpr int kStreamConsumers = 8;                                  // warps
+constexpr int kStreamThreads = (kStreamConsumers + 1) * 32;          // + the producer warp
+constexpr int kStreamPieceBytes = 512;
+constexpr int kStreamUnitRows = 64;
+constexpr int kStreamStageBytes = kStreamUnitRows * kStreamPieceBytes;
+constexpr int kStreamStages = 5;
+constexpr int kStatusStreamData = 0x53544d31;    // "STM1": a unit's data never arrived
+constexpr int kStatusStreamRing = 0x53544d32;    // "STM2": a stage was never handed back
+
+struct StreamArgs {
+  long long reduce, inner;
+  long long units;            // outer * panels per slice * units per panel
+  int units_per_panel;        // reduce / 64
+  int panels_per_slice;       // inner / columns per panel
+  int slots;                  // partial rows reserved per panel
+  int mean;
+  WaitStatus status;
+};
+
+__device__ __forceinline__ long long stream_first_unit(long long cta, long long units, long long grid) { return cta * units / grid; }
+
+// The CTA whose range holds `unit`.
+__device__ __forceinline__ int stream_owner(long long unit, long long units, int grid) {
+  long long c = unit * grid / units;
+  while (c + 1 < grid && stream_first_unit(c + 1, units, grid) <= unit) ++c;
+  while (c > 0 && stream_first_unit(c, units, grid) > unit) --c;
+  return static_cast<int>(c);
+}
+
+template <typename T, typename R>
+__global__ void __launch_bounds__(kStreamThreads, 1)
+reduce_columns_stream(const __grid_constant__ CUtensorMap map, const StreamArgs args, typename R::Out* __restrict__ out,
+                      typename R::Acc* __restrict__ partials, unsigned* __restrict__ tickets) {
+  using Acc = typename R::Acc;
+  constexpr int V = 16 / static_cast<int>(sizeof(T));
+  constexpr int kColumns = 32 * V;
+  constexpr int kConsumerThreads = kStreamConsumers * 32;
+  constexpr int kRowsPerWarp = kStreamUnitRows / kStreamConsumers;
+  extern __shared__ __align__(128) unsigned char stream_smem[];
+  __shared__ int is_last;
+  unsigned char* ring = stream_smem;
+  Acc* scratch = reinterpret_cast<Acc*>(ring + kStreamStages * kStreamStageBytes);   // [8 warps][columns]
+  uint64_t* barriers = reinterpret_cast<uint64_t*>(scratch + kStreamConsumers * kColumns);
+  const uint32_t full0 = smem_address(barriers), empty0 = full0 + 8 * kStreamStages;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStreamStages; ++s) {
+      barrier_init(full0 + 8 * s, 1);
+      barrier_init(empty0 + 8 * s, kStreamConsumers);
+    }
+    if (blockIdx.x == 0) args.status.begin();
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int grid = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
+  const long long first = stream_first_unit(cta, args.units, grid), last = stream_first_unit(cta + 1, args.units, grid);
+  const int upp = args.units_per_panel;
+  int stage = 0;
+  uint32_t phase = 0;
+
+  if (warp == kStreamConsumers) {
+    // ---- producer ---------------------------------------------------------------------------------
+    if (lane == 0) {
+      for (long long u = first; u < last; ++u) {
+        const long long panel = u / upp;
+        const int unit = static_cast<int>(u - panel * upp);
+        const long long slice = panel / args.panels_per_slice;
+        const int column = static_cast<int>(panel - slice * args.panels_per_slice) * kColumns;
+        if (!barrier_wait(empty0 + 8 * stage, phase ^ 1, args.status, kStatusStreamRing)) break;
+        barrier_expect_tx(full0 + 8 * stage, kStreamStageBytes);
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                         smem_address(ring) + stage * kStreamStageBytes),
+                     "l"(&map), "r"(full0 + 8 * stage), "r"(column), "r"(static_cast<int>(slice * args.reduce + static_cast<long long>(unit) * kStreamUnitRows))
+                     : "memory");
+        if (++stage == kStreamStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      // nothing may still be on its way into this CTA's shared memory when it leaves: the consumers
+      // wait for every tile they were promised, and after a give-up the loads already issued are
+      // waited for here (a stage that was never armed answers at once)
+      if (args.status.aborted()) {
+        for (int s = 0; s < kStreamStages; ++s) {
+          const uint32_t parity = s < stage ? phase : phase ^ 1;
+          for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+            if (barrier_try_wait(full0 + 8 * s, parity)) break;
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // ---- consumers: a segment is the part of the CTA's range that lies in one panel --------------------
+  bool alive = true;
+  for (long long u = first; u < last && alive;) {
+    const long long panel = u / upp;
+    const long long panel_first = panel * upp;
+    long long segment_end = panel_first + upp;
+    if (segment_end > last) segment_end = last;
+    typename R::template Local<1> local[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) local[e] = R::template local_identity<1>();
+    const long long segment_first = u;
+    for (; u < segment_end; ++u) {
+      if (!barrier_wait(full0 + 8 * stage, phase, args.status, kStatusStreamData)) {
+        alive = false;
+        break;
+      }
+      const Vec<T, V>* mine = reinterpret_cast<const Vec<T, V>*>(ring + static_cast<size_t>(stage) * kStreamStageBytes +
+                                                                 static_cast<size_t>(warp) * kStreamPieceBytes) + lane;
+      long long row = (u - panel_first) * kStreamUnitRows + warp;   // within the slice
+      if constexpr (R::kSeeded) {
+        if (u == segment_first) {
+          const Vec<T, V> x = mine[0];
+#pragma unroll
+          for (int e = 0; e < V; ++e) R::template seed<1>(local[e], x.v[e]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kRowsPerWarp; ++i) {
+        const Vec<T, V> x = mine[i * kStreamConsumers * (kStreamPieceBytes / 16)];
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          if constexpr (R::kSeeded) {
+            R::template step_seeded<1>(local[e], x.v[e]);
+          } else {
+            R::template step<1>(local[e], x.v[e], row);
+          }
+        }
+        row += kStreamConsumers;
+      }
+      __syncwarp();
+      if (lane == 0) barrier_arrive(empty0 + 8 * stage);
+      if (++stage == kStreamStages) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+    if (!alive) break;
+    if constexpr (R::kSeeded) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) R::template set_count<1>(local[e], static_cast<int>(segment_end - segment_first) * kRowsPerWarp);
+    }
+    // the eight warps' accumulators meet in shared memory (the first barrier: everyone is done reading
+    // what the previous segment left there), one thread per column folds them in warp order
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+#pragma unroll
+    for (int e = 0; e < V; ++e) scratch[warp * kColumns + lane * V + e] = R::template to_acc<1>(local[e]);
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+    const int owner_first = stream_owner(panel_first, args.units, grid);
+    const int owner_last = stream_owner(panel_first + upp - 1, args.units, grid);
+    const int sharers = owner_last - owner_first + 1;
+    const long long slice = panel / args.panels_per_slice;
+    typename R::Out* out_row = out + slice * args.inner + (panel - slice * args.panels_per_slice) * kColumns;
+    Acc* panel_partials = partials + panel * args.slots * kColumns;
+    for (int column = threadIdx.x; column < kColumns; column += kConsumerThreads) {
+      Acc total = scratch[column];
+#pragma unroll
+      for (int w = 1; w < kStreamConsumers; ++w) total = R::combine(total, scratch[w * kColumns + column]);
+      if (sharers == 1) {
+        out_row[column] = R::finish(total, args.reduce, args.mean != 0);
+      } else {
+        panel_partials[(cta - owner_first) * kColumns + column] = total;
+      }
+    }
+    if (sharers > 1) {
+      // the last CTA of the panel to take a ticket folds the partials in CTA order, which is row order
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+      if (threadIdx.x == 0) is_last = atomicAdd(&tickets[panel], 1u) == static_cast<unsigned>(sharers - 1) ? 1 : 0;
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+      if (is_last) {
+        __threadfence();
+        for (int column = threadIdx.x; column < kColumns; column += kConsumerThreads) {
+          Acc total = R::identity();
+          for (int j = 0; j < sharers; j += 12) {
+            Acc batch[12];
+#pragma unroll
+            for (int k = 0; k < 12; ++k) {
+              if (j + k < sharers) batch[k] = load_partial(panel_partials + (j + k) * kColumns + column);
+            }
+#pragma unroll
+            for (int k = 0; k < 12; ++k) {
+              if (j + k < sharers) total = R::combine(total, batch[k]);
+            }
+          }
+          out_row[column] = R::finish(total, args.reduce, args.mean != 0);
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Host: the plan and the launch
 
-enum class Shape { kWarpPerSlice, kCtaPerSlice, kColumns };
+enum class Shape { kWarpPerSlice, kCtaPerSlice, kColumns, kColumnStream };
 
 struct Plan {
   Shape shape = Shape::kWarpPerSlice;
@@ -619,7 +828,46 @@ struct Plan {
   size_t acc_bytes = 0;
   size_t partial_bytes = 0;   // scratch for partials (0 when one cluster covers a slice)
   size_t ticket_bytes = 0;
+  // the streaming columns kernel
+  int device = 0;
+  int grid = 0;               // CTAs: one per SM
+  long long units = 0;        // outer * panels per slice * units per panel
+  int units_per_panel = 0;
+  int panels_per_slice = 0;
+  int slots = 0;              // partial rows per panel
 };
+
+// Whether the persistent streaming kernel takes a column reduction, and its tiling. Measured on B200
+// at [32768, 4096] against reduce_columns: bf16 sum / mean / amax 51-52 us against 54-55, bf16 argmax
+// 60 against 72, f32 argmax 93 against 103, bf16 moments (inside LayerNorm over a transposed view) 18 us
+// less; f32 sum / mean / amax 89-91 us against 82-85, so those stay with reduce_columns. The streaming
+// kernel moves 5.9-6.0 TB/s whatever the reducer until the reducer's instructions bind (bf16 argmax);
+// what it loses is fixed: about 2 us until the first tile lands and 3 us for the last panel's fold.
+bool plan_stream(Plan& p, tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, long long inner, int32_t device,
+                 int vec_bytes_limit) {
+  const int size = dtype_size(dtype);
+  if (dtype != TQ_F32 && dtype != TQ_F16 && dtype != TQ_BF16) return false;
+  if (!(size == 2 || op == TQ_ARGMAX || static_cast<int>(op) >= kOpSoftmaxStat)) return false;
+  if (vec_bytes_limit != 16 || (inner * size) % kStreamPieceBytes != 0 || reduce % kStreamUnitRows != 0) return false;
+  if (outer * reduce >= (1ll << 31) || inner >= (1ll << 31)) return false;   // TMA coordinates are 32 bits
+  if (outer * reduce * inner * size < (64ll << 20)) return false;
+  const int sms = sm_count(device);
+  const long long panels = outer * (inner * size / kStreamPieceBytes);
+  const long long units = panels * (reduce / kStreamUnitRows);
+  if (units < 4ll * sms || panels > (1ll << 24)) return false;
+  p.shape = Shape::kColumnStream;
+  p.device = device;
+  p.grid = sms;
+  p.units = units;
+  p.units_per_panel = static_cast<int>(reduce / kStreamUnitRows);
+  p.panels_per_slice = static_cast<int>(inner * size / kStreamPieceBytes);
+  p.slots = static_cast<int>((p.units_per_panel + units / sms - 1) / (units / sms)) + 1;
+  p.tiles = panels;
+  const long long columns = kStreamPieceBytes / size;
+  p.partial_bytes = (static_cast<size_t>(panels) * p.slots * columns * p.acc_bytes + 255) / 256 * 256;
+  p.ticket_bytes = (static_cast<size_t>(panels) * sizeof(unsigned) + 255) / 256 * 256;
+  return true;
+}
 
 int floor_pow2(long long v) {
   int p = 1;
@@ -658,6 +906,7 @@ Plan plan(tq_reduce_op op, tq_dtype dtype, long long outer, long long reduce, lo
     }
     p.tiles = outer;
   } else {
+    if (plan_stream(p, op, dtype, outer, reduce, inner, device, vec_bytes_limit)) return p;
     p.shape = Shape::kColumns;
     int vec = vec_bytes_limit / size;
     if (vec > 8) vec = 8;
@@ -788,6 +1037,43 @@ tq_status run(const Plan& p, const void* in, void* out, long long outer, long lo
         if (p.vec == 8) return p.ring ? go(reduce_columns<T, R, 8, true>, 8) : go(reduce_columns<T, R, 8, false>, 8);
       }
       return fail(TQ_INTERNAL, "no column kernel for %d elements per thread", p.vec);
+    }
+    case Shape::kColumnStream: {
+      if constexpr (std::is_same_v<T, float> || std::is_same_v<T, __half> || std::is_same_v<T, __nv_bfloat16>) {
+        constexpr int kColumns = kStreamPieceBytes / static_cast<int>(sizeof(T));
+        EncodeTiled encode = encode_tiled();
+        TQ_REQUIRE(encode != nullptr, TQ_EXTERNAL, "the CUDA driver does not provide cuTensorMapEncodeTiled");
+        // in[outer * reduce, inner] as a two-axis map; a tile is one unit: 512 bytes of 64 consecutive rows
+        CUtensorMap map;
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer * reduce)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(inner) * sizeof(T)};
+        const cuuint32_t box[2] = {static_cast<cuuint32_t>(kColumns), static_cast<cuuint32_t>(kStreamUnitRows)};
+        const cuuint32_t element_strides[2] = {1, 1};
+        const CUtensorMapDataType type = std::is_same_v<T, float>    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                         : std::is_same_v<T, __half> ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                                     : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        const CUresult encoded = encode(&map, type, 2, const_cast<T*>(input), dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        TQ_REQUIRE(encoded == CUDA_SUCCESS, TQ_EXTERNAL, "cuTensorMapEncodeTiled refused the reduction's input (%d)", static_cast<int>(encoded));
+        StreamArgs args = {};
+        args.reduce = reduce;
+        args.inner = inner;
+        args.units = p.units;
+        args.units_per_panel = p.units_per_panel;
+        args.panels_per_slice = p.panels_per_slice;
+        args.slots = p.slots;
+        args.mean = mean ? 1 : 0;
+        args.status = wait_status_for(p.device);
+        TQ_REQUIRE(args.status.abort != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
+        auto kernel = reduce_columns_stream<T, R>;
+        const size_t smem = static_cast<size_t>(kStreamStages) * kStreamStageBytes + static_cast<size_t>(kStreamConsumers) * kColumns * sizeof(Acc) +
+                            2 * kStreamStages * 8;
+        TQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        kernel<<<static_cast<unsigned>(p.grid), kStreamThreads, smem, stream>>>(map, args, output, partials, tickets);
+        return check_launch("reduce_columns_stream");
+      } else {
+        return fail(TQ_INTERNAL, "the streaming columns kernel was planned for an element type it does not serve");
+      }
     }
   }
   return fail(TQ_INTERNAL, "unreachable reduction shape");

@@ -486,6 +486,47 @@ def test_config_2_full_size_reductions(tq):
     assert torch.equal(tq.argmax(xd.t(), -1).cpu(), x.argmax(0))
 
 
+@pytest.mark.parametrize("dtype, shape", [(torch.bfloat16, (16384, 2304)), (torch.float16, (2, 8192, 2048)), (torch.float32, (3, 4096, 1408)),
+                                          (torch.bfloat16, (9536, 3584))])
+def test_column_reductions_of_large_tensors_stream_through_shared_memory(tq, dtype, shape):
+    """Reductions over the second-to-last axis of tensors of 64 MiB and more whose rows are a multiple
+    of 512 bytes and whose reduced extent is a multiple of 64 take the persistent kernel that streams
+    64-row tiles through shared memory (2-byte types: every reduction; 4-byte: argmax): every SM gets
+    a contiguous range of tiles, so a panel of columns is shared by several CTAs and, with three
+    slices or 149 tiles per panel, ranges end in the middle of panels and slices."""
+    g = torch.Generator().manual_seed(sum(shape))
+    x = (torch.randn(*shape, generator=g) * 2 + 0.25).to(dtype)
+    flat = x.view(-1, shape[-2], shape[-1])
+    flat[0, 5, 3] = float("nan")                        # a NaN wins amax, amin and argmax
+    flat[-1, shape[-2] - 1, 7] = float("nan")           # ... also in the last row of the last slice
+    flat[0, :, 9] = 1.5                                 # all equal: the lowest index
+    flat[0, 100, 11] = float("inf")
+    flat[0, 4000, 11] = float("inf")                    # two maxima far apart (different CTAs): the first one
+    flat[0, :, 13] = float("-inf")
+    xd = dev(x)
+    dim = len(shape) - 2
+    for op in ("amax", "amin"):
+        assert torch.equal(torch.nan_to_num(getattr(tq, op)(xd, dim).cpu().float(), nan=7.0),
+                           torch.nan_to_num(tessiq0.reduce(op, x, dim).float(), nan=7.0)), op
+    assert torch.equal(tq.argmax(xd, dim).cpu(), tessiq0.reduce("argmax", x, dim))
+    clean = x.clone()
+    clean.view(-1, shape[-2], shape[-1])[0, :, [3, 11, 13]] = 0.5
+    clean.view(-1, shape[-2], shape[-1])[-1, :, 7] = 0.5
+    cd = dev(clean)
+    half_ulp = {torch.bfloat16: 2.0**-8, torch.float16: 2.0**-11, torch.float32: 2.0**-24}[dtype]
+    truth = clean.double().sum(dim)
+    got = tq.sum(cd, dim).cpu().double()
+    assert ((got - truth).abs() <= half_ulp * truth.abs() + sum_budget(clean, dim)).all()
+    got = tq.mean(cd, dim).cpu().double()
+    assert ((got - truth / shape[-2]).abs() <= half_ulp * (truth / shape[-2]).abs() + sum_budget(clean, dim) / shape[-2]).all()
+    again = tq.sum(cd, dim).cpu().double()              # fixed merge order: the same bits every time
+    assert torch.equal(again, tq.sum(cd, dim).cpu().double())
+    status = ctypes.c_int32(-1)
+    from tessiq_b200 import kernel as K
+    K.check(K.lib.tq_status_poll(0, None, ctypes.byref(status)))
+    assert status.value == 0
+
+
 # ---------------------------------------------------------------------------------------------
 # softmax, LayerNorm, RMSNorm, BatchNorm
 
