@@ -728,8 +728,6 @@ __global__ void __launch_bounds__(kPanelThreads, 1) panel_normalize_kernel(const
                                                              column_block * 16);
         }
       }
-      __syncwarp();
-      if (lane == 0) barrier_arrive(empty_n0 + 8 * stage);
 #pragma unroll
       for (int q = 0; q < kBlocksPerThread; ++q) {
         const int r = sub * kStageRows + 8 * q * V;   // this block's first row, from the thread's first row of the item
@@ -766,6 +764,10 @@ __global__ void __launch_bounds__(kPanelThreads, 1) panel_normalize_kernel(const
           line_target += args.rows;
         }
       }
+      // the stage goes back only after every value read from it has been used (handing it back right
+      // after the shared-memory loads were issued can let the next tile land under the last of them)
+      __syncwarp();
+      if (lane == 0) barrier_arrive(empty_n0 + 8 * stage);
       if (++stage == stages) {
         stage = 0;
         phase ^= 1;
