@@ -264,3 +264,17 @@ def test_registration_table_is_in_the_references_format():
         with reference.open("rb") as handle:
             theirs = [name for op in tomllib.load(handle)["op"] for name in (op["name"], *op["aten"])]
         assert not set(theirs) & set(spelled)
+
+
+def test_coverage_table_of_the_added_operations_is_up_to_date():
+    """tessiq_b200/op_coverage_b200.md is what gen_ops_b200.py makes of ops_b200.toml (the counterpart
+    of the reference's docs/op_coverage.md, tools/gen_ops.py --check)."""
+    import importlib.util
+    from pathlib import Path
+
+    path = Path(__file__).resolve().parents[1] / "tessiq_b200" / "gen_ops_b200.py"
+    spec = importlib.util.spec_from_file_location("gen_ops_b200", path)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    assert module.COVERAGE.read_text() == module.coverage(module.load())
+
