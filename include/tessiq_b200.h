@@ -445,7 +445,8 @@ tq_status tq_gemm_bias_act_residual_launch(tq_dtype dtype,
  *   {batch, head, token} and its head_dim elements are contiguous — so the slices of a fused QKV
  *   projection are read where they lie and the result can be written in [batch, token, head, dim]
  *   order.
- * Declines (TQ_UNSUPPORTED): head_dim != 64, a scale that is not positive and finite, q/k/v that
+ * head_dim is 8, 16, ... 64 (a head narrower than 64 rides in the kernel's 64-wide tiles, whose other
+ * columns TMA fills with zeros). Declines (TQ_UNSUPPORTED): any other head_dim, a scale that is not positive and finite, q/k/v that
  * are not 16-byte aligned or whose strides are not positive multiples of 8 elements (TMA's rules).
  * Bounded waits report through tq_status_poll like the GEMM's. */
 tq_status tq_attention_launch(tq_dtype dtype,

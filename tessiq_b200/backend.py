@@ -364,7 +364,7 @@ def _match_attention(last: fx.Node, constant: set[fx.Node], folded: dict) -> Att
     if shapes[1] != shapes[2] or shapes[0][:-2] != shapes[1][:-2] or shapes[0][-1] != shapes[1][-1]:
         raise _NoMatch(f"operand shapes {shapes}")
     dtypes = {n.meta["val"].dtype for n in (q, k, v, last)}
-    if len(dtypes) != 1 or dtypes.pop() not in (torch.bfloat16, torch.float16) or shapes[0][-1] != 64 or not scale > 0:
+    if len(dtypes) != 1 or dtypes.pop() not in (torch.bfloat16, torch.float16) or shapes[0][-1] not in HEAD_WIDTHS or not scale > 0:
         raise _NoMatch(f"no kernel for heads of {shapes[0][-1]} elements in this type, or a scale that is not positive")
     if any(len(n.users) != 1 for n in path):          # an intermediate value has another reader
         raise _NoMatch("an intermediate value has another reader: " + ", ".join(n.name for n in path if len(n.users) != 1))
@@ -394,6 +394,9 @@ def _sdpa_targets() -> dict:
 
 SDPA = _sdpa_targets()
 
+#: head widths the fused attention kernel takes (narrower than 64: zero-filled columns of its 64-wide tiles)
+HEAD_WIDTHS = (8, 16, 24, 32, 40, 48, 56, 64)
+
 
 def _attention_step(match: Attention) -> Step:
     scale, causal = match.scale, match.causal
@@ -421,7 +424,7 @@ def _attention_step(match: Attention) -> Step:
 
 def _sdpa_step(node: fx.Node) -> Step | None:
     """One of ATen's fused attention operators, when only its first result is read and it asks for
-    nothing the kernel lacks (dropout, a bias, a head width other than 64)."""
+    nothing the kernel lacks (dropout, a bias, a head wider than 64)."""
     bias_at, causal_at = SDPA[node.target]
     args = list(node.args)
     q, k, v = args[:3]
@@ -438,7 +441,7 @@ def _sdpa_step(node: fx.Node) -> Step | None:
         return None
     causal = bool(args[causal_at]) if len(args) > causal_at else bool(node.kwargs.get("is_causal", False))
     shapes = [_shape(n) for n in (q, k, v)]
-    if any(len(sh) != 4 for sh in shapes) or shapes[0][-1] != 64 or shapes[1] != shapes[2] or shapes[0][:2] != shapes[1][:2]:
+    if any(len(sh) != 4 for sh in shapes) or shapes[0][-1] not in HEAD_WIDTHS or shapes[1] != shapes[2] or shapes[0][:2] != shapes[1][:2]:
         return None
     if q.meta["val"].dtype not in (torch.bfloat16, torch.float16):
         return None

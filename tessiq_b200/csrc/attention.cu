@@ -83,6 +83,7 @@ enum AttnWait { kWaitQ = 201, kWaitKeyEmpty = 202, kWaitValueEmpty = 203, kWaitK
 
 struct AttnParams {
   int batch, heads, q_tokens, k_tokens;
+  int head_dim;                    // 8, 16, ... 64: narrower heads ride in 64-wide tiles whose other columns TMA fills with zeros
   int q_blocks;                    // CTAs per head
   int causal;
   float scale_log2;                // scale * log2(e)
@@ -411,26 +412,31 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const float inverse = 1.0f / row_sum;
         T* out_row = static_cast<T*>(p.out) + batch * p.out_batch + head * p.out_head + static_cast<long long>(query) * p.out_token;
         const bool vector_ok = (reinterpret_cast<uintptr_t>(out_row) & 15) == 0;
+        const int width = p.head_dim;       // a multiple of 8: whole 16-byte vectors
         if (vector_ok) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint4 word;
-            word.x = pack_pair<T>(__uint_as_float(o0[v * 8 + 0]) * inverse, __uint_as_float(o0[v * 8 + 1]) * inverse);
-            word.y = pack_pair<T>(__uint_as_float(o0[v * 8 + 2]) * inverse, __uint_as_float(o0[v * 8 + 3]) * inverse);
-            word.z = pack_pair<T>(__uint_as_float(o0[v * 8 + 4]) * inverse, __uint_as_float(o0[v * 8 + 5]) * inverse);
-            word.w = pack_pair<T>(__uint_as_float(o0[v * 8 + 6]) * inverse, __uint_as_float(o0[v * 8 + 7]) * inverse);
-            *reinterpret_cast<uint4*>(out_row + v * 8) = word;
-            word.x = pack_pair<T>(__uint_as_float(o1[v * 8 + 0]) * inverse, __uint_as_float(o1[v * 8 + 1]) * inverse);
-            word.y = pack_pair<T>(__uint_as_float(o1[v * 8 + 2]) * inverse, __uint_as_float(o1[v * 8 + 3]) * inverse);
-            word.z = pack_pair<T>(__uint_as_float(o1[v * 8 + 4]) * inverse, __uint_as_float(o1[v * 8 + 5]) * inverse);
-            word.w = pack_pair<T>(__uint_as_float(o1[v * 8 + 6]) * inverse, __uint_as_float(o1[v * 8 + 7]) * inverse);
-            *reinterpret_cast<uint4*>(out_row + 32 + v * 8) = word;
+            if (v * 8 < width) {
+              word.x = pack_pair<T>(__uint_as_float(o0[v * 8 + 0]) * inverse, __uint_as_float(o0[v * 8 + 1]) * inverse);
+              word.y = pack_pair<T>(__uint_as_float(o0[v * 8 + 2]) * inverse, __uint_as_float(o0[v * 8 + 3]) * inverse);
+              word.z = pack_pair<T>(__uint_as_float(o0[v * 8 + 4]) * inverse, __uint_as_float(o0[v * 8 + 5]) * inverse);
+              word.w = pack_pair<T>(__uint_as_float(o0[v * 8 + 6]) * inverse, __uint_as_float(o0[v * 8 + 7]) * inverse);
+              *reinterpret_cast<uint4*>(out_row + v * 8) = word;
+            }
+            if (32 + v * 8 < width) {
+              word.x = pack_pair<T>(__uint_as_float(o1[v * 8 + 0]) * inverse, __uint_as_float(o1[v * 8 + 1]) * inverse);
+              word.y = pack_pair<T>(__uint_as_float(o1[v * 8 + 2]) * inverse, __uint_as_float(o1[v * 8 + 3]) * inverse);
+              word.z = pack_pair<T>(__uint_as_float(o1[v * 8 + 4]) * inverse, __uint_as_float(o1[v * 8 + 5]) * inverse);
+              word.w = pack_pair<T>(__uint_as_float(o1[v * 8 + 6]) * inverse, __uint_as_float(o1[v * 8 + 7]) * inverse);
+              *reinterpret_cast<uint4*>(out_row + 32 + v * 8) = word;
+            }
           }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            out_row[i] = from_compute<T, float>(__uint_as_float(o0[i]) * inverse);
-            out_row[32 + i] = from_compute<T, float>(__uint_as_float(o1[i]) * inverse);
+            if (i < width) out_row[i] = from_compute<T, float>(__uint_as_float(o0[i]) * inverse);
+            if (32 + i < width) out_row[32 + i] = from_compute<T, float>(__uint_as_float(o1[i]) * inverse);
           }
         }
       }
@@ -446,18 +452,20 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   }
 }
 
-// A four-axis map over one of Q, K, V: 64 contiguous elements, then tokens, heads, batch with the
-// caller's element strides; box = 64 x 128 x 1 x 1, 128-byte swizzle, rows beyond the tokens read 0.
-tq_status attention_map(CUtensorMap* map, tq_dtype dtype, const void* pointer, long long tokens, long long heads, long long batch,
-                        const int64_t* strides) {
+// A four-axis map over one of Q, K, V: `head_dim` contiguous elements, then tokens, heads, batch with
+// the caller's element strides; box = 64 x 128 x 1 x 1, 128-byte swizzle. Rows beyond the tokens read
+// 0, and so do the columns beyond a head narrower than 64: zeros add nothing to q . k and give
+// result columns nobody stores, so a narrow head runs through the same 64-wide tiles.
+tq_status attention_map(CUtensorMap* map, tq_dtype dtype, const void* pointer, long long head_dim, long long tokens, long long heads,
+                        long long batch, const int64_t* strides) {
   EncodeTiled encode = encode_tiled();
   TQ_REQUIRE(encode != nullptr, TQ_EXTERNAL, "the CUDA driver does not provide cuTensorMapEncodeTiled");
-  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(kHeadDim), static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(heads),
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(heads),
                               static_cast<cuuint64_t>(batch)};
   // an axis of extent 1 never moves, so its stride only has to be legal
-  const long long token_stride = tokens > 1 ? strides[2] : kHeadDim;
-  const long long head_stride = heads > 1 ? strides[1] : kHeadDim;
-  const long long batch_stride = batch > 1 ? strides[0] : kHeadDim;
+  const long long token_stride = tokens > 1 ? strides[2] : head_dim;
+  const long long head_stride = heads > 1 ? strides[1] : head_dim;
+  const long long batch_stride = batch > 1 ? strides[0] : head_dim;
   const cuuint64_t byte_strides[3] = {static_cast<cuuint64_t>(token_stride) * 2, static_cast<cuuint64_t>(head_stride) * 2,
                                       static_cast<cuuint64_t>(batch_stride) * 2};
   const cuuint32_t box[4] = {static_cast<cuuint32_t>(kHeadDim), static_cast<cuuint32_t>(kRows), 1, 1};
@@ -469,9 +477,9 @@ tq_status attention_map(CUtensorMap* map, tq_dtype dtype, const void* pointer, l
   return TQ_OK;
 }
 
-bool legal_strides(const void* pointer, const int64_t* strides, long long tokens, long long heads, long long batch) {
+bool legal_strides(const void* pointer, const int64_t* strides, long long head_dim, long long tokens, long long heads, long long batch) {
   if (!aligned_to(pointer, 16)) return false;
-  if (tokens > 1 && (strides[2] < kHeadDim || strides[2] % 8 != 0)) return false;
+  if (tokens > 1 && (strides[2] < head_dim || strides[2] % 8 != 0)) return false;
   if (heads > 1 && (strides[1] <= 0 || strides[1] % 8 != 0)) return false;
   if (batch > 1 && (strides[0] <= 0 || strides[0] % 8 != 0)) return false;
   return true;
@@ -504,16 +512,16 @@ extern "C" tq_status tq_attention_launch(tq_dtype dtype, const void* q, const vo
   TQ_REQUIRE(batch >= 0 && heads >= 0 && q_tokens >= 0 && k_tokens >= 0, TQ_INVALID_ARGUMENT,
              "negative extent in batch=%lld heads=%lld q_tokens=%lld k_tokens=%lld", (long long)batch, (long long)heads,
              (long long)q_tokens, (long long)k_tokens);
-  TQ_REQUIRE(head_dim == tq::kHeadDim, TQ_UNSUPPORTED, "fused attention has a kernel for heads of %d elements, not %lld", tq::kHeadDim,
-             (long long)head_dim);
+  TQ_REQUIRE(head_dim >= 8 && head_dim <= tq::kHeadDim && head_dim % 8 == 0, TQ_UNSUPPORTED,
+             "fused attention has a kernel for heads of 8, 16, ... %d elements, not %lld", tq::kHeadDim, (long long)head_dim);
   if (batch == 0 || heads == 0 || q_tokens == 0) return TQ_OK;
   TQ_REQUIRE(k_tokens > 0, TQ_UNSUPPORTED, "a softmax over no keys has no kernel");
   TQ_REQUIRE(std::isfinite(scale) && scale > 0.0, TQ_UNSUPPORTED, "the score scale must be positive and finite, not %g", scale);
   TQ_REQUIRE(q != nullptr && k != nullptr && v != nullptr && out != nullptr, TQ_INVALID_ARGUMENT, "null operand or result");
   TQ_REQUIRE(q_tokens < (1LL << 30) && k_tokens < (1LL << 30) && heads < 65536 && batch * heads < (1LL << 24), TQ_UNSUPPORTED,
              "extents beyond the kernel's index range");
-  TQ_REQUIRE(tq::legal_strides(q, q_strides, q_tokens, heads, batch) && tq::legal_strides(k, k_strides, k_tokens, heads, batch) &&
-                 tq::legal_strides(v, v_strides, k_tokens, heads, batch),
+  TQ_REQUIRE(tq::legal_strides(q, q_strides, head_dim, q_tokens, heads, batch) && tq::legal_strides(k, k_strides, head_dim, k_tokens, heads, batch) &&
+                 tq::legal_strides(v, v_strides, head_dim, k_tokens, heads, batch),
              TQ_UNSUPPORTED, "Q, K and V must be 16-byte aligned with positive strides that are multiples of 8 elements (TMA's rules)");
   TQ_REQUIRE(tq::aligned_to(out, 2) && out_strides[0] >= 0 && out_strides[1] >= 0 && out_strides[2] >= 0, TQ_INVALID_ARGUMENT,
              "misaligned result or negative result stride");
@@ -523,15 +531,16 @@ extern "C" tq_status tq_attention_launch(tq_dtype dtype, const void* q, const vo
   TQ_REQUIRE(status.abort != nullptr, TQ_RESOURCE_EXHAUSTED, "no device memory for the status word");
 
   CUtensorMap map_q, map_k, map_v;
-  if (tq_status s = tq::attention_map(&map_q, dtype, q, q_tokens, heads, batch, q_strides)) return s;
-  if (tq_status s = tq::attention_map(&map_k, dtype, k, k_tokens, heads, batch, k_strides)) return s;
-  if (tq_status s = tq::attention_map(&map_v, dtype, v, k_tokens, heads, batch, v_strides)) return s;
+  if (tq_status s = tq::attention_map(&map_q, dtype, q, head_dim, q_tokens, heads, batch, q_strides)) return s;
+  if (tq_status s = tq::attention_map(&map_k, dtype, k, head_dim, k_tokens, heads, batch, k_strides)) return s;
+  if (tq_status s = tq::attention_map(&map_v, dtype, v, head_dim, k_tokens, heads, batch, v_strides)) return s;
 
   tq::AttnParams p = {};
   p.batch = static_cast<int>(batch);
   p.heads = static_cast<int>(heads);
   p.q_tokens = static_cast<int>(q_tokens);
   p.k_tokens = static_cast<int>(k_tokens);
+  p.head_dim = static_cast<int>(head_dim);
   p.q_blocks = static_cast<int>((q_tokens + tq::kGroups * tq::kRows - 1) / (tq::kGroups * tq::kRows));
   p.causal = causal != 0;
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);

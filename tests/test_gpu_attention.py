@@ -76,6 +76,29 @@ def test_attention_matches_oracle(tq, shape, causal):
     assert poll() == 0
 
 
+@pytest.mark.parametrize("width", [8, 32, 48])
+@pytest.mark.parametrize("causal", [True, False], ids=["causal", "full"])
+def test_attention_with_heads_narrower_than_64(tq, width, causal):
+    """Heads of 8, 16, ... 56 elements ride in the kernel's 64-wide tiles: TMA fills the other columns
+    with zeros, which add nothing to q . k, and the result columns they produce are not stored."""
+    q = draw((2, 3, 200, width), torch.bfloat16, 21)
+    k = draw((2, 3, 333, width), torch.bfloat16, 22)
+    v = draw((2, 3, 333, width), torch.bfloat16, 23)
+    scale = width ** -0.5
+    guard = torch.full((2, 200, 3, width + 8), 7.0, dtype=torch.bfloat16, device="cuda")   # the result sits inside a wider buffer
+    got = tq.attention(q.cuda(), k.cuda(), v.cuda(), scale, causal)
+    check(got, q, k, v, scale, causal)
+    from tessiq_b200.kernel import AttentionKernel
+    AttentionKernel(scale, causal).launch([q.cuda(), k.cuda(), v.cuda()], guard[..., :width].transpose(1, 2), stream=None)
+    torch.cuda.synchronize()
+    assert torch.equal(guard[..., :width].transpose(1, 2), got) and (guard[..., width:] == 7.0).all()      # nothing beyond the head is written
+    # a fused projection of narrow heads, read in place
+    qkv = draw((2, 160, 3 * 4 * width), torch.float16, 24).cuda()
+    q, k, v = (z.view(2, 160, 4, width).transpose(1, 2) for z in qkv.split(4 * width, dim=-1))
+    check(tq.attention(q, k, v, scale, causal), q.cpu(), k.cpu(), v.cpu(), scale, causal)
+    assert poll() == 0
+
+
 def test_attention_golden(tq, golden):
     q, k, v = (torch.from_numpy(golden[n].copy()).view(torch.bfloat16) for n in ("attn_q", "attn_k", "attn_v"))
     for causal, name in ((True, "attn_causal_bf16"), (False, "attn_full_bf16")):
@@ -153,9 +176,10 @@ def test_attention_properties_at_the_decoder_block_size(tq):
 def test_attention_declines_what_it_has_no_kernel_for(tq):
     from tessiq_b200._lib import Declined
 
-    q = torch.zeros(1, 1, 16, 32, dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(Declined):
-        tq.attention(q, q, q, None, True)             # heads of 32 elements
+    for width in (128, 36):
+        q = torch.zeros(1, 1, 16, width, dtype=torch.bfloat16, device="cuda")
+        with pytest.raises(Declined):
+            tq.attention(q, q, q, None, True)         # heads wider than 64, or not a multiple of 8 elements
     q = torch.zeros(1, 1, 16, 64, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(Declined):
         tq.attention(q, q, q, -1.0, True)             # a negative scale turns the maximum into a minimum
