@@ -663,6 +663,14 @@ def other_configs(device: int, stream) -> dict:
     out["config4_causal_attention_bf16"] = {"us": round(seconds * 1e6, 1), "tflops_causal": round(masked_flop / seconds / 1e12, 1),
                                             "note": "one fused kernel; flop counted over the lower triangle only"}
     del qkv, q, k, v
+    # the same attention with 6 heads of 128 elements (the same flop): two 64-wide sub-tiles side by side, one group per CTA
+    qkv = torch.randn(64, 1024, 3 * 768, device=dev).bfloat16()
+    q, k, v = (z.view(64, 1024, 6, 128).transpose(1, 2) for z in qkv.split(768, dim=-1))
+    with torch.cuda.stream(stream):
+        seconds = timed(lambda: ops.attention(q, k, v, None, True), 10)
+    out["causal_attention_heads_of_128_bf16"] = {"us": round(seconds * 1e6, 1), "tflops_causal": round(masked_flop / seconds / 1e12, 1),
+                                                 "note": "64 x 6 heads x 1024 tokens x 128; not tuned (half the softmax warps idle)"}
+    del qkv, q, k, v
     out["config4_decoder_block_bf16"] = decoder_block(dev, stream)
     return out
 
@@ -895,7 +903,10 @@ def kernel_name(step, name: str, label: str) -> str:
                 "three-pass": f"reduce_columns<statistics> + transpose_normalize_kernel<{kind}>"}[form]
     if label.endswith("_rows"):
         return {"softmax_rows": "row_cluster_kernel<softmax>", "layer_norm_rows": "row_cluster_kernel<LayerNorm>"}.get(label, "reduce_warp_per_slice")
-    return "pack_transpose_blocks" if label == "pack" else "reduce_columns"
+    if label == "pack":
+        return "pack_transpose_blocks"
+    # column reductions: 2-byte types and argmax stream TMA tiles through shared memory (reduce.cu: plan_stream)
+    return "reduce_columns_stream" if (dtype != step.torch.float32 or label.startswith("argmax")) else "reduce_columns"
 
 
 # ---------------------------------------------------------------------------------------------

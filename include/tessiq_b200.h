@@ -445,8 +445,9 @@ tq_status tq_gemm_bias_act_residual_launch(tq_dtype dtype,
  *   {batch, head, token} and its head_dim elements are contiguous — so the slices of a fused QKV
  *   projection are read where they lie and the result can be written in [batch, token, head, dim]
  *   order.
- * head_dim is 8, 16, ... 64 (a head narrower than 64 rides in the kernel's 64-wide tiles, whose other
- * columns TMA fills with zeros). Declines (TQ_UNSUPPORTED): any other head_dim, a scale that is not positive and finite, q/k/v that
+ * head_dim is 8, 16, ... 128: the kernel works on 64-wide tiles, one per head up to 64 elements and two
+ * side by side beyond (then one group of 128 query rows per CTA instead of two); the columns a head
+ * does not have are filled with zeros by TMA. Declines (TQ_UNSUPPORTED): any other head_dim, a scale that is not positive and finite, q/k/v that
  * are not 16-byte aligned or whose strides are not positive multiples of 8 elements (TMA's rules).
  * Bounded waits report through tq_status_poll like the GEMM's. */
 tq_status tq_attention_launch(tq_dtype dtype,

@@ -394,8 +394,9 @@ def _sdpa_targets() -> dict:
 
 SDPA = _sdpa_targets()
 
-#: head widths the fused attention kernel takes (narrower than 64: zero-filled columns of its 64-wide tiles)
-HEAD_WIDTHS = (8, 16, 24, 32, 40, 48, 56, 64)
+#: head widths the fused attention kernel takes (64-wide tiles, one or two side by side; columns a head
+#: does not have are filled with zeros)
+HEAD_WIDTHS = tuple(range(8, 129, 8))
 
 
 def _attention_step(match: Attention) -> Step:
@@ -424,7 +425,7 @@ def _attention_step(match: Attention) -> Step:
 
 def _sdpa_step(node: fx.Node) -> Step | None:
     """One of ATen's fused attention operators, when only its first result is read and it asks for
-    nothing the kernel lacks (dropout, a bias, a head wider than 64)."""
+    nothing the kernel lacks (dropout, a bias, a head wider than 128)."""
     bias_at, causal_at = SDPA[node.target]
     args = list(node.args)
     q, k, v = args[:3]

