@@ -375,12 +375,30 @@ def batch_norm_eval(x, weight, bias, running_mean, running_var, eps):
 # GEMM
 
 
+def _realigned(t):
+    """A GEMM operand whose first element is not 16-byte aligned (a view that starts inside an
+    allocation: tests/python/test_gemm_bias_gelu_tanh.py:129-139 of the reference), copied by the pack
+    kernel into a fresh allocation, which is. TMA cannot read the operand where it lies; the copy costs
+    one pass over it. Other operands come back as they are."""
+    if t is None or t.data_ptr() % 16 == 0 or t.numel() == 0:
+        return t
+    fresh = torch.empty(t.shape, dtype=t.dtype, device=t.device)
+    PackKernel().launch([t], fresh, stream=None)
+    return fresh
+
+
 def _gemm(a, b, bias, activation, residual=None):
     out = torch.empty([*a.shape[:-1], b.shape[-1]], dtype=a.dtype, device=a.device)
     if out.numel() == 0:
         return out
     kernel = GemmKernel(activation, has_bias=bias is not None, has_residual=residual is not None)
-    kernel.launch([t for t in (a, b, bias, residual) if t is not None], out, stream=None)
+    try:
+        kernel.launch([t for t in (a, b, bias, residual) if t is not None], out, stream=None)
+    except Declined:
+        moved = [_realigned(t) for t in (a, b, bias, residual)]
+        if all(m is t for m, t in zip(moved, (a, b, bias, residual))):
+            raise                        # nothing was misaligned: the decline has another reason (f32, a ragged leading dimension)
+        kernel.launch([t for t in moved if t is not None], out, stream=None)
     return out
 
 

@@ -172,6 +172,26 @@ def test_bmm_and_padded_leading_dimensions(tq):
     check(tq.mm(a_view, bb.cuda()), truth(a_view.cpu(), bb, None, None), torch.bfloat16, 72)
 
 
+def test_an_operand_that_starts_inside_an_allocation_is_copied_to_an_aligned_one(tq):
+    """tests/python/test_gemm_bias_gelu_tanh.py:129-139 of the reference: x starts a few bytes into its
+    storage. TMA cannot read it there; the pack kernel moves it (one pass) and the tensor-core kernel runs."""
+    g = torch.Generator().manual_seed(12)
+    x = (torch.randn(64, 128, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(96, 128, generator=g) * 0.5).bfloat16()
+    b = torch.randn(96, generator=g).bfloat16()
+    storage = torch.empty(64 * 128 + 2, dtype=torch.bfloat16, device="cuda")
+    shifted = storage[2:].view(64, 128)
+    shifted.copy_(x)
+    assert shifted.data_ptr() % 16 == 4
+    got = tq.gemm_bias_gelu_tanh(shifted, w.cuda(), b.cuda())
+    check(got, truth(x, w.t(), b, "gelu_tanh"), torch.bfloat16, 128)
+    w_storage = torch.empty(96 * 128 + 4, dtype=torch.bfloat16, device="cuda")
+    w_shifted = w_storage[4:].view(96, 128)
+    w_shifted.copy_(w)
+    check(tq.gemm_bias_gelu_tanh(shifted, w_shifted, b.cuda()), truth(x, w.t(), b, "gelu_tanh"), torch.bfloat16, 128)
+    assert poll() == 0
+
+
 def test_declines_and_empty(tq):
     a, b = torch.randn(16, 16, device="cuda"), torch.randn(16, 16, device="cuda")
     with pytest.raises(TypeError):
