@@ -835,17 +835,29 @@ def compile_graph(gm: fx.GraphModule, example_inputs, *, mode: str | None = None
         runners.append(runner)
         return make_boxed_func(lambda *args: runner.run(*args))
 
-    fn = aot_autograd(fw_compiler=compile_forward, decompositions=_decompositions())(gm, example_inputs)
     if devices is not None and len(devices) > 1:
         # the batch is split over the GPUs of one runtime: the arguments named by `shard` (default: every
-        # tensor argument that is not a parameter of the module) along dim 0, the others replicated
+        # tensor argument that is not a parameter of the module) along dim 0, the others replicated.
+        # AOTAutograd bakes the example inputs' sizes into the ATen graph (a Linear over [batch, tokens,
+        # width] becomes a view to [batch * tokens, width]), so each GPU's recipe is built from ITS
+        # shard's shapes, on that GPU, the first time a shard of those shapes arrives.
         from .runtime import Runtime, ShardedRunner
 
         positions = list(shard) if shard is not None else [i for i, a in enumerate(example_inputs)
                                                            if isinstance(a, torch.Tensor) and not isinstance(a, torch.nn.Parameter) and a.dim() > 0]
-        single = fn
+        built: dict = {}
+
+        def single(*args):
+            key = tuple((tuple(a.shape), a.dtype, a.device.index) if isinstance(a, torch.Tensor) else a for a in args)
+            made = built.get(key)
+            if made is None:
+                made = built[key] = aot_autograd(fw_compiler=compile_forward, decompositions=_decompositions())(gm, list(args))
+            return made(*args)
+
         fn = ShardedRunner(Runtime(devices), single, positions)
         fn.devices = devices
+    else:
+        fn = aot_autograd(fw_compiler=compile_forward, decompositions=_decompositions())(gm, example_inputs)
     fn.recipes = compiled  # for tests and reports: which kernels a graph became
     fn.runners = runners
     return fn

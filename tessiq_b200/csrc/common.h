@@ -44,10 +44,12 @@ class DeviceScope {
   explicit DeviceScope(int32_t device) {
     if (cudaGetDevice(&previous_) != cudaSuccess) previous_ = -1;
     status_ = use_device(device);
-    changed_ = status_ == TQ_OK && previous_ >= 0 && previous_ != device;
   }
+  // Whatever the block did in between (the runtime handle's calls walk over several GPUs), the thread
+  // leaves on the device it came with.
   ~DeviceScope() {
-    if (changed_) cudaSetDevice(previous_);
+    int now = -1;
+    if (previous_ >= 0 && cudaGetDevice(&now) == cudaSuccess && now != previous_) cudaSetDevice(previous_);
   }
   DeviceScope(const DeviceScope&) = delete;
   DeviceScope& operator=(const DeviceScope&) = delete;
@@ -56,7 +58,6 @@ class DeviceScope {
  private:
   int previous_ = -1;
   tq_status status_ = TQ_OK;
-  bool changed_ = false;
 };
 
 // Number of SMs of `device` (cached).

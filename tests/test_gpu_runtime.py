@@ -239,6 +239,7 @@ def test_runtime_handle_streams_and_arena_slices(abi):
     runtime.release()
     assert runtime.used(0) == 0
     runtime.close()
+    assert torch.cuda.current_device() == 0     # fork, join, synchronize and close walk over the GPUs and come back
 
 
 def test_scratch_that_grows_between_a_capture_and_its_replay_stays_valid():
