@@ -254,6 +254,14 @@ TQ_DEV void tq_read_strided(const void* pointer, Index idx, const tq_layout_t& l
     tq_load_bytes<sizeof(raw) * VEC>((const raw*)pointer + tq_unravel<Index>(layout, idx), x.v);
 #pragma unroll
     for (int e = 0; e < VEC; ++e) out[e] = tq_storage<S>::load(x.v[e]);
+  } else if (VEC > 1 && layout.rank > 0 && layout.sizes[layout.rank - 1] % VEC == 0) {
+    // the vector's elements share every coordinate but the innermost (a tile starts on a multiple of VEC,
+    // the innermost extent is one): one unravel, then steps of the innermost stride — a column slice, an
+    // every-other-column view and a broadcast innermost axis (stride 0) all come here
+    const long long first = tq_unravel<Index>(layout, idx);
+    const long long step = layout.strides[layout.rank - 1];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) out[e] = tq_read_one<S, long long>(pointer, first + (long long)e * step);
   } else {
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
