@@ -4,7 +4,7 @@
 # reference's own answers. The reference tree is read-only, so it is copied to a scratch directory
 # first; nothing of it is copied into this repository (oracle/_ref/ is ignored by git).
 #
-#   oracle/build_ref.sh [/path/to/reference]      (default /root/reference)
+#   oracle/build_ref.sh [/path/to/reference]      (without an argument: the checkout this script is set up for, REFERENCE below)
 #
 # Takes about two minutes on 8 cores. Needs cmake, ninja, a host g++ with a shared libstdc++
 # (/usr/bin/g++), pybind11 and the PyTorch the reference pins.
