@@ -393,11 +393,17 @@ def prefers_transposed(kind: str, dtype: torch.dtype, batch: int = 0, rows: int 
     """Whether op(x.transpose(-1, -2), -1) should take the in-place path rather than pack-then-rows
     (4 passes). Always when the shape takes the two-pass slab kernel. For the three-pass form,
     measured on B200 at [32768, 4096]: it wins for 4-byte softmax (310 vs 357 us) and for LayerNorm
-    (f32 331 vs 394, bf16 214 vs 238); for 2-byte softmax its statistics pass is issue-bound and
-    pack-then-rows stays ahead (198 vs 228 us)."""
+    (f32 331 vs 394, bf16 214 vs 238); for 2-byte softmax its statistics pass was issue-bound and
+    pack-then-rows stayed ahead (198 vs 228 us) until the statistics came from the streaming reduction
+    with sixteen consumer warps (189 vs 193 us); smaller or ragged 2-byte tensors still pack first."""
     if kind == "layer_norm" or dtype.itemsize >= 4:
         return True
-    return rows > 0 and transposed_passes(kind, dtype, batch, rows, cols) == 2
+    if rows > 0 and transposed_passes(kind, dtype, batch, rows, cols) == 2:
+        return True
+    # 2-byte softmax where the statistics pass is the persistent streaming reduction (64 MiB and more, rows a
+    # multiple of 64, row bytes a multiple of 512): measured 190 us against 193 for pack-then-rows, three passes
+    # over HBM instead of four
+    return batch * rows * cols * dtype.itemsize >= (64 << 20) and rows % 64 == 0 and (cols * dtype.itemsize) % 512 == 0
 
 
 def launch_transposed(kind: str, base: torch.Tensor, weight, bias, out: torch.Tensor, batch: int, rows: int, cols: int,

@@ -521,6 +521,13 @@ def test_column_reductions_of_large_tensors_stream_through_shared_memory(tq, dty
     assert ((got - truth / shape[-2]).abs() <= half_ulp * (truth / shape[-2]).abs() + sum_budget(clean, dim) / shape[-2]).all()
     again = tq.sum(cd, dim).cpu().double()              # fixed merge order: the same bits every time
     assert torch.equal(again, tq.sum(cd, dim).cpu().double())
+    if dtype != torch.float32 and len(shape) == 2:
+        # softmax and LayerNorm over the transposed view of the same tensor: their statistics pass is this kernel
+        # (sixteen consumer warps for the softmax statistics of 2-byte elements), then the transposing normalise
+        from tessiq_b200 import kernel as K
+        assert K.prefers_transposed("softmax", dtype, 1, shape[0], shape[1]) and K.transposed_form("softmax", dtype, 1, shape[0], shape[1]) == "three-pass"
+        close16(tq.softmax(cd.t(), -1), tessiq0.softmax(clean.t(), -1))
+        close16(tq.layer_norm(cd.t(), [shape[0]]), tessiq0.native_layer_norm(clean.t(), [shape[0]], None, None, 1e-5)[0])
     status = ctypes.c_int32(-1)
     from tessiq_b200 import kernel as K
     K.check(K.lib.tq_status_poll(0, None, ctypes.byref(status)))
