@@ -305,7 +305,8 @@ _WAIT_CODES = {0x53454c46: "the bounded-wait self test", 0x504e4c31: "panel norm
                0x504e4c32: "panel normalisation: a stage's data never arrived", 0x504e4c33: "panel normalisation: a stage was never handed back",
                0x504e4c34: "panel normalisation: the publishers' next item never came", 0x504e4c35: "panel normalisation: accumulators never handed back",
                0x504e4c36: "panel normalisation: a statistics buffer was never handed back", 0x504e4c37: "panel normalisation: statistics never reached shared memory",
-               0x504e4c38: "panel normalisation: the second visit never caught up", 0x504e4c39: "panel normalisation: a stage arrived out of order"}
+               0x504e4c38: "panel normalisation: the second visit never caught up", 0x504e4c39: "panel normalisation: a stage arrived out of order",
+               0x53544d31: "streaming column reduction: a tile's data never arrived", 0x53544d32: "streaming column reduction: a stage was never handed back"}
 
 
 def check_status(device: int = 0, stream: int | None = None) -> None:
