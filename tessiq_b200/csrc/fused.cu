@@ -732,9 +732,9 @@ std::string generate(const Program& p) {
   int divisor = 0, layout = 0;
   for (const Input& in : p.inputs) {
     if (in.read == Read::kRepeated || in.read == Read::kCycled) {
-      params << ", long long d" << divisor;
-      tile_params << ", Index d" << divisor;
-      forward << ", (Index)d" << divisor;
+      params << ", long long d" << divisor << ", unsigned long long m" << divisor;
+      tile_params << ", Index d" << divisor << ", unsigned long long m" << divisor;
+      forward << ", (Index)d" << divisor << ", m" << divisor;
       ++divisor;
     }
   }
@@ -765,10 +765,12 @@ std::string generate(const Program& p) {
           r << "      tq_read_same<tq_s" << k << ", " << width << ", Index>(p" << k << ", " << index << ", " << target << k << target_suffix << ");\n";
           break;
         case Read::kCycled:
-          r << "      tq_read_cycled<tq_s" << k << ", " << width << ", Index>(p" << k << ", " << index << ", d" << d++ << ", (flags >> " << k << ") & 1u, " << target << k << target_suffix << ");\n";
+          r << "      tq_read_cycled<tq_s" << k << ", " << width << ", Index>(p" << k << ", " << index << ", d" << d << ", m" << d << ", (flags >> " << k << ") & 1u, " << target << k << target_suffix << ");\n";
+          ++d;
           break;
         case Read::kRepeated:
-          r << "      tq_read_repeated<tq_s" << k << ", " << width << ", Index>(p" << k << ", " << index << ", d" << d++ << ", (flags >> " << k << ") & 1u, " << target << k << target_suffix << ");\n";
+          r << "      tq_read_repeated<tq_s" << k << ", " << width << ", Index>(p" << k << ", " << index << ", d" << d << ", m" << d << ", (flags >> " << k << ") & 1u, " << target << k << target_suffix << ");\n";
+          ++d;
           break;
         case Read::kStrided:
           r << "      tq_read_strided<tq_s" << k << ", " << width << ", Index>(p" << k << ", " << index << ", l" << l++ << ", (flags >> " << k << ") & 1u, " << target << k << target_suffix << ");\n";
@@ -1120,15 +1122,29 @@ tq_status tq_fused_launch(const tq_fused* kernel, const void* const* inputs, voi
   long long n_slot = elements;
   arguments.push_back(&out_slot);
   arguments.push_back(&n_slot);
+  // Each divisor and each extent of a layout travels with floor(2^64 / d) + 1, which turns the kernels'
+  // 32-bit `/` and `%` into a multiplication (tq_quotient in the prelude).
+  auto magic_of = [](long long d) { return d == 1 ? ~0ull : ~0ull / static_cast<unsigned long long>(d) + 1ull; };
   std::vector<long long> divisor_slots(p.divisors);
+  std::vector<unsigned long long> magic_slots(p.divisors);
   for (int j = 0; j < p.divisors; ++j) {
     divisor_slots[j] = divisors[j];
+    magic_slots[j] = magic_of(divisors[j]);
     arguments.push_back(&divisor_slots[j]);
+    arguments.push_back(&magic_slots[j]);
   }
-  std::vector<tq_layout> layout_slots(p.layouts);
+  struct DeviceLayout { int rank; long long sizes[8]; long long strides[8]; unsigned long long magics[8]; };   // tq_layout_t of the prelude
+  std::vector<DeviceLayout> layout_slots(p.layouts);
   for (int j = 0; j < p.layouts; ++j) {
-    layout_slots[j] = layouts[j];
-    arguments.push_back(&layout_slots[j]);
+    DeviceLayout& l = layout_slots[j];
+    l = DeviceLayout{};
+    l.rank = layouts[j].rank;
+    for (int d = 0; d < l.rank; ++d) {
+      l.sizes[d] = layouts[j].sizes[d];
+      l.strides[d] = layouts[j].strides[d];
+      l.magics[d] = magic_of(layouts[j].sizes[d]);
+    }
+    arguments.push_back(&l);
   }
   arguments.push_back(&flags);
   union Slot { float f; double d; int i; long long l; bool b; };

@@ -18,7 +18,7 @@ struct tq_f16_tag { unsigned short bits; };
 #define TQ_DEV __device__ __forceinline__
 #define TQ_BLOCK 256
 
-struct tq_layout_t { int rank; long long sizes[8]; long long strides[8]; };
+struct tq_layout_t { int rank; long long sizes[8]; long long strides[8]; unsigned long long magics[8]; };   // magics: see tq_quotient
 
 // ---- conversions between storage and compute types --------------------------------------
 template <typename S> struct tq_storage;   // ::compute, ::load(S) -> compute, ::store(compute) -> S
@@ -190,12 +190,24 @@ TQ_DEV typename tq_storage<S>::compute tq_read_one(const void* pointer, Index po
   return tq_storage<S>::load(__ldg((const raw*)pointer + position));
 }
 
+// i / d without a division. For 32-bit indices the host passes magic = floor(2^64 / d) + 1 (2^64 - 1
+// for d = 1): the high half of idx * magic is the quotient for every idx below 2^32 and every d below
+// 2^32 (the excess of magic * d over 2^64 is at most d, so the error stays below 2^-32 <= 1 / d); the
+// single correction step covers d = 1. A 32-bit `/` or `%` costs about sixteen instructions, three of
+// them on the special-function unit that the exponentials of a fused chain need.
+TQ_DEV unsigned tq_quotient(unsigned idx, unsigned divisor, unsigned long long magic) {
+  unsigned q = (unsigned)__umul64hi(magic, (unsigned long long)idx);
+  if (idx - q * divisor >= divisor) ++q;
+  return q;
+}
+TQ_DEV long long tq_quotient(long long idx, long long divisor, unsigned long long) { return idx / divisor; }
+
 // i % d: a row that repeats, such as a bias.
 template <typename S, int VEC, typename Index>
-TQ_DEV void tq_read_cycled(const void* pointer, Index idx, Index divisor, bool fast,
+TQ_DEV void tq_read_cycled(const void* pointer, Index idx, Index divisor, unsigned long long magic, bool fast,
                            typename tq_storage<S>::compute (&out)[VEC]) {
   typedef typename tq_storage<S>::raw raw;
-  Index position = idx % divisor;
+  Index position = idx - tq_quotient(idx, divisor, magic) * divisor;
   if (VEC > 1 && fast) {
     tq_raw_vec<S, VEC> x;
     tq_load_bytes_cached<sizeof(raw) * VEC>((const raw*)pointer + position, x.v);
@@ -212,9 +224,9 @@ TQ_DEV void tq_read_cycled(const void* pointer, Index idx, Index divisor, bool f
 
 // i / d: one value per run of d outputs, such as an [N, 1] column.
 template <typename S, int VEC, typename Index>
-TQ_DEV void tq_read_repeated(const void* pointer, Index idx, Index divisor, bool fast,
+TQ_DEV void tq_read_repeated(const void* pointer, Index idx, Index divisor, unsigned long long magic, bool fast,
                              typename tq_storage<S>::compute (&out)[VEC]) {
-  Index position = idx / divisor;
+  Index position = tq_quotient(idx, divisor, magic);
   if (VEC > 1 && fast) {
     const typename tq_storage<S>::compute value = tq_read_one<S, Index>(pointer, position);
 #pragma unroll
@@ -236,8 +248,9 @@ TQ_DEV long long tq_unravel(const tq_layout_t& layout, Index idx) {
   for (int d = 7; d >= 0; --d) {
     if (d < layout.rank) {
       const Index extent = (Index)layout.sizes[d];
-      const Index coordinate = idx % extent;
-      idx /= extent;
+      const Index quotient = tq_quotient(idx, extent, layout.magics[d]);
+      const Index coordinate = idx - quotient * extent;
+      idx = quotient;
       offset += (long long)coordinate * layout.strides[d];
     }
   }

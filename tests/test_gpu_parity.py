@@ -233,6 +233,24 @@ def test_binary_ops_and_broadcast_forms(tq, op):
         torch.testing.assert_close(got.cpu(), tessiq0.elementwise(op, torch.tensor(1.0), a), rtol=2e-6, atol=1e-5)
 
 
+@pytest.mark.parametrize("shape", [(32771, 4097), (3, 1, 44739243), (8191, 3, 5461)])
+def test_broadcast_positions_without_a_division_at_large_indices(tq, shape):
+    # The kernels turn i / d and i % d into a multiplication by a constant the host derives from d; odd
+    # extents and indices up to 2^27 hold that against the oracle, bit for bit, for a repeating row, a
+    # value per row, one element and a transposed view.
+    g = torch.Generator().manual_seed(17)
+    a = torch.randn(shape, generator=g)
+    row = torch.randn(shape[-1], generator=g)
+    column = torch.randn(shape[:-1] + (1,), generator=g)
+    one = torch.randn(1, generator=g)
+    assert torch.equal(tq.elementwise("add", dev(a), dev(row)).cpu(), tessiq0.elementwise("add", a, row))
+    assert torch.equal(tq.elementwise("mul", dev(a), dev(column)).cpu(), tessiq0.elementwise("mul", a, column))
+    assert torch.equal(tq.elementwise("sub", dev(a), dev(one)).cpu(), tessiq0.elementwise("sub", a, one))
+    if len(shape) == 2:
+        b = torch.randn(shape[1], shape[0], generator=g)
+        assert torch.equal(tq.elementwise("add", dev(a), dev(b).t()).cpu(), tessiq0.elementwise("add", a, b.t()))
+
+
 def test_strided_operands_are_read_in_place(tq):
     g = torch.Generator().manual_seed(13)
     a = torch.randn(64, 48, generator=g)
