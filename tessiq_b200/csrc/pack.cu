@@ -67,11 +67,12 @@ pack_transpose_kernel(const W* __restrict__ src, W* __restrict__ dst, View view,
   const long long rows = view.sizes[row_axis], cols = view.sizes[last];
   const long long col_stride = view.strides[last];
 
-  long long tile_id = blockIdx.x;
-  const long long col_tile = tile_id % col_tiles;
-  tile_id /= col_tiles;
-  const long long row_tile = tile_id % row_tiles;
-  long long batch = tile_id / row_tiles;
+  // the grid holds fewer than 2^31 tiles: 32-bit divisions, a quarter of the instructions of 64-bit ones
+  unsigned tile_id = blockIdx.x;
+  const long long col_tile = tile_id % static_cast<unsigned>(col_tiles);
+  tile_id /= static_cast<unsigned>(col_tiles);
+  const long long row_tile = tile_id % static_cast<unsigned>(row_tiles);
+  long long batch = tile_id / static_cast<unsigned>(row_tiles);
 
   // Unravel the batch index over the remaining axes; `dst_stride` is the packed stride.
   long long src_base = 0, dst_base = 0, dst_stride = cols, row_dst_stride = 0;
@@ -128,11 +129,12 @@ pack_transpose_blocks(const W* __restrict__ src, W* __restrict__ dst, View view,
   const long long rows = view.sizes[row_axis], cols = view.sizes[last];
   const long long col_stride = view.strides[last];
 
-  long long tile_id = blockIdx.x;
-  const long long col_tile = tile_id % col_tiles;
-  tile_id /= col_tiles;
-  const long long row_tile = tile_id % row_tiles;
-  long long batch = tile_id / row_tiles;
+  // the grid holds fewer than 2^31 tiles: 32-bit divisions, a quarter of the instructions of 64-bit ones
+  unsigned tile_id = blockIdx.x;
+  const long long col_tile = tile_id % static_cast<unsigned>(col_tiles);
+  tile_id /= static_cast<unsigned>(col_tiles);
+  const long long row_tile = tile_id % static_cast<unsigned>(row_tiles);
+  long long batch = tile_id / static_cast<unsigned>(row_tiles);
   long long src_base = 0, dst_base = 0, dst_stride = cols, row_dst_stride = 0;
   for (int d = last - 1; d >= 0; --d) {
     if (d == row_axis) {
@@ -267,11 +269,11 @@ transpose_normalize_kernel(const T* __restrict__ in, T* __restrict__ out, const 
                            const T* __restrict__ weight, const T* __restrict__ bias, long long rows, long long cols,
                            long long row_tiles, long long col_tiles, float eps) {
   constexpr int kTile = 16 * V;
-  long long tile_id = blockIdx.x;
-  const long long col_tile = tile_id % col_tiles;
-  tile_id /= col_tiles;
-  const long long row_tile = tile_id % row_tiles;
-  const long long batch = tile_id / row_tiles;
+  unsigned tile_id = blockIdx.x;   // fewer than 2^31 tiles: 32-bit divisions
+  const long long col_tile = tile_id % static_cast<unsigned>(col_tiles);
+  tile_id /= static_cast<unsigned>(col_tiles);
+  const long long row_tile = tile_id % static_cast<unsigned>(row_tiles);
+  const long long batch = tile_id / static_cast<unsigned>(row_tiles);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c_block = (lane & 7) + 8 * (warp & 1);
   const int r_block = (lane >> 3) + 4 * (warp >> 1);

@@ -638,11 +638,15 @@ struct StreamArgs {
   WaitStatus status;
 };
 
-__device__ __forceinline__ long long stream_first_unit(long long cta, long long units, long long grid) { return cta * units / grid; }
+// units * grid stays below 2^32 (the plan declines otherwise), so the kernel's divisions are 32-bit ones:
+// a 64-bit division is about a hundred dependent instructions, and a segment's end runs six of them.
+__device__ __forceinline__ long long stream_first_unit(long long cta, long long units, long long grid) {
+  return static_cast<unsigned>(cta * units) / static_cast<unsigned>(grid);
+}
 
 // The CTA whose range holds `unit`.
 __device__ __forceinline__ int stream_owner(long long unit, long long units, int grid) {
-  long long c = unit * grid / units;
+  long long c = static_cast<unsigned>(unit * grid) / static_cast<unsigned>(units);
   while (c + 1 < grid && stream_first_unit(c + 1, units, grid) <= unit) ++c;
   while (c > 0 && stream_first_unit(c, units, grid) > unit) --c;
   return static_cast<int>(c);
@@ -686,9 +690,9 @@ reduce_columns_stream(const __grid_constant__ CUtensorMap map, const StreamArgs 
     // ---- producer ---------------------------------------------------------------------------------
     if (lane == 0) {
       for (long long u = first; u < last; ++u) {
-        const long long panel = u / upp;
+        const long long panel = static_cast<unsigned>(u) / static_cast<unsigned>(upp);
         const int unit = static_cast<int>(u - panel * upp);
-        const long long slice = panel / args.panels_per_slice;
+        const long long slice = static_cast<unsigned>(panel) / static_cast<unsigned>(args.panels_per_slice);
         const int column = static_cast<int>(panel - slice * args.panels_per_slice) * kColumns;
         if (!barrier_wait(empty0 + 8 * stage, phase ^ 1, args.status, kStatusStreamRing)) break;
         barrier_expect_tx(full0 + 8 * stage, kStreamStageBytes);
@@ -719,7 +723,7 @@ reduce_columns_stream(const __grid_constant__ CUtensorMap map, const StreamArgs 
   // ---- consumers: a segment is the part of the CTA's range that lies in one panel --------------------
   bool alive = true;
   for (long long u = first; u < last && alive;) {
-    const long long panel = u / upp;
+    const long long panel = static_cast<unsigned>(u) / static_cast<unsigned>(upp);
     const long long panel_first = panel * upp;
     long long segment_end = panel_first + upp;
     if (segment_end > last) segment_end = last;
@@ -776,7 +780,7 @@ reduce_columns_stream(const __grid_constant__ CUtensorMap map, const StreamArgs 
     const int owner_first = stream_owner(panel_first, args.units, grid);
     const int owner_last = stream_owner(panel_first + upp - 1, args.units, grid);
     const int sharers = owner_last - owner_first + 1;
-    const long long slice = panel / args.panels_per_slice;
+    const long long slice = static_cast<unsigned>(panel) / static_cast<unsigned>(args.panels_per_slice);
     typename R::Out* out_row = out + slice * args.inner + (panel - slice * args.panels_per_slice) * kColumns;
     Acc* panel_partials = partials + panel * args.slots * kColumns;
     for (int column = threadIdx.x; column < kColumns; column += kConsumerThreads) {
@@ -861,6 +865,7 @@ bool plan_stream(Plan& p, tq_reduce_op op, tq_dtype dtype, long long outer, long
   const long long panels = outer * (inner * size / kStreamPieceBytes);
   const long long units = panels * (reduce / kStreamUnitRows);
   if (units < 4ll * sms || panels > (1ll << 24)) return false;
+  if (units * (sms + 1) >= (1ll << 32)) return false;   // the kernel divides unit x CTA products as 32-bit numbers
   p.shape = Shape::kColumnStream;
   p.device = device;
   p.grid = sms;
