@@ -472,6 +472,8 @@ reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long
             if constexpr (R::kSeeded) {
 #pragma unroll
               for (int e = 0; e < VEC; ++e) R::template step_seeded<1>(local[e], x.v[e]);
+            } else if constexpr (has_column_step<R>::value) {
+              R::template step_columns<VEC>(local, x);
             } else {
 #pragma unroll
               for (int e = 0; e < VEC; ++e) R::template step<1>(local[e], x.v[e], ri);
@@ -499,8 +501,12 @@ reduce_columns(const T* __restrict__ in, typename R::Out* __restrict__ out, long
         for (int u = 0; u < UNROLL; ++u) {
           const long long ri = r + static_cast<long long>(u) * lanes_y;
           if (ri < end) {
+            if constexpr (has_column_step<R>::value) {
+              R::template step_columns<VEC>(local, x[u]);
+            } else {
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) R::template step<1>(local[e], x[u].v[e], ri);
+              for (int e = 0; e < VEC; ++e) R::template step<1>(local[e], x[u].v[e], ri);
+            }
           }
         }
       }
@@ -749,12 +755,16 @@ reduce_columns_stream(const __grid_constant__ CUtensorMap map, const StreamArgs 
 #pragma unroll
       for (int i = 0; i < kRowsPerWarp; ++i) {
         const Vec<T, V> x = mine[i * kStreamConsumers * (kStreamPieceBytes / 16)];
+        if constexpr (has_column_step<R>::value) {
+          R::template step_columns<V>(local, x);
+        } else {
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-          if constexpr (R::kSeeded) {
-            R::template step_seeded<1>(local[e], x.v[e]);
-          } else {
-            R::template step<1>(local[e], x.v[e], row);
+          for (int e = 0; e < V; ++e) {
+            if constexpr (R::kSeeded) {
+              R::template step_seeded<1>(local[e], x.v[e]);
+            } else {
+              R::template step<1>(local[e], x.v[e], row);
+            }
           }
         }
         row += kStreamConsumers;

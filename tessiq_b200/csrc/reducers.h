@@ -122,6 +122,28 @@ struct SoftmaxStatReducer {
 #pragma unroll
     for (int e = 0; e < VEC; ++e) step<VEC>(local, x.v[e], 0);
   }
+  // One row of V neighbouring columns, each with its own accumulator: the test for "far above the
+  // reference" is taken once for the V elements, so that the common path is V independent
+  // subtract-scale / ex2 / add chains with no branch between them (with a branch per element the ex2
+  // latency of every element was exposed, and the pass ran at that latency rather than at the memory's
+  // rate). The rare path is the per-element step; both give the same bits as V calls of `step`.
+  static constexpr bool kColumnStep = true;
+  template <int V> __device__ static void step_columns(Acc (&local)[V], const Vec<T, V>& x) {
+    float t[V];
+    bool near = true;
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      t[e] = (to_compute(x.v[e]) - local[e].m) * kLog2e;
+      near = near && t[e] <= kSlack;
+    }
+    if (near) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) local[e].s += stat_exp2(t[e]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) step<1>(local[e], x.v[e], 0);
+    }
+  }
   template <int VEC> __device__ static Acc to_acc(Acc local) { return local; }
   // A slice whose maximum is +inf is NaN throughout (inf - inf), as the plain three-pass form gives.
   __device__ static Out finish(Acc a, long long, bool) {
@@ -195,5 +217,9 @@ struct MomentsReducer {
   }
   __device__ static Out finish(Acc a, long long, bool) { return Out{a.mean, a.m2 / a.n}; }
 };
+
+// Whether a reducer steps V neighbouring columns at once (step_columns above).
+template <typename R, typename = void> struct has_column_step : std::false_type {};
+template <typename R> struct has_column_step<R, std::void_t<decltype(R::kColumnStep)>> : std::true_type {};
 
 }  // namespace tq
