@@ -128,7 +128,7 @@ struct SoftmaxStatReducer {
   // latency of every element was exposed, and the pass ran at that latency rather than at the memory's
   // rate). The rare path is the per-element step; both give the same bits as V calls of `step`.
   static constexpr bool kColumnStep = true;
-  template <int V> __device__ static void step_columns(Acc (&local)[V], const Vec<T, V>& x) {
+  template <int V> __device__ static void step_columns(Acc (&local)[V], const Vec<T, V>& x, long long) {
     float t[V];
     bool near = true;
 #pragma unroll
@@ -220,6 +220,6 @@ struct MomentsReducer {
 
 // Whether a reducer steps V neighbouring columns at once (step_columns above).
 template <typename R, typename = void> struct has_column_step : std::false_type {};
-template <typename R> struct has_column_step<R, std::void_t<decltype(R::kColumnStep)>> : std::true_type {};
+template <typename R> struct has_column_step<R, std::void_t<decltype(R::kColumnStep)>> : std::bool_constant<R::kColumnStep> {};
 
 }  // namespace tq
