@@ -239,6 +239,27 @@ struct PairState<T, 0> {
     }
     sum = __fadd2_rn(sum, make_float2(stat_exp2(t.x), stat_exp2(t.y)));
   }
+  // One row of a thread's P pairs behind a single test, so that the common path is P independent
+  // scale / ex2 / add chains with no branch between them; the rare path is `step`, pair by pair.
+  template <int P>
+  __device__ static void step_row(PairState (&pairs)[P], const Vec<T, 2 * P>& x) {
+    constexpr float kLog2e = 1.4426950408889634f;
+    float2 t[P];
+    float worst = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < P; ++e) {
+      t[e] = __fmul2_rn(__fadd2_rn(make_float2(to_compute(x.v[2 * e]), to_compute(x.v[2 * e + 1])), pairs[e].negated_reference),
+                        make_float2(kLog2e, kLog2e));
+      worst = ExtremeReducer<float, true>::combine(worst, ExtremeReducer<float, true>::combine(t[e].x, t[e].y));
+    }
+    if (!(worst <= SoftmaxStatReducer<T>::kSlack)) {
+#pragma unroll
+      for (int e = 0; e < P; ++e) pairs[e].step(x.v[2 * e], x.v[2 * e + 1]);
+      return;
+    }
+#pragma unroll
+    for (int e = 0; e < P; ++e) pairs[e].sum = __fadd2_rn(pairs[e].sum, make_float2(stat_exp2(t[e].x), stat_exp2(t[e].y)));
+  }
   __device__ float4 packed(int) const { return make_float4(-negated_reference.x, sum.x, -negated_reference.y, sum.y); }
 };
 
@@ -256,6 +277,11 @@ struct PairState<T, 1> {
     const float2 d = __fadd2_rn(make_float2(to_compute(a), to_compute(b)), negated_pivot);
     s1 = __fadd2_rn(s1, d);
     s2 = __ffma2_rn(d, d, s2);
+  }
+  template <int P>
+  __device__ static void step_row(PairState (&pairs)[P], const Vec<T, 2 * P>& x) {
+#pragma unroll
+    for (int e = 0; e < P; ++e) pairs[e].step(x.v[2 * e], x.v[2 * e + 1]);
   }
   __device__ float4 packed(int count) const {
     using R = MomentsReducer<T>;
@@ -617,8 +643,7 @@ __global__ void __launch_bounds__(kPanelThreads, 1) panel_normalize_kernel(const
 #pragma unroll
       for (int i = 0; i < kRowsPerWarp; ++i) {
         const Vec<T, V> x = mine[i * kGroupWarps * (kPieceBytes / 16)];
-#pragma unroll
-        for (int e = 0; e < V / 2; ++e) local[e].step(x.v[2 * e], x.v[2 * e + 1]);
+        PairState<T, KIND>::template step_row<V / 2>(local, x);
       }
       __syncwarp();
       if (lane == 0) barrier_arrive(empty_s0 + 8 * stage);
