@@ -118,20 +118,40 @@ class GraphedRecipe:
     def _signature(args) -> tuple:
         return tuple((tuple(a.shape), a.dtype, a.device.index, tuple(a.stride())) if isinstance(a, torch.Tensor) else ("scalar", a) for a in args)
 
+    @staticmethod
+    def static_copies(args) -> list:
+        """The buffers a capture reads. A module parameter is read where it lives (its storage outlasts
+        the call, and an in-place update is seen by the next replay); everything else is cloned and
+        refreshed by a copy per call. A block's dozen weights would otherwise cost a dozen copy
+        launches per call, which is what a small batch's call then consists of."""
+        return [a if isinstance(a, torch.nn.Parameter) else a.clone() for a in args]
+
+    @staticmethod
+    def refresh(static_inputs, args) -> bool:
+        """Brings the captured buffers up to date; False when a parameter was REPLACED since the
+        capture (another storage), which the capture cannot follow."""
+        for static, arg in zip(static_inputs, args):
+            if static is arg or not isinstance(static, torch.Tensor) or static.data_ptr() == arg.data_ptr():
+                continue
+            if isinstance(static, torch.nn.Parameter):
+                return False
+            static.copy_(arg)
+        return True
+
     def run(self, *args):
         key = self._signature(args)
         entry = self._graphs.get(key)
         if entry is not None:
             graph, static_inputs, outputs = entry
-            for static, arg in zip(static_inputs, args):
-                if isinstance(static, torch.Tensor) and static.data_ptr() != arg.data_ptr():
-                    static.copy_(arg)
-            graph.replay()
-            return outputs
+            if self.refresh(static_inputs, args):
+                graph.replay()
+                return outputs
+            del self._graphs[key]   # captured again on the next call
+            return self.recipe.run(*args)
         if key not in self._seen or not all(isinstance(a, torch.Tensor) and a.is_cuda for a in args):
             self._seen.add(key)
             return self.recipe.run(*args)
-        static_inputs = [a.clone() for a in args]
+        static_inputs = self.static_copies(args)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
@@ -181,7 +201,7 @@ class NativeRecipe:
         entry = self._recorded.get(key)
         if entry is None:
             self.recipe.run(*args)  # an eager run first: modules loaded, scratch allocated
-            static_inputs = [a.clone() for a in args]
+            static_inputs = GraphedRecipe.static_copies(args)
             handle = ctypes.c_void_p()
             self._lib.check(self._lib.lib.tq_recipe_create(ctypes.byref(handle)))
             kept: list = []
@@ -199,9 +219,10 @@ class NativeRecipe:
             entry = (handle, static_inputs, outputs, kept)
             self._recorded[key] = entry
         handle, static_inputs, outputs, _ = entry
-        for static, arg in zip(static_inputs, args):
-            if static.data_ptr() != arg.data_ptr():
-                static.copy_(arg)
+        if not GraphedRecipe.refresh(static_inputs, args):
+            self._lib.check(self._lib.lib.tq_recipe_destroy(handle))   # a parameter was replaced: record again next time
+            del self._recorded[key]
+            return self.recipe.run(*args)
         device = args[0].device.index if args else torch.cuda.current_device()
         stream = torch.cuda.current_stream(device).cuda_stream
         self._lib.check(self._lib.lib.tq_recipe_run(handle, device, ctypes.c_void_p(stream)))

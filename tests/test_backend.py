@@ -258,6 +258,51 @@ def test_decoder_block_matches_eager_cpu(graphed, d, heads, t):
     assert ("attention" in counts) == (d // heads <= 128) and holder["fn"].recipes[0].interpreted == []
 
 
+def test_captured_inputs_read_parameters_in_place_and_copy_the_rest():
+    from tessiq_b200.executor import GraphedRecipe
+
+    weight = torch.nn.Parameter(torch.randn(4, 4))
+    x = torch.randn(2, 4)
+    static = GraphedRecipe.static_copies([weight, x])
+    assert static[0] is weight and static[1] is not x and torch.equal(static[1], x)
+    newer = torch.randn(2, 4)
+    assert GraphedRecipe.refresh(static, [weight, newer]) and torch.equal(static[1], newer)   # activations are copied in
+    with torch.no_grad():
+        weight.mul_(2.0)                                                                      # an in-place update needs no copy
+    assert GraphedRecipe.refresh(static, [weight, newer]) and static[0] is weight
+    replaced = torch.nn.Parameter(torch.randn(4, 4))
+    assert not GraphedRecipe.refresh(static, [replaced, newer])                               # another storage: capture again
+    assert torch.equal(static[0], weight)                                                     # and the old one was not written to
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("option", ["cuda_graph", "native"])
+def test_replays_see_parameters_updated_in_place(option):
+    # the capture reads the module's parameters where they live: an optimiser-style in-place update
+    # between two replays changes the next result, with no copy of the weights per call
+    from tessiq_b200.backend import compile_graph
+
+    torch._dynamo.reset()
+    torch.manual_seed(5)
+    model = torch.nn.Sequential(torch.nn.LayerNorm(256), torch.nn.Linear(256, 512), torch.nn.GELU(approximate="tanh")).eval().bfloat16().cuda()
+    x = torch.randn(512, 256).bfloat16().cuda()
+
+    def backend(gm, inputs):
+        return compile_graph(gm, inputs, options={option: True})
+
+    compiled = torch.compile(model, backend=backend)
+    with torch.no_grad():
+        for _ in range(3):  # eager, capture or record, replay
+            first = compiled(x).clone()
+        torch.testing.assert_close(first.float(), model(x).float(), rtol=2e-2, atol=2e-2)
+        model[1].bias.add_(1.0)
+        model[0].weight.mul_(0.5)
+        second = compiled(x).clone()
+        expected = model(x).float()
+    torch.testing.assert_close(second.float(), expected, rtol=2e-2, atol=2e-2)
+    assert (second.float() - first.float()).abs().max().item() > 0.1
+
+
 @pytest.mark.gpu
 def test_kernel_costs_lists_every_kernel_slowest_first():
     from tessiq_b200.backend import build_recipe
