@@ -106,34 +106,37 @@ def _nodes_in(structure) -> list[fx.Node]:
 
 class GraphedRecipe:
     """Runs a recipe eagerly the first time it sees a signature of input shapes, captures it into a
-    CUDA graph the second time, and replays the graph from then on (inputs are copied into the
-    graph's static buffers; outputs are the graph's static outputs, valid until the next call)."""
+    CUDA graph the second time, and replays the graph from then on (outputs are the graph's static
+    outputs, valid until the next call; how the inputs reach the graph: `static_copies`)."""
 
     def __init__(self, recipe: Recipe):
         self.recipe = recipe
         self._seen: set = set()
         self._graphs: dict = {}
+        self._moving: set = set()    # signatures whose inputs came in more than one storage
 
     @staticmethod
     def _signature(args) -> tuple:
         return tuple((tuple(a.shape), a.dtype, a.device.index, tuple(a.stride())) if isinstance(a, torch.Tensor) else ("scalar", a) for a in args)
 
     @staticmethod
-    def static_copies(args) -> list:
+    def static_copies(args, borrow: bool = False) -> list:
         """The buffers a capture reads. A module parameter is read where it lives (its storage outlasts
-        the call, and an in-place update is seen by the next replay); everything else is cloned and
-        refreshed by a copy per call. A block's dozen weights would otherwise cost a dozen copy
-        launches per call, which is what a small batch's call then consists of."""
-        return [a if isinstance(a, torch.nn.Parameter) else a.clone() for a in args]
+        the call, and an in-place update is seen by the next replay): a block's dozen weights would
+        otherwise cost a dozen copy launches per call, which is what a small batch's call then consists
+        of. Other tensors are cloned and refreshed by a copy per call, unless `borrow` says to read them
+        in place too (a caller that fills the same input buffer for every call)."""
+        return [a if borrow or isinstance(a, torch.nn.Parameter) else a.clone() for a in args]
 
     @staticmethod
-    def refresh(static_inputs, args) -> bool:
-        """Brings the captured buffers up to date; False when a parameter was REPLACED since the
-        capture (another storage), which the capture cannot follow."""
+    def refresh(static_inputs, args, borrowed: bool = False) -> bool:
+        """Brings the captured buffers up to date; False when a tensor the capture reads in place came
+        in ANOTHER storage this time (a replaced parameter, a borrowed input), which the capture cannot
+        follow. Nothing the caller owns is ever written to."""
         for static, arg in zip(static_inputs, args):
             if static is arg or not isinstance(static, torch.Tensor) or static.data_ptr() == arg.data_ptr():
                 continue
-            if isinstance(static, torch.nn.Parameter):
+            if borrowed or isinstance(static, torch.nn.Parameter):
                 return False
             static.copy_(arg)
         return True
@@ -142,16 +145,22 @@ class GraphedRecipe:
         key = self._signature(args)
         entry = self._graphs.get(key)
         if entry is not None:
-            graph, static_inputs, outputs = entry
-            if self.refresh(static_inputs, args):
+            graph, static_inputs, outputs, borrowed = entry
+            if self.refresh(static_inputs, args, borrowed):
                 graph.replay()
                 return outputs
-            del self._graphs[key]   # captured again on the next call
+            del self._graphs[key]   # captured again on the next call, with buffers of its own if an input moved
+            if borrowed:
+                self._moving.add(key)
             return self.recipe.run(*args)
         if key not in self._seen or not all(isinstance(a, torch.Tensor) and a.is_cuda for a in args):
             self._seen.add(key)
             return self.recipe.run(*args)
-        static_inputs = self.static_copies(args)
+        # The first capture of a signature reads every input where the caller keeps it (no copy per
+        # call); a caller that then comes with the same shapes in other storage gets a capture with
+        # buffers of its own and a copy per call.
+        borrowed = key not in self._moving
+        static_inputs = self.static_copies(args, borrow=borrowed)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
@@ -161,7 +170,7 @@ class GraphedRecipe:
             with torch.cuda.graph(graph, stream=side):
                 outputs = self.recipe.run(*static_inputs)
         torch.cuda.current_stream().wait_stream(side)
-        self._graphs[key] = (graph, static_inputs, outputs)
+        self._graphs[key] = (graph, static_inputs, outputs, borrowed)
         graph.replay()
         return outputs
 

@@ -273,6 +273,11 @@ def test_captured_inputs_read_parameters_in_place_and_copy_the_rest():
     replaced = torch.nn.Parameter(torch.randn(4, 4))
     assert not GraphedRecipe.refresh(static, [replaced, newer])                               # another storage: capture again
     assert torch.equal(static[0], weight)                                                     # and the old one was not written to
+    borrowed = GraphedRecipe.static_copies([weight, x], borrow=True)
+    assert borrowed[1] is x and GraphedRecipe.refresh(borrowed, [weight, x], borrowed=True)   # the caller's own buffer, read in place
+    kept = newer.clone()
+    assert not GraphedRecipe.refresh(borrowed, [weight, newer], borrowed=True)                # other storage: capture again,
+    assert torch.equal(newer, kept) and borrowed[1] is x                                      # nothing of the caller's is written to
 
 
 @pytest.mark.gpu
@@ -301,6 +306,13 @@ def test_replays_see_parameters_updated_in_place(option):
         expected = model(x).float()
     torch.testing.assert_close(second.float(), expected, rtol=2e-2, atol=2e-2)
     assert (second.float() - first.float()).abs().max().item() > 0.1
+    # the same buffer refilled is read in place; the same shapes in other storage get a capture with buffers of its own
+    with torch.no_grad():
+        x.copy_(torch.randn(512, 256).bfloat16())
+        torch.testing.assert_close(compiled(x).float(), model(x).float(), rtol=2e-2, atol=2e-2)
+        for seed in range(4):
+            other = torch.randn(512, 256, generator=torch.Generator().manual_seed(seed)).bfloat16().cuda()
+            torch.testing.assert_close(compiled(other).float(), model(other).float(), rtol=2e-2, atol=2e-2)
 
 
 @pytest.mark.gpu
