@@ -262,64 +262,80 @@ tq_status run_pack(const View& view, long long total, const void* src, void* dst
 // The register-block transpose with a normalisation applied on the way: out[b][c][r] =
 // f(in[b][r][c]). KIND 0: softmax over r with per-column statistics (max, 1/sum); KIND 1:
 // LayerNorm over r with per-column (mean, variance) and weight/bias indexed by r. A thread loads
-// V vectors of V consecutive c (rows r0 .. r0+V-1), and stores V vectors of V consecutive r.
-template <typename T, int V, int KIND>
+// RB vectors of V consecutive c (rows r0 .. r0+RB-1), and stores V vectors of RB consecutive r.
+// A warp is kLanesR lanes along r by kLanesC along c, chosen so that its stores are 64-byte runs
+// (kLanesR * RB elements) and its loads at least that; a CTA is 4 warps along r by 2 along c.
+// RB is 4 for every type: with 8 x 8 blocks of 2-byte elements a thread held 32 registers of data
+// and 16 of statistics, 63 in all, and four CTAs per SM were too few to keep the memory busy (the
+// same kernel with the statistics replaced by constants, 48 registers, five CTAs: 100 us against
+// 127 at [32768, 4096] bf16, and it is not the statistics' loads that cost, see below).
+template <typename T, int V, int RB, int KIND>
 __global__ void __launch_bounds__(256)
 transpose_normalize_kernel(const T* __restrict__ in, T* __restrict__ out, const float2* __restrict__ stats,
                            const T* __restrict__ weight, const T* __restrict__ bias, long long rows, long long cols,
                            long long row_tiles, long long col_tiles, float eps) {
-  constexpr int kTile = 16 * V;
+  constexpr int kLanesR = 64 / (RB * static_cast<int>(sizeof(T)));   // 4 (f32) or 8 (2-byte types)
+  constexpr int kLanesC = 32 / kLanesR;
+  constexpr int kTileRows = 4 * kLanesR * RB, kTileCols = 2 * kLanesC * V;
+  static_assert(kLanesC * V == 32, "a warp's columns are one statistic per lane");
   unsigned tile_id = blockIdx.x;   // fewer than 2^31 tiles: 32-bit divisions
-  const long long col_tile = tile_id % static_cast<unsigned>(col_tiles);
-  tile_id /= static_cast<unsigned>(col_tiles);
   const long long row_tile = tile_id % static_cast<unsigned>(row_tiles);
-  const long long batch = tile_id / static_cast<unsigned>(row_tiles);
+  tile_id /= static_cast<unsigned>(row_tiles);
+  const long long col_tile = tile_id % static_cast<unsigned>(col_tiles);
+  const long long batch = tile_id / static_cast<unsigned>(col_tiles);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int c_block = (lane & 7) + 8 * (warp & 1);
-  const int r_block = (lane >> 3) + 4 * (warp >> 1);
-  const long long c0 = col_tile * kTile + c_block * V, r0 = row_tile * kTile + r_block * V;
-  if (r0 >= rows || c0 >= cols) return;
+  const int lane_c = lane % kLanesC, lane_r = lane / kLanesC;
+  const long long warp_c0 = col_tile * kTileCols + (warp & 1) * 32;
+  const long long c0 = warp_c0 + lane_c * V, r0 = row_tile * kTileRows + ((warp >> 1) * kLanesR + lane_r) * RB;
+  const bool active = r0 < rows && c0 < cols;
   const T* source = in + batch * rows * cols;
   T* target = out + batch * rows * cols;
 
-  Vec<T, V> block[V];
+  Vec<T, V> block[RB];
 #pragma unroll
-  for (int i = 0; i < V; ++i) block[i] = load_stream<T, V>(source + (r0 + i) * cols + c0);
-
-  float first[V], second[V];   // per column c0 + j
+  for (int i = 0; i < RB; ++i) {
+    if (active) {
+      block[i] = load_stream<T, V>(source + (r0 + i) * cols + c0);
+    } else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) block[i].v[e] = T();
+    }
+  }
+  // The statistics of the warp's 32 columns: one coalesced request (lane l fetches column l) and two
+  // shuffles per column, instead of V requests per thread whose lanes touch separate sectors.
+  float2 held = make_float2(0.f, 0.f);
+  if (warp_c0 + lane < cols) held = __ldg(stats + batch * cols + warp_c0 + lane);
+  if (KIND == 1) held.y = rsqrtf(held.y + eps);
+  float scale[RB], shift[RB];    // per row r0 + i (LayerNorm only); r0 is a multiple of RB: one vector each
+  Vec<T, RB> weights, biases;
+  if (KIND == 1 && weight != nullptr && active) weights = *reinterpret_cast<const Vec<T, RB>*>(weight + r0);
+  if (KIND == 1 && bias != nullptr && active) biases = *reinterpret_cast<const Vec<T, RB>*>(bias + r0);
+#pragma unroll
+  for (int i = 0; i < RB; ++i) {
+    scale[i] = (KIND == 1 && weight != nullptr && active) ? to_compute(weights.v[i]) : 1.0f;
+    shift[i] = (KIND == 1 && bias != nullptr && active) ? to_compute(biases.v[i]) : 0.0f;
+  }
 #pragma unroll
   for (int j = 0; j < V; ++j) {
-    const float2 st = __ldg(stats + batch * cols + c0 + j);
-    first[j] = st.x;
-    second[j] = KIND == 0 ? st.y : rsqrtf(st.y + eps);
-  }
-  float scale[V], shift[V];    // per row r0 + i (LayerNorm only); r0 is a multiple of V: one vector each
-  Vec<T, V> weights, biases;
-  if (KIND == 1 && weight != nullptr) weights = *reinterpret_cast<const Vec<T, V>*>(weight + r0);
-  if (KIND == 1 && bias != nullptr) biases = *reinterpret_cast<const Vec<T, V>*>(bias + r0);
+    // column c0 + j's statistics, from the lane that fetched them (every lane takes part in the shuffles)
+    const float first = __shfl_sync(0xffffffffu, held.x, lane_c * V + j);
+    const float second = __shfl_sync(0xffffffffu, held.y, lane_c * V + j);
+    Vec<T, RB> line;
 #pragma unroll
-  for (int i = 0; i < V; ++i) {
-    scale[i] = (KIND == 1 && weight != nullptr) ? to_compute(weights.v[i]) : 1.0f;
-    shift[i] = (KIND == 1 && bias != nullptr) ? to_compute(biases.v[i]) : 0.0f;
-  }
-#pragma unroll
-  for (int j = 0; j < V; ++j) {
-    Vec<T, V> line;
-#pragma unroll
-    for (int i = 0; i < V; ++i) {
+    for (int i = 0; i < RB; ++i) {
       const float x = to_compute(block[i].v[j]);
       float y;
       if constexpr (KIND == 0) {
         float e;
-        const float t = (x - first[j]) * 1.4426950408889634f;
+        const float t = (x - first) * 1.4426950408889634f;
         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
-        y = e * second[j];
+        y = e * second;
       } else {
-        y = (x - first[j]) * second[j] * scale[i] + shift[i];
+        y = (x - first) * second * scale[i] + shift[i];
       }
       line.v[i] = from_compute<T, float>(y);
     }
-    store_stream<T, V>(target + (c0 + j) * rows + r0, line);
+    if (active) store_stream<T, RB>(target + (c0 + j) * rows + r0, line);
   }
 }
 
@@ -327,14 +343,16 @@ template <typename T, int KIND>
 tq_status run_transpose_normalize(const void* in, void* out, const void* stats, const void* weight, const void* bias,
                                   long long batch, long long rows, long long cols, float eps, cudaStream_t stream) {
   constexpr int kV = 16 / sizeof(T);
-  constexpr int kTile = 16 * kV;
+  constexpr int kRB = 4;
+  constexpr int kLanesR = 64 / (kRB * static_cast<int>(sizeof(T)));
+  constexpr int kTileRows = 4 * kLanesR * kRB, kTileCols = 2 * (32 / kLanesR) * kV;
   TQ_REQUIRE(rows % kV == 0 && cols % kV == 0 && aligned_to(in, 16) && aligned_to(out, 16) && aligned_to(stats, 8) &&
                  (weight == nullptr || aligned_to(weight, 16)) && (bias == nullptr || aligned_to(bias, 16)),
              TQ_UNSUPPORTED, "the transposing normalisation needs extents that are multiples of %d and 16-byte-aligned tensors", kV);
-  const long long row_tiles = (rows + kTile - 1) / kTile, col_tiles = (cols + kTile - 1) / kTile;
+  const long long row_tiles = (rows + kTileRows - 1) / kTileRows, col_tiles = (cols + kTileCols - 1) / kTileCols;
   const long long blocks = batch * row_tiles * col_tiles;
   TQ_REQUIRE(blocks <= 0x7fffffffLL, TQ_UNSUPPORTED, "%lld tiles are more than a grid holds", blocks);
-  transpose_normalize_kernel<T, kV, KIND><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+  transpose_normalize_kernel<T, kV, kRB, KIND><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
       static_cast<const T*>(in), static_cast<T*>(out), static_cast<const float2*>(stats), static_cast<const T*>(weight),
       static_cast<const T*>(bias), rows, cols, row_tiles, col_tiles, eps);
   return check_launch("transpose_normalize_kernel");
