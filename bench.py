@@ -685,6 +685,7 @@ def decoder_block(dev: str, stream, batch: int = 64) -> dict:
 
     from tessiq_b200.backend import compile_graph
 
+    torch._dynamo.reset()   # each batch size compiles for itself: a second size in one process would otherwise get symbolic shapes
     d, heads, tokens = 768, 12, 1024
 
     class Block(torch.nn.Module):

@@ -126,7 +126,7 @@ class GraphedRecipe:
         otherwise cost a dozen copy launches per call, which is what a small batch's call then consists
         of. Other tensors are cloned and refreshed by a copy per call, unless `borrow` says to read them
         in place too (a caller that fills the same input buffer for every call)."""
-        return [a if borrow or isinstance(a, torch.nn.Parameter) else a.clone() for a in args]
+        return [a if borrow or not isinstance(a, torch.Tensor) or isinstance(a, torch.nn.Parameter) else a.clone() for a in args]
 
     @staticmethod
     def refresh(static_inputs, args, borrowed: bool = False) -> bool:
@@ -153,7 +153,9 @@ class GraphedRecipe:
             if borrowed:
                 self._moving.add(key)
             return self.recipe.run(*args)
-        if key not in self._seen or not all(isinstance(a, torch.Tensor) and a.is_cuda for a in args):
+        # sizes that reach the recipe as integers (symbolic shapes) are part of the signature: a capture serves one set of them
+        tensors = [a for a in args if isinstance(a, torch.Tensor)]
+        if key not in self._seen or not tensors or not all(a.is_cuda for a in tensors):
             self._seen.add(key)
             return self.recipe.run(*args)
         # The first capture of a signature reads every input where the caller keeps it (no copy per

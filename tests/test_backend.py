@@ -333,18 +333,22 @@ def test_kernel_costs_lists_every_kernel_slowest_first():
 
 
 @pytest.mark.gpu
-def test_one_compiled_graph_serves_changing_sizes():
+@pytest.mark.parametrize("graphed", [False, True])
+def test_one_compiled_graph_serves_changing_sizes(graphed):
     # symbolic sizes: extents are launch arguments, not part of the kernels (the reference's
-    # tests/python/test_dynamic_shapes.py holds its kernels to the same)
+    # tests/python/test_dynamic_shapes.py holds its kernels to the same); with CUDA-graph replay the
+    # sizes arrive as integers beside the tensors and every set of them gets a capture of its own
     from oracle import tessiq0
     from tessiq_b200.backend import compile_graph
 
     torch._dynamo.reset()
     seen = []
+    compiled_fns = []
 
     def backend(gm, inputs):
         seen.append(gm)
-        return compile_graph(gm, inputs)
+        compiled_fns.append(compile_graph(gm, inputs, options={"cuda_graph": graphed}))
+        return compiled_fns[-1]
 
     def fn(x, b):
         return torch.softmax(chain1(x, b), -1)
@@ -352,12 +356,18 @@ def test_one_compiled_graph_serves_changing_sizes():
     compiled = torch.compile(fn, backend=backend, dynamic=True)
     g = torch.Generator().manual_seed(1)
     b = torch.randn(512, generator=g) * 0.02
-    for rows in (64, 200, 33):
+    bd = b.cuda()
+    buffer = torch.empty(200, 512, device="cuda")     # the caller's own input buffer, refilled per call
+    for rows in (64, 200, 33, 200, 200, 64, 64):
         x = torch.randn(rows, 512, generator=g)
-        got = compiled(x.cuda(), b.cuda())
+        buffer[:rows].copy_(x)
+        got = compiled(buffer[:rows], bd)
         ref = tessiq0.softmax(tessiq0.chain_gelu_sigmoid(x, b), -1)
         torch.testing.assert_close(got.cpu(), ref, rtol=1e-5, atol=1e-6)
     assert len(seen) == 1
+    if graphed:
+        runner = compiled_fns[0].runners[0]
+        assert len(runner._graphs) >= 2          # 200 and 64 rows came back and were captured
 
 
 def test_native_recipe_records_without_a_gpu_launch():
