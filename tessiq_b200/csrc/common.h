@@ -195,6 +195,15 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_compute<__nv_bfloat16,
   return __float2bfloat16_rn(v);
 }
 
+// Two neighbouring results rounded and packed with one conversion (`to` is 4-byte aligned for the 2-byte types).
+__device__ __forceinline__ void store_pair(__nv_bfloat16* to, float2 y) { *reinterpret_cast<__nv_bfloat162*>(to) = __floats2bfloat162_rn(y.x, y.y); }
+__device__ __forceinline__ void store_pair(__half* to, float2 y) { *reinterpret_cast<__half2*>(to) = __floats2half2_rn(y.x, y.y); }
+template <typename T>
+__device__ __forceinline__ void store_pair(T* to, float2 y) {
+  to[0] = from_compute<T, float>(y.x);
+  to[1] = from_compute<T, float>(y.y);
+}
+
 // A vector of N elements of T moved with one instruction when N*sizeof(T) is 4, 8 or 16 bytes.
 template <typename T, int N>
 struct alignas(sizeof(T) * N) Vec {

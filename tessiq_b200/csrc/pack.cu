@@ -271,15 +271,6 @@ __device__ __forceinline__ float half_element(const Vec<__half, V>& v, int j) { 
 template <typename T, int V>
 __device__ __forceinline__ float half_element(const Vec<T, V>& v, int j) { return to_compute(v.v[j]); }
 
-// Two results rounded and packed with one conversion.
-__device__ __forceinline__ void store_pair(__nv_bfloat16* to, float2 y) { *reinterpret_cast<__nv_bfloat162*>(to) = __floats2bfloat162_rn(y.x, y.y); }
-__device__ __forceinline__ void store_pair(__half* to, float2 y) { *reinterpret_cast<__half2*>(to) = __floats2half2_rn(y.x, y.y); }
-template <typename T>
-__device__ __forceinline__ void store_pair(T* to, float2 y) {
-  to[0] = from_compute<T, float>(y.x);
-  to[1] = from_compute<T, float>(y.y);
-}
-
 // The register-block transpose with a normalisation applied on the way: out[b][c][r] =
 // f(in[b][r][c]). KIND 0: softmax over r with per-column statistics (max, 1/sum); KIND 1:
 // LayerNorm over r with per-column (mean, variance) and weight/bias indexed by r. A thread loads

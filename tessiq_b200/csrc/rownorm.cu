@@ -193,15 +193,21 @@ __device__ __forceinline__ void finish_row(Vec<T, VEC> (&x)[K], int first, int s
     for (int j = 0; j < K; ++j) {
       if (first + j * step < vectors) {
         Vec<OutT, VEC> y;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
+        auto result = [&](int e) {
           float value;
           if constexpr (kKeepsFloats) {
             value = widen(x[j], e);
           } else {
             value = exp2_approx((widen(x[j], e) - row_max) * kLog2e);
           }
-          y.v[e] = from_compute<OutT, float>(value * inverse);
+          return value * inverse;
+        };
+        if constexpr (sizeof(OutT) == 2 && VEC % 2 == 0) {   // one conversion per pair of results
+#pragma unroll
+          for (int e = 0; e < VEC; e += 2) store_pair(&y.v[e], make_float2(result(e), result(e + 1)));
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) y.v[e] = from_compute<OutT, float>(result(e));
         }
         store_stream<OutT, VEC>(out_row + static_cast<long long>(first + j * step) * VEC, y);
       }
@@ -246,12 +252,18 @@ __device__ __forceinline__ void finish_row(Vec<T, VEC> (&x)[K], int first, int s
         if (weight) w = *reinterpret_cast<const Vec<T, VEC>*>(weight + offset);
         if (bias) b = *reinterpret_cast<const Vec<T, VEC>*>(bias + offset);
         Vec<OutT, VEC> y;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
+        auto result = [&](int e) {
           float value = (widen(x[j], e) - mean) * rstd;
-          if (weight) value *= to_compute(w.v[e]);
-          if (bias) value += to_compute(b.v[e]);
-          y.v[e] = from_compute<OutT, float>(value);
+          if (weight) value *= widen(w, e);
+          if (bias) value += widen(b, e);
+          return value;
+        };
+        if constexpr (sizeof(OutT) == 2 && VEC % 2 == 0) {   // one conversion per pair of results
+#pragma unroll
+          for (int e = 0; e < VEC; e += 2) store_pair(&y.v[e], make_float2(result(e), result(e + 1)));
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) y.v[e] = from_compute<OutT, float>(result(e));
         }
         store_stream<OutT, VEC>(out_row + offset, y);
       }
