@@ -273,6 +273,9 @@ def test_captured_inputs_read_parameters_in_place_and_copy_the_rest():
     replaced = torch.nn.Parameter(torch.randn(4, 4))
     assert not GraphedRecipe.refresh(static, [replaced, newer])                               # another storage: capture again
     assert torch.equal(static[0], weight)                                                     # and the old one was not written to
+    sized = GraphedRecipe.static_copies([weight, 7, x])                                      # a symbolic size arrives as an integer
+    assert sized[1] == 7 and sized[2] is not x and GraphedRecipe.refresh(sized, [weight, 7, newer]) and torch.equal(sized[2], newer)
+    assert GraphedRecipe._signature([weight, 7, x]) != GraphedRecipe._signature([weight, 8, x])  # ... and keys the capture
     borrowed = GraphedRecipe.static_copies([weight, x], borrow=True)
     assert borrowed[1] is x and GraphedRecipe.refresh(borrowed, [weight, x], borrowed=True)   # the caller's own buffer, read in place
     kept = newer.clone()
